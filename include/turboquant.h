@@ -1,0 +1,212 @@
+/*
+ * libturboquant — C ABI of the B200 (sm_100a) compressed-KV library.
+ *
+ * Part 1 re-exports, with identical names, argument order, struct layouts and
+ * return codes, the `extern "C"` surface of the reference project
+ * (src/tq_capi.cpp), so its ctypes bindings (tq_backend/turboquant_wrapper.py)
+ * load this library unchanged.  Part 2 adds entry points the reference does
+ * not have (batched paged GQA decode, split-KV partials and their merge,
+ * [H,N,D] dequant, chunk prefill, host page allocator / block table).
+ *
+ * Conventions (all from the reference):
+ *   return 0 ok, -1 null/invalid argument, -2 CUDA or shape error with the
+ *   text available from tq_last_error() (thread-local).
+ *   Every pointer except structs is DEVICE memory owned by the caller.
+ *   Launches are asynchronous on `stream`; the library never synchronises.
+ *   key/value/out_key/out_value: fp16 [num_tokens, num_kv_heads, head_dim].
+ *   slot_mapping: int32 [num_tokens]; slot = physical_block*block_size + t.
+ *   query/output: fp16 [num_queries, num_kv_heads, head_dim] — one query row
+ *   per KV head (GQA group member g of kv-head h is row g).
+ * Supported shapes: head_dim == 128, block_size >= 1, num_kv_heads 1..32.
+ */
+#ifndef TURBOQUANT_H
+#define TURBOQUANT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tq_stream_t; /* cudaStream_t */
+typedef uint16_t tq_half;  /* IEEE binary16 bits (`half` in the reference) */
+
+/* include/tq_config.h:4-13 (32 bytes) */
+typedef struct TQConfig {
+    int block_size;     /* 16 */
+    int num_kv_heads;   /* 8 */
+    int head_dim;       /* 128 */
+    int nbits;          /* 4 */
+    int group_size;     /* 128 */
+    int page_alignment; /* 256 */
+    int scale_type;     /* TQScaleType::FP16 = 0 */
+    int quant_mode;     /* TQQuantMode::MSE_INT4 = 0 */
+} TQConfig;
+
+/* include/tq_turbo_prod.cuh:15-28 (64 bytes) */
+typedef struct TQTurboProdPageLayout {
+    size_t page_size_bytes;
+    size_t k4_codes_offset;
+    size_t k_residual_scales_offset;
+    size_t k_scales_offset;
+    size_t v4_codes_offset;
+    size_t v_scales_offset;
+    int k4_bytes_per_token_head;
+    int v4_bytes_per_token_head;
+    int scale_bytes_per_token_head;
+} TQTurboProdPageLayout;
+
+/* include/tq_turbo_mse_layout.h:5-15 (56 bytes) */
+typedef struct TQTurbomsePageLayout {
+    size_t code_bytes_per_token_head;
+    size_t norm_bytes_per_token_head;
+    size_t k_codes_offset;
+    size_t v_codes_offset;
+    size_t k_norms_offset;
+    size_t v_norms_offset;
+    size_t page_size_bytes;
+} TQTurbomsePageLayout;
+
+/* ------------------------------------------------------------------------ */
+/* Part 1 — the reference surface                                           */
+/* ------------------------------------------------------------------------ */
+
+/* src/tq_capi.cpp:17-19 */
+const char* tq_last_error(void);
+/* src/tq_capi.cpp:35-39 */
+int tq_make_default_config(TQConfig* out_cfg);
+/* src/tq_capi.cpp:41-47 -> src/tq_turbo_prod.cpp:7-39 */
+int tq_make_turbo_prod_layout(const TQConfig* cfg, TQTurboProdPageLayout* out_layout);
+/* src/tq_capi.cpp:118-124 -> src/tq_turbo_mse_layout.cpp:7-28 */
+int tq_make_turbo_mse_layout(const TQConfig* cfg, TQTurbomsePageLayout* out_layout);
+
+/* src/tq_capi.cpp:49-64 -> src/cuda/tq_turbo_prod_kernels.cu:110-260 */
+int tq_launch_turbo_prod_pack_kv(const tq_half* key, const tq_half* value,
+                                 const int32_t* slot_mapping, uint8_t* page_pool,
+                                 const TQTurboProdPageLayout* layout, const TQConfig* cfg,
+                                 int num_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:66-80 -> tq_turbo_prod_kernels.cu:265-341 */
+int tq_launch_turbo_prod_dequant_kv(const uint8_t* page_pool, const int32_t* slot_mapping,
+                                    tq_half* out_key, tq_half* out_value,
+                                    const TQTurboProdPageLayout* layout, const TQConfig* cfg,
+                                    int num_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:82-97 -> tq_turbo_prod_kernels.cu:346-434; logits fp32
+ * [(q*H + h)*num_kv_tokens + t], scaled by 1/sqrt(head_dim). */
+int tq_launch_turbo_prod_fused_attention_logits(const tq_half* query, const uint8_t* page_pool,
+                                                const int32_t* slot_mapping, float* logits,
+                                                const TQTurboProdPageLayout* layout,
+                                                const TQConfig* cfg, int num_queries,
+                                                int num_kv_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:99-114 -> tq_turbo_prod_kernels.cu:439-571 */
+int tq_launch_turbo_prod_fused_attention_output(const tq_half* query, const uint8_t* page_pool,
+                                                const int32_t* slot_mapping, tq_half* output,
+                                                const TQTurboProdPageLayout* layout,
+                                                const TQConfig* cfg, int num_queries,
+                                                int num_kv_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:126-141 -> src/cuda/tq_turbo_mse_kernels.cu:186-237 */
+int tq_launch_turbo_mse_pack_kv(const tq_half* key, const tq_half* value,
+                                const int32_t* slot_mapping, uint8_t* page_pool,
+                                const TQTurbomsePageLayout* layout, const TQConfig* cfg,
+                                int num_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:143-157 -> tq_turbo_mse_kernels.cu:239-287 */
+int tq_launch_turbo_mse_dequant_kv(const uint8_t* page_pool, const int32_t* slot_mapping,
+                                   tq_half* out_key, tq_half* out_value,
+                                   const TQTurbomsePageLayout* layout, const TQConfig* cfg,
+                                   int num_tokens, tq_stream_t stream);
+/* src/tq_capi.cpp:159-174 -> tq_turbo_mse_kernels.cu:302-417 */
+int tq_launch_turbo_mse_fused_attention_output(const tq_half* query, const uint8_t* page_pool,
+                                               const int32_t* slot_mapping, tq_half* output,
+                                               const TQTurbomsePageLayout* layout,
+                                               const TQConfig* cfg, int num_queries,
+                                               int num_kv_tokens, tq_stream_t stream);
+
+/* ------------------------------------------------------------------------ */
+/* Part 2 — additions (no counterpart in the reference's C API)             */
+/* ------------------------------------------------------------------------ */
+
+#define TQ_SCHEME_TURBO_PROD 0
+#define TQ_SCHEME_TURBO_MSE 1
+
+/* Floats per (sequence, query head) in a split-KV partial: the rotated-domain
+ * unnormalised accumulator acc[128], then the running maximum m (natural-log
+ * logit units) and the denominator l.  Same triple the reference's fused
+ * kernel carries in sh_m / sh_l / vaccum (tq_turbo_prod_kernels.cu:463-470). */
+#define TQ_PARTIAL_STRIDE 130
+
+/* Number of KV splits the decode kernels use for `batch` sequences of at most
+ * `max_kv_tokens` tokens on the current device, and the scratch bytes a call
+ * needs (partials for every split). */
+int tq_decode_num_splits(int batch, int max_kv_tokens, int num_kv_heads, int block_size);
+size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_splits);
+
+/* Batched paged GQA decode over compressed pages (generalises
+ * tq_turbo_prod_kernels.cu:439-571 / tq_turbo_mse_kernels.cu:302-417 to many
+ * sequences, block tables and grouped query heads).
+ *   query/output : fp16 [batch, num_q_heads, 128]; query head j reads kv head
+ *                  j / (num_q_heads / num_kv_heads).
+ *   block_tables : int32 [batch, table_stride]; token t of sequence b lives in
+ *                  slot block_tables[b][t / block_size]*block_size + t % block_size
+ *                  (src/tq_block_table.cpp:24-39).
+ *   seq_lens     : int32 [batch] cached tokens per sequence (0 allowed: zeros out).
+ *   kv_begin/kv_end : token range of every sequence this call attends to
+ *                  (clamped to seq_lens; pass 0 and INT32_MAX for all).
+ *   workspace    : device scratch of tq_decode_workspace_bytes(...) bytes, or
+ *                  NULL to use a per-device cache the library grows on demand.
+ *   partials_out : if non-NULL, fp32 [batch, num_q_heads, TQ_PARTIAL_STRIDE]
+ *                  receives the merged (acc, m, l) of this call's range and
+ *                  `output` may be NULL (used for multi-GPU KV splits).
+ * `layout` is a TQTurboProdPageLayout* or TQTurbomsePageLayout* per `scheme`. */
+int tq_decode_paged(int scheme, const tq_half* query, const uint8_t* page_pool,
+                    const int32_t* block_tables, int table_stride, const int32_t* seq_lens,
+                    tq_half* output, float* partials_out, const void* layout,
+                    const TQConfig* cfg, int batch, int num_q_heads, int max_kv_tokens,
+                    int kv_begin, int kv_end, void* workspace, size_t workspace_bytes,
+                    tq_stream_t stream);
+
+/* Log-sum-exp merge of `num_parts` partial sets laid out
+ * [num_parts, rows, TQ_PARTIAL_STRIDE] (e.g. an all-gather over ranks), then
+ * normalise, inverse rotation and fp16 store: output [rows, 128] with
+ * rows = batch*num_q_heads.  Query head of row r is r % num_q_heads. */
+int tq_merge_partials(const float* partials, int num_parts, tq_half* output, int rows,
+                      int num_q_heads, int num_kv_heads, tq_stream_t stream);
+
+/* Dequant straight into the [num_kv_heads, num_tokens, 128] layout a Hugging
+ * Face cache wants (fuses the permute().contiguous() of
+ * tq_backend/cag_store.py:250-251). */
+int tq_dequant_kv_hnd(int scheme, const uint8_t* page_pool, const int32_t* slot_mapping,
+                      tq_half* out_key, tq_half* out_value, const void* layout,
+                      const TQConfig* cfg, int num_tokens, tq_stream_t stream);
+
+/* Chunked query prefill over a turbo_mse prefix plus an optional causal fp16
+ * chunk.  query/output fp16 [batch, num_q_tokens, num_q_heads, 128];
+ * chunk_key/chunk_value fp16 [batch, num_q_tokens, num_kv_heads, 128] or NULL. */
+int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_pool,
+                         const int32_t* block_tables, int table_stride,
+                         const int32_t* seq_lens, const tq_half* chunk_key,
+                         const tq_half* chunk_value, tq_half* output,
+                         const TQTurbomsePageLayout* layout, const TQConfig* cfg, int batch,
+                         int num_q_tokens, int num_q_heads, tq_stream_t stream);
+
+/* Host-side page allocator and block table (LIFO free list and the slot
+ * formula of src/tq_allocator.cpp:5-31, src/tq_block_table.cpp:7-39; the pool
+ * memory itself stays with the caller). */
+typedef struct TQBlockTableHandle TQBlockTableHandle;
+TQBlockTableHandle* tq_block_table_create(int num_pages, int block_size);
+void tq_block_table_destroy(TQBlockTableHandle* h);
+int tq_block_table_free_pages(const TQBlockTableHandle* h);
+/* Appends `append_tokens` to sequence `seq_id`, allocating pages as needed,
+ * and writes their slots to slots_out[append_tokens] (host). -2 "out of blocks". */
+int tq_block_table_append(TQBlockTableHandle* h, int seq_id, int append_tokens,
+                          int32_t* slots_out);
+int tq_block_table_num_tokens(const TQBlockTableHandle* h, int seq_id);
+/* Copies the sequence's page ids to pages_out (host, capacity max_pages);
+ * returns the page count or -1. */
+int tq_block_table_pages(const TQBlockTableHandle* h, int seq_id, int32_t* pages_out,
+                         int max_pages);
+int tq_block_table_release(TQBlockTableHandle* h, int seq_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOQUANT_H */

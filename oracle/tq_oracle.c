@@ -1,0 +1,666 @@
+/*
+ * CPU oracle for the TurboCAG compressed-KV hot path (see tq_oracle.h).
+ * TEST INFRASTRUCTURE ONLY — never linked into the shipped library.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fopenmp -fPIC -shared  (see Makefile).
+ * -ffp-contract=off keeps every multiply and add separately rounded; the
+ * places where the reference's nvcc build fuses a multiply-add are written
+ * with fmaf() explicitly and say so.
+ */
+#include "tq_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* scalar helpers                                                            */
+/* ------------------------------------------------------------------------- */
+
+float orc_h2f(uint16_t h) {
+    _Float16 x;
+    memcpy(&x, &h, 2);
+    return (float)x;
+}
+
+uint16_t orc_f2h(float f) { /* round-to-nearest-even, as __float2half */
+    _Float16 x = (_Float16)f;
+    uint16_t h;
+    memcpy(&h, &x, 2);
+    return h;
+}
+
+#define h2f orc_h2f
+#define f2h orc_f2h
+
+/* rsqrtf(128.f) as the GPU evaluates it; fp32 nearest to 2^-3.5. */
+static uint32_t g_inv_sqrt_d_bits = 0x3DB504F3u;
+static int g_mse_pair_fma = 1;
+static int g_threads = 0;
+
+uint32_t orc_inv_sqrt_d_bits(void) { return g_inv_sqrt_d_bits; }
+void orc_set_inv_sqrt_d_bits(uint32_t b) { g_inv_sqrt_d_bits = b; }
+void orc_set_mse_pair_fma(int m) { g_mse_pair_fma = m; }
+void orc_set_threads(int n) { g_threads = n; }
+
+static int nthreads(void) {
+#ifdef _OPENMP
+    return g_threads > 0 ? g_threads : omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+static float inv_sqrt_d(int d) {
+    if (d == 128) {
+        float c;
+        memcpy(&c, &g_inv_sqrt_d_bits, 4);
+        return c;
+    }
+    return 1.0f / sqrtf((float)d);
+}
+
+/* tq_turbo_prod_kernels.cu:19-23 — low bit of an integer hash; with both
+ * multipliers and the addend odd it equals bit0(head) ^ bit0(idx) ^ 1. */
+float orc_sign_flip(int idx, int head) {
+    uint32_t x = ((uint32_t)head * 2654435761u) ^
+                 ((uint32_t)idx * 1103515245u + 12345u);
+    return (x & 1u) ? 1.0f : -1.0f;
+}
+
+/* tq_turbo_prod_kernels.cu:26-37, tq_turbo_mse_kernels.cu:24-29 */
+static const float kCb3[8] = {-2.1513f,  -1.34326f, -0.755526f, -0.244919f,
+                              0.244919f, 0.755526f, 1.34326f,   2.1513f};
+static const float kCb4[16] = {-2.7326f, -2.0690f, -1.6180f, -1.2562f,
+                               -0.9423f, -0.6568f, -0.3880f, -0.1284f,
+                               0.1284f,  0.3880f,  0.6568f,  0.9423f,
+                               1.2562f,  1.6180f,  2.0690f,  2.7326f};
+const float* orc_cb3(void) { return kCb3; }
+const float* orc_cb4(void) { return kCb4; }
+
+/* tq_turbo_prod_kernels.cu:39-59 — first index attaining the minimum. */
+static int nearest(const float* cb, int n, float x) {
+    int best = 0;
+    float bd = fabsf(x - cb[0]);
+    for (int i = 1; i < n; ++i) {
+        float d = fabsf(x - cb[i]);
+        if (d < bd) {
+            bd = d;
+            best = i;
+        }
+    }
+    return best;
+}
+int orc_nearest_k3(float x) { return nearest(kCb3, 8, x); }
+int orc_nearest_v4(float x) { return nearest(kCb4, 16, x); }
+
+static float clampf(float x, float lo, float hi) {
+    return x < lo ? lo : (x > hi ? hi : x);
+}
+
+/* tq_turbo_prod_kernels.cu:89-105 — stages len = 1,2,..,d/2; butterfly
+ * `t` of a stage touches (i0, i0+len) with i0 = (t/len)*2len + t%len. */
+void orc_fwht128(float* x, int d) {
+    for (int len = 1; len < d; len <<= 1) {
+        for (int t = 0; t < d / 2; ++t) {
+            int i0 = (t / len) * (len << 1) + (t % len);
+            int i1 = i0 + len;
+            float a = x[i0], b = x[i1];
+            x[i0] = a + b;
+            x[i1] = a - b;
+        }
+    }
+}
+
+/* tq_turbo_prod_kernels.cu:195-198 — x[i] += x[i+stride], stride = n/2..1. */
+static float tree_sum(float* r, int n) {
+    for (int s = n >> 1; s > 0; s >>= 1)
+        for (int i = 0; i < s; ++i) r[i] += r[i + s];
+    return r[0];
+}
+
+/* tq_shared_device.cuh:61-64 — even index = low nibble. */
+static inline int nib_get(const uint8_t* p, int i) {
+    uint8_t b = p[i >> 1];
+    return (i & 1) ? (b >> 4) & 0xF : b & 0xF;
+}
+
+/* ------------------------------------------------------------------------- */
+/* config and layouts                                                        */
+/* ------------------------------------------------------------------------- */
+
+/* tq_config.h:4-13 */
+void orc_default_config(OrcConfig* c) {
+    c->block_size = 16;
+    c->num_kv_heads = 8;
+    c->head_dim = 128;
+    c->nbits = 4;
+    c->group_size = 128;
+    c->page_alignment = 256;
+    c->scale_type = 0;
+    c->quant_mode = 0;
+}
+
+static size_t up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+/* src/tq_turbo_prod.cpp:7-39 */
+void orc_prod_layout(const OrcConfig* c, OrcProdLayout* l) {
+    memset(l, 0, sizeof *l);
+    l->k4_bytes_per_token_head = (c->head_dim + 1) / 2;
+    l->v4_bytes_per_token_head = (c->head_dim * 4 + 7) / 8;
+    l->scale_bytes_per_token_head = 2;
+    size_t th = (size_t)c->block_size * c->num_kv_heads;
+    size_t cur = 0;
+    l->k4_codes_offset = cur;
+    cur += th * l->k4_bytes_per_token_head;
+    cur = up(cur, 2);
+    l->k_residual_scales_offset = cur;
+    cur += th * 2;
+    l->k_scales_offset = cur;
+    cur += th * 2;
+    l->v4_codes_offset = cur;
+    cur += th * l->v4_bytes_per_token_head;
+    cur = up(cur, 2);
+    l->v_scales_offset = cur;
+    cur += th * 2;
+    l->page_size_bytes = up(cur, 2);
+}
+
+/* src/tq_turbo_mse_layout.cpp:7-28 */
+void orc_mse_layout(const OrcConfig* c, OrcMseLayout* l) {
+    l->code_bytes_per_token_head = (size_t)(c->head_dim * c->nbits + 7) / 8;
+    l->norm_bytes_per_token_head = 2;
+    size_t th = (size_t)c->block_size * c->num_kv_heads;
+    size_t a = (size_t)c->page_alignment;
+    l->k_codes_offset = 0;
+    l->v_codes_offset = up(th * l->code_bytes_per_token_head, a);
+    l->k_norms_offset =
+        up(l->v_codes_offset + th * l->code_bytes_per_token_head, a);
+    l->v_norms_offset = up(l->k_norms_offset + th * 2, a);
+    l->page_size_bytes = up(l->v_norms_offset + th * 2, a);
+}
+
+/* src/tq_block_table.cpp:24-39 */
+void orc_build_slot_map(const int32_t* blocks, int num_tokens_before,
+                        int append_tokens, int block_size, int32_t* slots) {
+    for (int i = 0; i < append_tokens; ++i) {
+        int t = num_tokens_before + i;
+        slots[i] = blocks[t / block_size] * block_size + t % block_size;
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* turbo_prod                                                                */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+    uint8_t* k4;
+    uint16_t* kres;
+    uint16_t* ks;
+    uint8_t* v4;
+    uint16_t* vs;
+} ProdCell;
+
+/* tq_turbo_prod_kernels.cu:136-162 and tq_turbo_prod.cuh:37-43 */
+static ProdCell prod_cell(const uint8_t* pool, const OrcProdLayout* l,
+                          const OrcConfig* c, int slot, int head) {
+    int blk = slot / c->block_size, tib = slot % c->block_size;
+    uint8_t* page = (uint8_t*)pool + (size_t)blk * l->page_size_bytes;
+    size_t th = (size_t)tib * c->num_kv_heads + head;
+    ProdCell p;
+    p.k4 = page + l->k4_codes_offset + th * l->k4_bytes_per_token_head;
+    p.kres = (uint16_t*)(page + l->k_residual_scales_offset +
+                         th * l->scale_bytes_per_token_head);
+    p.ks = (uint16_t*)(page + l->k_scales_offset +
+                       th * l->scale_bytes_per_token_head);
+    p.v4 = page + l->v4_codes_offset + th * l->v4_bytes_per_token_head;
+    p.vs = (uint16_t*)(page + l->v_scales_offset +
+                       th * l->scale_bytes_per_token_head);
+    return p;
+}
+
+/* q' = FWHT(s .* q) * rsqrt(D): tq_turbo_prod_kernels.cu:372-379 */
+static void rotate_fwd(const uint16_t* src, int head, int d, float* x) {
+    for (int i = 0; i < d; ++i) x[i] = h2f(src[i]) * orc_sign_flip(i, head);
+    orc_fwht128(x, d);
+    float c = inv_sqrt_d(d);
+    for (int i = 0; i < d; ++i) x[i] *= c;
+}
+
+/* tq_turbo_prod_kernels.cu:179-259 */
+void orc_prod_pack(const uint16_t* key, const uint16_t* value,
+                   const int32_t* slots, uint8_t* pool,
+                   const OrcProdLayout* lay, const OrcConfig* cfg, int n,
+                   float* dbg_kn, float* dbg_vn) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t) {
+        for (int h = 0; h < H; ++h) {
+            float sk[128], sv[128], red[128], e[128];
+            int kidx[128], kbit[128], vidx[128];
+            size_t base = ((size_t)t * H + h) * d;
+            ProdCell p = prod_cell(pool, lay, cfg, slots[t], h);
+            rotate_fwd(key + base, h, d, sk);
+            rotate_fwd(value + base, h, d, sv);
+
+            for (int i = 0; i < d; ++i) red[i] = sk[i] * sk[i];
+            float krms = sqrtf(tree_sum(red, d) / (float)d);
+            if (krms < 1e-8f) krms = 1e-8f;
+            *p.ks = f2h(krms);
+            for (int i = 0; i < d; ++i) red[i] = sv[i] * sv[i];
+            float vrms = sqrtf(tree_sum(red, d) / (float)d);
+            if (vrms < 1e-8f) vrms = 1e-8f;
+            *p.vs = f2h(vrms);
+
+            for (int i = 0; i < d; ++i) {
+                float kn = clampf(sk[i] / krms, -2.5f, 2.5f);
+                float vn = clampf(sv[i] / vrms, -2.75f, 2.75f);
+                kidx[i] = orc_nearest_k3(kn);
+                e[i] = kn - kCb3[kidx[i]];
+                kbit[i] = e[i] >= 0.0f ? 1 : 0;
+                vidx[i] = orc_nearest_v4(vn);
+                if (dbg_kn) dbg_kn[base + i] = kn;
+                if (dbg_vn) dbg_vn[base + i] = vn;
+            }
+            for (int i = 0; i < d; ++i) red[i] = e[i] * e[i];
+            float rms_e = sqrtf(tree_sum(red, d) / (float)d);
+            if (rms_e < 1e-8f) rms_e = 1e-8f;
+            *p.kres = f2h(rms_e);
+
+            for (int j = 0; j < d / 2; ++j) {
+                int i0 = 2 * j, i1 = i0 + 1;
+                p.k4[j] = (uint8_t)(((kbit[i0] << 3) | kidx[i0]) |
+                                    (((kbit[i1] << 3) | kidx[i1]) << 4));
+                p.v4[j] = (uint8_t)((vidx[i1] << 4) | vidx[i0]);
+            }
+        }
+    }
+}
+
+/* tq_turbo_prod_kernels.cu:315-340 */
+static void prod_decode_rot(const ProdCell* p, int d, float* k, float* v) {
+    float ks = h2f(*p->ks), re = h2f(*p->kres), vs = h2f(*p->vs);
+    for (int i = 0; i < d; ++i) {
+        int nb = nib_get(p->k4, i);
+        float sgn = (nb >> 3) ? 1.0f : -1.0f;
+        /* cb + re*sgn: re*sgn is exact, so a fused form rounds identically */
+        float kval = kCb3[nb & 7] + re * sgn;
+        k[i] = kval * ks;
+        v[i] = kCb4[nib_get(p->v4, i)] * vs;
+    }
+}
+
+static void rotate_inv_store(float* x, int head, int d, uint16_t* dst) {
+    orc_fwht128(x, d);
+    float c = inv_sqrt_d(d);
+    for (int i = 0; i < d; ++i)
+        dst[i] = f2h(x[i] * c * orc_sign_flip(i, head));
+}
+
+void orc_prod_dequant(const uint8_t* pool, const int32_t* slots,
+                      uint16_t* out_key, uint16_t* out_value,
+                      const OrcProdLayout* lay, const OrcConfig* cfg, int n) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t)
+        for (int h = 0; h < H; ++h) {
+            float k[128], v[128];
+            ProdCell p = prod_cell(pool, lay, cfg, slots[t], h);
+            prod_decode_rot(&p, d, k, v);
+            size_t base = ((size_t)t * H + h) * d;
+            rotate_inv_store(k, h, d, out_key + base);
+            rotate_inv_store(v, h, d, out_value + base);
+        }
+}
+
+/* tq_turbo_prod_kernels.cu:400-426 — two tree reductions per token. */
+static float prod_logit(const float* qrot, const ProdCell* p, int d) {
+    float red[128];
+    float ks = h2f(*p->ks), re = h2f(*p->kres);
+    float res_ks = ks * re;
+    for (int i = 0; i < d; ++i)
+        red[i] = qrot[i] * kCb3[nib_get(p->k4, i) & 7] * ks;
+    float base = tree_sum(red, d);
+    for (int i = 0; i < d; ++i)
+        red[i] = qrot[i] * ((nib_get(p->k4, i) >> 3) ? 1.0f : -1.0f);
+    float corr = tree_sum(red, d);
+    /* nvcc fuses corr*res_ks + base */
+    return fmaf(corr, res_ks, base) * inv_sqrt_d(d);
+}
+
+void orc_prod_logits(const uint16_t* query, const uint8_t* pool,
+                     const int32_t* slots, float* logits,
+                     const OrcProdLayout* lay, const OrcConfig* cfg, int nq,
+                     int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            float qrot[128];
+            rotate_fwd(query + ((size_t)qi * H + h) * d, h, d, qrot);
+            for (int t = 0; t < nkv; ++t) {
+                ProdCell p = prod_cell(pool, lay, cfg, slots[t], h);
+                logits[((size_t)qi * H + h) * nkv + t] =
+                    prod_logit(qrot, &p, d);
+            }
+        }
+}
+
+/* tq_turbo_prod_kernels.cu:472-570 — token-serial online softmax.  Writes
+ * the rotated-domain accumulator acc[0..d), then m and l, to `state`. */
+static void prod_attn_state(const uint16_t* q, const uint8_t* pool,
+                            const int32_t* slots, const OrcProdLayout* lay,
+                            const OrcConfig* cfg, int h, int nkv,
+                            float* state) {
+    const int d = cfg->head_dim;
+    float qrot[128], acc[128];
+    rotate_fwd(q, h, d, qrot);
+    for (int i = 0; i < d; ++i) acc[i] = 0.0f;
+    float m = -1e30f, l = 0.0f;
+    for (int t = 0; t < nkv; ++t) {
+        ProdCell p = prod_cell(pool, lay, cfg, slots[t], h);
+        float logit = prod_logit(qrot, &p, d);
+        float m_new = fmaxf(m, logit);
+        float a = expf(m - m_new), b = expf(logit - m_new);
+        l = fmaf(l, a, b);
+        m = m_new;
+        float vs = h2f(*p.vs);
+        for (int i = 0; i < d; ++i) {
+            float vval = kCb4[nib_get(p.v4, i)] * vs;
+            acc[i] = fmaf(b, vval, acc[i] * a);
+        }
+    }
+    memcpy(state, acc, sizeof(float) * d);
+    state[d] = m;
+    state[d + 1] = l;
+}
+
+static void attn_finish(float* state, int h, int d, uint16_t* out) {
+    float inv_l = state[d + 1] > 0.0f ? 1.0f / state[d + 1] : 1.0f;
+    for (int i = 0; i < d; ++i) state[i] *= inv_l;
+    rotate_inv_store(state, h, d, out);
+}
+
+void orc_prod_attn_f32(const uint16_t* query, const uint8_t* pool,
+                       const int32_t* slots, float* out_f32,
+                       const OrcProdLayout* lay, const OrcConfig* cfg, int nq,
+                       int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            size_t r = (size_t)qi * H + h;
+            prod_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv,
+                            out_f32 + r * (d + 2));
+        }
+}
+
+void orc_prod_attn(const uint16_t* query, const uint8_t* pool,
+                   const int32_t* slots, uint16_t* out,
+                   const OrcProdLayout* lay, const OrcConfig* cfg, int nq,
+                   int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            float st[130];
+            size_t r = (size_t)qi * H + h;
+            prod_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv, st);
+            attn_finish(st, h, d, out + r * d);
+        }
+}
+
+/* ------------------------------------------------------------------------- */
+/* turbo_mse                                                                 */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+    uint8_t *kc, *vc;
+    uint16_t *kn, *vn;
+} MseCell;
+
+/* tq_turbo_mse_layout.h:25-41, tq_turbo_mse_kernels.cu:206-221 */
+static MseCell mse_cell(const uint8_t* pool, const OrcMseLayout* l,
+                        const OrcConfig* c, int slot, int head) {
+    int blk = slot / c->block_size, tib = slot % c->block_size;
+    uint8_t* page = (uint8_t*)pool + (size_t)blk * l->page_size_bytes;
+    size_t th = (size_t)(tib * c->num_kv_heads + head);
+    MseCell m;
+    m.kc = page + l->k_codes_offset + th * l->code_bytes_per_token_head;
+    m.vc = page + l->v_codes_offset + th * l->code_bytes_per_token_head;
+    m.kn = (uint16_t*)(page + l->k_norms_offset +
+                       th * l->norm_bytes_per_token_head);
+    m.vn = (uint16_t*)(page + l->v_norms_offset +
+                       th * l->norm_bytes_per_token_head);
+    return m;
+}
+
+/* tq_turbo_mse_kernels.cu:65-136 — 64 workers, one element pair each; the
+ * RMS tree starts from the 64 pair sums. */
+static void mse_quantize(const uint16_t* src, uint8_t* codes, uint16_t* scale,
+                         int d, int head, float* dbg) {
+    float x[128], red[64];
+    rotate_fwd(src, head, d, x);
+    for (int j = 0; j < d / 2; ++j) {
+        float a = x[2 * j], b = x[2 * j + 1];
+        if (g_mse_pair_fma == 1)
+            red[j] = fmaf(a, a, b * b);
+        else if (g_mse_pair_fma == 2)
+            red[j] = fmaf(b, b, a * a);
+        else
+            red[j] = a * a + b * b;
+    }
+    float rms = sqrtf(tree_sum(red, d / 2) / (float)d);
+    if (rms < 1e-8f) rms = 1e-8f;
+    *scale = f2h(rms);
+    for (int j = 0; j < d / 2; ++j) {
+        float a = clampf(x[2 * j] / rms, -2.75f, 2.75f);
+        float b = clampf(x[2 * j + 1] / rms, -2.75f, 2.75f);
+        if (dbg) {
+            dbg[2 * j] = a;
+            dbg[2 * j + 1] = b;
+        }
+        codes[j] = (uint8_t)((orc_nearest_v4(b) << 4) | orc_nearest_v4(a));
+    }
+}
+
+void orc_mse_pack(const uint16_t* key, const uint16_t* value,
+                  const int32_t* slots, uint8_t* pool, const OrcMseLayout* lay,
+                  const OrcConfig* cfg, int n, float* dbg_kn, float* dbg_vn) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t)
+        for (int h = 0; h < H; ++h) {
+            size_t base = ((size_t)t * H + h) * d;
+            MseCell c = mse_cell(pool, lay, cfg, slots[t], h);
+            mse_quantize(key + base, c.kc, c.kn, d, h,
+                         dbg_kn ? dbg_kn + base : NULL);
+            mse_quantize(value + base, c.vc, c.vn, d, h,
+                         dbg_vn ? dbg_vn + base : NULL);
+        }
+}
+
+/* tq_turbo_mse_kernels.cu:138-184 */
+static void mse_decode_rot(const uint8_t* codes, const uint16_t* scale, int d,
+                           float* x) {
+    float rms = h2f(*scale);
+    for (int i = 0; i < d; ++i) x[i] = kCb4[nib_get(codes, i)] * rms;
+}
+
+void orc_mse_dequant(const uint8_t* pool, const int32_t* slots,
+                     uint16_t* out_key, uint16_t* out_value,
+                     const OrcMseLayout* lay, const OrcConfig* cfg, int n) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t)
+        for (int h = 0; h < H; ++h) {
+            float x[128];
+            size_t base = ((size_t)t * H + h) * d;
+            MseCell c = mse_cell(pool, lay, cfg, slots[t], h);
+            mse_decode_rot(c.kc, c.kn, d, x);
+            rotate_inv_store(x, h, d, out_key + base);
+            mse_decode_rot(c.vc, c.vn, d, x);
+            rotate_inv_store(x, h, d, out_value + base);
+        }
+}
+
+/* tq_turbo_mse_kernels.cu:335-416 */
+static void mse_attn_state(const uint16_t* q, const uint8_t* pool,
+                           const int32_t* slots, const OrcMseLayout* lay,
+                           const OrcConfig* cfg, int h, int nkv,
+                           float* state) {
+    const int d = cfg->head_dim;
+    float qrot[128], acc[128], red[128];
+    rotate_fwd(q, h, d, qrot);
+    float c = inv_sqrt_d(d);
+    for (int i = 0; i < d; ++i) acc[i] = 0.0f;
+    float m = -1e30f, l = 0.0f;
+    for (int t = 0; t < nkv; ++t) {
+        MseCell cell = mse_cell(pool, lay, cfg, slots[t], h);
+        float ks = h2f(*cell.kn), vs = h2f(*cell.vn);
+        for (int i = 0; i < d; ++i) {
+            float kval = kCb4[nib_get(cell.kc, i)] * ks;
+            red[i] = qrot[i] * kval;
+        }
+        float logit = tree_sum(red, d) * c;
+        float m_new = fmaxf(m, logit);
+        float a = expf(m - m_new), b = expf(logit - m_new);
+        l = fmaf(l, a, b);
+        m = m_new;
+        for (int i = 0; i < d; ++i) {
+            float vval = kCb4[nib_get(cell.vc, i)] * vs;
+            acc[i] = fmaf(b, vval, acc[i] * a);
+        }
+    }
+    memcpy(state, acc, sizeof(float) * d);
+    state[d] = m;
+    state[d + 1] = l;
+}
+
+void orc_mse_attn_f32(const uint16_t* query, const uint8_t* pool,
+                      const int32_t* slots, float* out_f32,
+                      const OrcMseLayout* lay, const OrcConfig* cfg, int nq,
+                      int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            size_t r = (size_t)qi * H + h;
+            mse_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv,
+                           out_f32 + r * (d + 2));
+        }
+}
+
+void orc_mse_attn(const uint16_t* query, const uint8_t* pool,
+                  const int32_t* slots, uint16_t* out, const OrcMseLayout* lay,
+                  const OrcConfig* cfg, int nq, int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            float st[130];
+            size_t r = (size_t)qi * H + h;
+            mse_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv, st);
+            attn_finish(st, h, d, out + r * d);
+        }
+}
+
+/* ------------------------------------------------------------------------- */
+/* dense reference attention and the chunk-prefill extension                 */
+/* ------------------------------------------------------------------------- */
+
+/* src/tq_attention_ref.cpp:10-56 */
+int orc_attention_ref_single_head(const uint16_t* q, const uint16_t* k_all,
+                                  const uint16_t* v_all, int n, int d,
+                                  float* out) {
+    if (n <= 0 || d <= 0) return -1;
+    float* sc = (float*)malloc(sizeof(float) * (size_t)n);
+    const float c = 1.0f / sqrtf((float)d);
+    float mx = -INFINITY;
+    for (int t = 0; t < n; ++t) {
+        float acc = 0.f;
+        for (int i = 0; i < d; ++i)
+            acc += h2f(q[i]) * h2f(k_all[(size_t)t * d + i]);
+        sc[t] = acc * c;
+        if (sc[t] > mx) mx = sc[t];
+    }
+    float den = 0.f;
+    for (int t = 0; t < n; ++t) {
+        sc[t] = expf(sc[t] - mx);
+        den += sc[t];
+    }
+    for (int t = 0; t < n; ++t) sc[t] /= den;
+    for (int i = 0; i < d; ++i) out[i] = 0.f;
+    for (int t = 0; t < n; ++t)
+        for (int i = 0; i < d; ++i)
+            out[i] += sc[t] * h2f(v_all[(size_t)t * d + i]);
+    free(sc);
+    return 0;
+}
+
+/* Prefix: restated turbo_mse decode in the rotated domain (fp32, the values
+ * the dequant kernel forms before its inverse rotation).  Chunk: fp16 K/V,
+ * rotated with the same transform so one dot product serves both; query row
+ * i sees the whole prefix and chunk rows 0..i.  Two-pass softmax in fp32. */
+void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
+                     const int32_t* slots, int nkv, const uint16_t* chunk_k,
+                     const uint16_t* chunk_v, int nq, int hq, float* out,
+                     const OrcMseLayout* lay, const OrcConfig* cfg) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads, grp = hq / H;
+    const float c = inv_sqrt_d(d);
+    for (int h = 0; h < H; ++h) {
+        int ntot = nkv + (chunk_k ? nq : 0);
+        float* kr = (float*)malloc(sizeof(float) * (size_t)ntot * d);
+        float* vr = (float*)malloc(sizeof(float) * (size_t)ntot * d);
+        for (int t = 0; t < nkv; ++t) {
+            MseCell cell = mse_cell(pool, lay, cfg, slots[t], h);
+            mse_decode_rot(cell.kc, cell.kn, d, kr + (size_t)t * d);
+            mse_decode_rot(cell.vc, cell.vn, d, vr + (size_t)t * d);
+        }
+        if (chunk_k)
+            for (int t = 0; t < nq; ++t) {
+                rotate_fwd(chunk_k + ((size_t)t * H + h) * d, h, d,
+                           kr + (size_t)(nkv + t) * d);
+                rotate_fwd(chunk_v + ((size_t)t * H + h) * d, h, d,
+                           vr + (size_t)(nkv + t) * d);
+            }
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+        for (int i = 0; i < nq; ++i)
+            for (int g = 0; g < grp; ++g) {
+                int j = h * grp + g;
+                float qrot[128], acc[128];
+                rotate_fwd(query + ((size_t)i * hq + j) * d, h, d, qrot);
+                int vis = nkv + (chunk_k ? i + 1 : 0);
+                float* sc = (float*)malloc(sizeof(float) * (size_t)(vis + 1));
+                float mx = -INFINITY;
+                for (int t = 0; t < vis; ++t) {
+                    float s = 0.f;
+                    for (int e = 0; e < d; ++e)
+                        s += qrot[e] * kr[(size_t)t * d + e];
+                    sc[t] = s * c;
+                    if (sc[t] > mx) mx = sc[t];
+                }
+                float den = 0.f;
+                for (int t = 0; t < vis; ++t) {
+                    sc[t] = expf(sc[t] - mx);
+                    den += sc[t];
+                }
+                for (int e = 0; e < d; ++e) acc[e] = 0.f;
+                for (int t = 0; t < vis; ++t)
+                    for (int e = 0; e < d; ++e)
+                        acc[e] += sc[t] * vr[(size_t)t * d + e];
+                float inv = vis > 0 && den > 0.f ? 1.0f / den : 1.0f;
+                for (int e = 0; e < d; ++e) acc[e] *= inv;
+                orc_fwht128(acc, d);
+                for (int e = 0; e < d; ++e)
+                    out[((size_t)i * hq + j) * d + e] =
+                        acc[e] * c * orc_sign_flip(e, h);
+                free(sc);
+            }
+        free(kr);
+        free(vr);
+    }
+}

@@ -1,0 +1,680 @@
+// Fused decode attention over compressed pages (turbo_prod and turbo_mse), sm_100a.
+//
+// Replaces turbo_prod_fused_attention_logits_kernel / turbo_prod_fused_attn_online_kernel
+// (src/cuda/tq_turbo_prod_kernels.cu:346-571) and turbo_mse_fused_attn_online_kernel
+// (src/cuda/tq_turbo_mse_kernels.cu:302-417).  The reference walks the KV tokens
+// serially inside one 128-thread CTA per (query, kv-head); here
+//   * the KV range of every sequence is cut into splits (one CTA each) and, inside
+//     a CTA, into per-warp streams of 16-token blocks; (acc, m, l) partials are
+//     merged by log-sum-exp (second kernel, also the multi-GPU reducer);
+//   * a warp owns one kv-head of a block: the 16x128 code tile is the A operand
+//     of mma.sync m16n8k16 (rows = tokens), the up-to-8 query heads that share the
+//     kv-head are the 8 columns, so GQA costs no extra code traffic or unpack work;
+//   * 4-bit codes go nibble -> fp16 in registers with byte-permute lookups
+//     (8-entry signed table for the 3-bit K code, 8-entry magnitude table plus a
+//     sign XOR for the 4-bit codes); the 1-bit residual sign is a second MMA with
+//     +-1 operands, scaled per token column (ks*re) afterwards;
+//   * V^T is the A operand of the second product: unpacked rows are staged in a
+//     per-warp swizzled shared tile and read back with ldmatrix.trans.
+// Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
+// and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
+#include "tq_common.cuh"
+#include "tq_launch.h"
+
+namespace tq {
+namespace {
+
+constexpr int kMaxHeads = 8;          // kv heads per CTA
+constexpr int kWarpSmemBytes = 4608;  // V tile (4096) or merge record (36*32*4)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeParams {
+    const __half* query;
+    const uint8_t* pool;
+    const int32_t* slot_mapping;
+    const int32_t* block_tables;
+    const int32_t* seq_lens;
+    float* partials;  // [batch, splits, rows_per_seq, 130]
+    float* logits;
+    PageGeom geo;
+    int table_stride;
+    int head_dim;
+    int groups;        // query heads per kv head
+    int ref_layout;    // query row of (g, h): g*H+h if set, else h*G+g
+    int max_kv_tokens;
+    int kv_begin, kv_end;
+    int splits;
+    int streams;       // warps per kv head inside a CTA
+    int bs_shift;      // log2(block_size) or -1
+    int aligned16;     // every code row starts on a 16-byte boundary
+};
+
+// ---- small PTX wrappers ------------------------------------------------------
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
+    return (a & b) ^ c;  // one LOP3
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t fp16_bits(float v) {
+    return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(v)));
+}
+
+// Byte pools for the permute lookups: entry e of an 8-entry fp16 table is split
+// into its high byte (pool hi.x/hi.y) and low byte (pool lo.x/lo.y).
+struct BytePools {
+    uint32_t hi_a, hi_b, lo_a, lo_b;
+};
+__device__ __forceinline__ BytePools make_pools(const float (&t)[8]) {
+    BytePools p = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const uint32_t a = fp16_bits(t[e]), b = fp16_bits(t[e + 4]);
+        p.hi_a |= (a >> 8) << (8 * e);
+        p.lo_a |= (a & 0xFFu) << (8 * e);
+        p.hi_b |= (b >> 8) << (8 * e);
+        p.lo_b |= (b & 0xFFu) << (8 * e);
+    }
+    return p;
+}
+
+// Eight 3-bit selectors (one per nibble, bit 3 of every nibble clear) -> four
+// half2 registers holding the table values of nibble pairs (0,4) (1,5) (2,6) (3,7).
+__device__ __forceinline__ void lookup8(uint32_t sel, const BytePools& t, uint32_t (&out)[4]) {
+    const uint32_t y = prmt(sel, sel, 0x3120u);  // nibbles 0,1,4,5 | 2,3,6,7
+    const uint32_t yh = y >> 16;
+    const uint32_t h_lo = prmt(t.hi_a, t.hi_b, y), l_lo = prmt(t.lo_a, t.lo_b, y);
+    const uint32_t h_hi = prmt(t.hi_a, t.hi_b, yh), l_hi = prmt(t.lo_a, t.lo_b, yh);
+    out[0] = prmt(l_lo, h_lo, 0x6240u);
+    out[1] = prmt(l_lo, h_lo, 0x7351u);
+    out[2] = prmt(l_hi, h_hi, 0x6240u);
+    out[3] = prmt(l_hi, h_hi, 0x7351u);
+}
+
+// turbo_prod K word: 3-bit code -> signed level (nibble bit 3 masked off).
+__device__ __forceinline__ void unpack_k3(uint32_t w, const BytePools& t, uint32_t (&out)[4]) {
+    lookup8(w & 0x77777777u, t, out);
+}
+// Residual sign bits (bit 3 of every nibble) -> +-1.0 halves, same pairing.
+__device__ __forceinline__ void unpack_sign(uint32_t w, uint32_t (&out)[4]) {
+    out[0] = lop3_and_xor(w << 12, 0x80008000u, 0xBC00BC00u);
+    out[1] = lop3_and_xor(w << 8, 0x80008000u, 0xBC00BC00u);
+    out[2] = lop3_and_xor(w << 4, 0x80008000u, 0xBC00BC00u);
+    out[3] = lop3_and_xor(w, 0x80008000u, 0xBC00BC00u);
+}
+// 4-bit code n -> cb4[n]: magnitude index is n-8 for n >= 8 and 7-n below, the
+// sign bit is set when bit 3 of the nibble is clear.
+__device__ __forceinline__ void unpack_c4(uint32_t w, const BytePools& mag, uint32_t (&out)[4]) {
+    const uint32_t s = w & 0x88888888u;
+    const uint32_t t = s - (s >> 3);  // 7 in every nibble whose bit 3 is set
+    const uint32_t sel = (w ^ t ^ 0x77777777u) & 0x77777777u;  // one LOP3
+    lookup8(sel, mag, out);
+    const uint32_t sn = s ^ 0x88888888u;  // bit 3 set where the value is negative
+    out[0] = lop3_and_xor(sn << 12, 0x80008000u, out[0]);
+    out[1] = lop3_and_xor(sn << 8, 0x80008000u, out[1]);
+    out[2] = lop3_and_xor(sn << 4, 0x80008000u, out[2]);
+    out[3] = lop3_and_xor(sn, 0x80008000u, out[3]);
+}
+
+// Slot of token t of sequence b.
+__device__ __forceinline__ int token_slot(const DecodeParams& p, int b, int t) {
+    if (p.slot_mapping) return __ldg(p.slot_mapping + t);
+    const int bs = p.geo.block_size;
+    const int pg = p.bs_shift >= 0 ? (t >> p.bs_shift) : t / bs;
+    return __ldg(p.block_tables + static_cast<long long>(b) * p.table_stride + pg) * bs +
+           (t - pg * bs);
+}
+
+struct Cell {
+    const uint8_t* page;
+    unsigned int th;
+};
+__device__ __forceinline__ Cell token_cell(const DecodeParams& p, int slot, int h) {
+    const int bs = p.geo.block_size;
+    const int blk = p.bs_shift >= 0 ? (slot >> p.bs_shift) : slot / bs;
+    Cell c;
+    c.page = p.pool + static_cast<unsigned long long>(blk) * p.geo.page_size;
+    c.th = static_cast<unsigned int>((slot - blk * bs) * p.geo.num_kv_heads + h);
+    return c;
+}
+
+__device__ __forceinline__ uint4 ld16(const uint8_t* p, bool aligned) {
+    if (aligned) return __ldg(reinterpret_cast<const uint4*>(p));
+    uint32_t v[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i >> 2] |= static_cast<uint32_t>(p[i]) << (8 * (i & 3));
+    return make_uint4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ float ld_scale(const uint8_t* p) {
+    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(p))));
+}
+
+// Raw (still packed) data of one 16-token block for one warp.
+struct BlockRaw {
+    uint4 k0, k1;        // K codes of token rows g and g+8, 16-byte chunk tig
+    uint4 v0, v1;        // V codes of token row rv, bytes [32*hb, 32*hb+32)
+    float ks0, ks1, re0, re1, vs0, vs1;
+};
+
+template <bool PROD>
+__device__ __forceinline__ void load_block(const DecodeParams& p, int b, int h, int tb, int t_end,
+                                           int lane, bool aligned, BlockRaw& r) {
+    const int g = lane >> 2, tig = lane & 3;
+    const int rv = (lane & 7) + 8 * (lane >> 4), hb = (lane >> 3) & 1;
+    const int last = t_end - 1;
+    const int t0 = min(tb + g, last), t1 = min(tb + g + 8, last), tv = min(tb + rv, last);
+    const Cell c0 = token_cell(p, token_slot(p, b, t0), h);
+    const Cell c1 = token_cell(p, token_slot(p, b, t1), h);
+    const Cell cv = token_cell(p, token_slot(p, b, tv), h);
+    r.k0 = ld16(c0.page + p.geo.k_codes + c0.th * 64 + 16 * tig, aligned);
+    r.k1 = ld16(c1.page + p.geo.k_codes + c1.th * 64 + 16 * tig, aligned);
+    r.v0 = ld16(cv.page + p.geo.v_codes + cv.th * 64 + 32 * hb, aligned);
+    r.v1 = ld16(cv.page + p.geo.v_codes + cv.th * 64 + 32 * hb + 16, aligned);
+    r.ks0 = ld_scale(c0.page + p.geo.k_scales + c0.th * 2);
+    r.ks1 = ld_scale(c1.page + p.geo.k_scales + c1.th * 2);
+    r.vs0 = ld_scale(c0.page + p.geo.v_scales + c0.th * 2);
+    r.vs1 = ld_scale(c1.page + p.geo.v_scales + c1.th * 2);
+    if (PROD) {
+        r.re0 = ld_scale(c0.page + p.geo.k_res + c0.th * 2);
+        r.re1 = ld_scale(c1.page + p.geo.k_res + c1.th * 2);
+    } else {
+        r.re0 = r.re1 = 0.0f;
+    }
+}
+
+// MODE 0: attention partials, MODE 1: logits only (turbo_prod).
+template <bool PROD, int MODE>
+__global__ void __launch_bounds__(256)
+decode_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int H = p.geo.num_kv_heads;
+    const int h = warp % H, stream = warp / H;
+    const int g = lane >> 2, tig = lane & 3;
+    const int split = blockIdx.x, b = blockIdx.y, qg = blockIdx.z;
+    const int G = p.groups;
+    const int gq0 = qg * 8;                // first query of this pass within the group
+    const int nq = min(8, G - gq0);        // live columns
+    const int rows_per_seq = G * H;
+    const bool aligned = p.aligned16 != 0;
+
+    uint8_t* warp_smem = smem_raw + warp * kWarpSmemBytes;
+    __half* qsm = reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * kWarpSmemBytes);
+
+    // ---- rotate the queries of this pass: q' = FWHT(s .* q) * rsqrt(D) ------------
+    // one warp per (kv head, column); lane holds 4 consecutive elements.
+    const float c = inv_sqrt_dim(p.head_dim);
+    const float qscale = (MODE == 0) ? c * c * kLog2e : c * c;
+    for (int col = stream; col < 8; col += p.streams) {
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (col < nq) {
+            const int gq = gq0 + col;
+            const long long qrow = static_cast<long long>(b) * rows_per_seq +
+                                   (p.ref_layout ? gq * H + h : h * G + gq);
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.query + qrow * kHeadDim) + lane);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            // even-head sign pattern (+,-,+,-); odd heads negate the result
+            float a0 = f0.x - f0.y, a1 = f0.x + f0.y, a2 = f1.x - f1.y, a3 = f1.x + f1.y;
+            x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float o = __shfl_xor_sync(0xffffffffu, x[e], m);
+                    x[e] = (lane & m) ? o - x[e] : x[e] + o;
+                }
+            }
+            const float sc = (h & 1) ? -qscale : qscale;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] *= sc;
+        }
+        __half2* dst = reinterpret_cast<__half2*>(qsm + (h * 8 + col) * kHeadDim + 4 * lane);
+        dst[0] = __floats2half2_rn(x[0], x[1]);
+        dst[1] = __floats2half2_rn(x[2], x[3]);
+    }
+    __syncthreads();
+
+    // B fragments: column g, dims 32*tig + 8*wi + {2hf, 2hf+4 | 2hf+1, 2hf+5}
+    uint32_t qf[8][2];
+    {
+        const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const int base = 8 * (s >> 1) + 2 * (s & 1);
+            const __half2 b01 = __halves2half2(qrow[base], qrow[base + 4]);
+            const __half2 b23 = __halves2half2(qrow[base + 1], qrow[base + 5]);
+            qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
+            qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
+        }
+    }
+
+    // ---- lookup tables ---------------------------------------------------------
+    const float t3[8] = {-TQ_C3_3, -TQ_C3_2, -TQ_C3_1, -TQ_C3_0, TQ_C3_0, TQ_C3_1, TQ_C3_2, TQ_C3_3};
+    const float t4[8] = {TQ_C4_0, TQ_C4_1, TQ_C4_2, TQ_C4_3, TQ_C4_4, TQ_C4_5, TQ_C4_6, TQ_C4_7};
+    const BytePools pool3 = make_pools(t3);
+    const BytePools mag4 = make_pools(t4);
+
+    // ---- this CTA's token range --------------------------------------------------
+    int n = p.seq_lens ? min(__ldg(p.seq_lens + b), p.max_kv_tokens) : p.max_kv_tokens;
+    const int t_begin = max(p.kv_begin, 0);
+    const int t_end = min(n, p.kv_end);
+    const int nblk = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
+    const int per = (nblk + p.splits - 1) / p.splits;
+    const int blk_lo = split * per, blk_hi = min(nblk, blk_lo + per);
+
+    float o[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float m_run[2] = {kInitMaxLogit, kInitMaxLogit}, l_run[2] = {0.0f, 0.0f};
+
+    const uint32_t tile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
+    const int rv = (lane & 7) + 8 * (lane >> 4), hb = (lane >> 3) & 1;
+
+    BlockRaw cur;
+    int blk = blk_lo + stream;
+    if (blk < blk_hi) load_block<PROD>(p, b, h, t_begin + 16 * blk, t_end, lane, aligned, cur);
+
+    for (; blk < blk_hi; blk += p.streams) {
+        const int tb = t_begin + 16 * blk;
+        BlockRaw nxt = cur;
+        if (blk + p.streams < blk_hi)
+            load_block<PROD>(p, b, h, t_begin + 16 * (blk + p.streams), t_end, lane, aligned, nxt);
+
+        // ---- S = K_hat Q'^T (rows = tokens g, g+8; cols = queries 2tig, 2tig+1) ----
+        float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
+        const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            uint32_t a[4], bq[4];
+            if (PROD) {
+                unpack_k3(kw0[wi], pool3, a);
+                unpack_k3(kw1[wi], pool3, bq);
+            } else {
+                unpack_c4(kw0[wi], mag4, a);
+                unpack_c4(kw1[wi], mag4, bq);
+            }
+            mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+            mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+            if (PROD) {
+                unpack_sign(kw0[wi], a);
+                unpack_sign(kw1[wi], bq);
+                mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+                mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+            }
+        }
+        const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
+        float lg[4];
+        lg[0] = s1[0] * cur.ks0;
+        lg[1] = s1[1] * cur.ks0;
+        lg[2] = s1[2] * cur.ks1;
+        lg[3] = s1[3] * cur.ks1;
+        if (PROD) {
+            const float r0 = cur.ks0 * cur.re0, r1 = cur.ks1 * cur.re1;
+            lg[0] = fmaf(s2[0], r0, lg[0]);
+            lg[1] = fmaf(s2[1], r0, lg[1]);
+            lg[2] = fmaf(s2[2], r1, lg[2]);
+            lg[3] = fmaf(s2[3], r1, lg[3]);
+        }
+
+        if (MODE == 1) {
+            // logits[(q*H + h)*N + t]  (tq_turbo_prod_kernels.cu:428-431)
+            const long long nkv = p.max_kv_tokens;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = 2 * tig + (e & 1);
+                const int t = tb + g + 8 * (e >> 1);
+                if (col < nq && t < t_end)
+                    p.logits[(static_cast<long long>(gq0 + col) * H + h) * nkv + t] = lg[e];
+            }
+            cur = nxt;
+            continue;
+        }
+
+        if (!ok0) lg[0] = lg[1] = -INFINITY;
+        if (!ok1) lg[2] = lg[3] = -INFINITY;
+
+        // ---- online softmax over the 16 tokens of the block ---------------------
+        float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
+#pragma unroll
+        for (int msk = 4; msk < 32; msk <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, msk));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
+        }
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+        const float p0 = ex2(lg[0] - mn0), p1 = ex2(lg[1] - mn1);
+        const float p2 = ex2(lg[2] - mn0), p3 = ex2(lg[3] - mn1);
+        l_run[0] = fmaf(l_run[0], al0, p0 + p2);
+        l_run[1] = fmaf(l_run[1], al1, p1 + p3);
+        if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                o[j][0] *= al0;
+                o[j][1] *= al1;
+                o[j][2] *= al0;
+                o[j][3] *= al1;
+            }
+        }
+        // P^T (k = token, n = query), V scale folded in
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * cur.vs0, p1 * cur.vs0));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * cur.vs1, p3 * cur.vs1));
+
+        // ---- V: unpack this lane's 64 codes into the swizzled tile ---------------
+        const uint32_t vw[8] = {cur.v0.x, cur.v0.y, cur.v0.z, cur.v0.w,
+                                cur.v1.x, cur.v1.y, cur.v1.z, cur.v1.w};
+#pragma unroll
+        for (int wi = 0; wi < 8; ++wi) {
+            uint32_t a[4];
+            unpack_c4(vw[wi], mag4, a);
+            const int unit = 8 * hb + wi;
+            *reinterpret_cast<uint4*>(warp_smem + rv * 256 + ((unit ^ (rv & 7)) << 4)) =
+                make_uint4(a[0], a[1], a[2], a[3]);
+        }
+        __syncwarp();
+        // ---- O^T += V^T P^T -------------------------------------------------------
+        {
+            const int mat = lane >> 3;
+            const int tok = (lane & 7) + 8 * (mat >> 1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int unit = 2 * j + (mat & 1);
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, tile_addr + tok * 256 + ((unit ^ (tok & 7)) << 4));
+                mma16816(o[j], a[0], a[1], a[2], a[3], pb0, pb1);
+            }
+        }
+        __syncwarp();
+        cur = nxt;
+    }
+
+    if (MODE == 1) return;
+
+    // ---- combine the streams of a kv head, then write the split partial --------
+#pragma unroll
+    for (int msk = 4; msk < 32; msk <<= 1) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], msk);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], msk);
+    }
+    __syncthreads();  // V tiles are dead; reuse the per-warp regions as records
+    float* rec = reinterpret_cast<float*>(warp_smem);
+    if (stream > 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) rec[(4 * j + e) * 32 + lane] = o[j][e];
+        rec[32 * 32 + lane] = m_run[0];
+        rec[33 * 32 + lane] = m_run[1];
+        rec[34 * 32 + lane] = l_run[0];
+        rec[35 * 32 + lane] = l_run[1];
+    }
+    __syncthreads();
+    if (stream > 0) return;
+    for (int s = 1; s < p.streams; ++s) {
+        const float* r = reinterpret_cast<const float*>(smem_raw + (s * H + h) * kWarpSmemBytes);
+        const float ms0 = r[32 * 32 + lane], ms1 = r[33 * 32 + lane];
+        const float mn0 = fmaxf(m_run[0], ms0), mn1 = fmaxf(m_run[1], ms1);
+        const float a0 = ex2(m_run[0] - mn0), a1 = ex2(m_run[1] - mn1);
+        const float b0 = ex2(ms0 - mn0), b1 = ex2(ms1 - mn1);
+        l_run[0] = l_run[0] * a0 + r[34 * 32 + lane] * b0;
+        l_run[1] = l_run[1] * a1 + r[35 * 32 + lane] * b1;
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j][0] = o[j][0] * a0 + r[(4 * j + 0) * 32 + lane] * b0;
+            o[j][1] = o[j][1] * a1 + r[(4 * j + 1) * 32 + lane] * b1;
+            o[j][2] = o[j][2] * a0 + r[(4 * j + 2) * 32 + lane] * b0;
+            o[j][3] = o[j][3] * a1 + r[(4 * j + 3) * 32 + lane] * b1;
+        }
+    }
+    // partial record: acc[128] (natural dim order), m in natural-log units, l
+    float* out = p.partials +
+                 (static_cast<long long>(b) * p.splits + split) * rows_per_seq * TQ_PARTIAL_STRIDE;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int col = 2 * tig + e;
+        if (col >= nq) continue;
+        float* row = out + static_cast<long long>(h * G + gq0 + col) * TQ_PARTIAL_STRIDE;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // accumulator rows g (unit 2j) and g+8 (unit 2j+1); position g of a
+            // unit is dim (g>>1) + 4*(g&1)
+            const int d = (g >> 1) + 4 * (g & 1);
+            row[16 * j + d] = o[j][e];
+            row[16 * j + 8 + d] = o[j][2 + e];
+        }
+        if (g == 0) {
+            row[128] = m_run[e] * kLn2;
+            row[129] = l_run[e];
+        }
+    }
+}
+
+// ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
+// One warp per (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
+__global__ void __launch_bounds__(128)
+merge_kernel(const float* __restrict__ partials, int num_parts, long long part_stride,
+             long long seq_stride, int rows_per_seq, __half* __restrict__ output,
+             float* __restrict__ partials_out, int rows, int num_q_heads, int num_kv_heads,
+             int ref_layout, int head_dim) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int seq = row / rows_per_seq, r = row - seq * rows_per_seq;
+    const float* base = partials + seq * seq_stride + static_cast<long long>(r) * TQ_PARTIAL_STRIDE;
+    float mmax = kInitMaxLogit;
+    for (int s = 0; s < num_parts; ++s) mmax = fmaxf(mmax, __ldg(base + s * part_stride + 128));
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+    for (int s = 0; s < num_parts; ++s) {
+        const float* ps = base + s * part_stride;
+        const float w = __expf(__ldg(ps + 128) - mmax);
+        l = fmaf(__ldg(ps + 129), w, l);
+        const float2 v0 = __ldg(reinterpret_cast<const float2*>(ps + 4 * lane));
+        const float2 v1 = __ldg(reinterpret_cast<const float2*>(ps + 4 * lane + 2));
+        acc[0] = fmaf(v0.x, w, acc[0]);
+        acc[1] = fmaf(v0.y, w, acc[1]);
+        acc[2] = fmaf(v1.x, w, acc[2]);
+        acc[3] = fmaf(v1.y, w, acc[3]);
+    }
+    if (partials_out) {
+        float* po = partials_out + static_cast<long long>(row) * TQ_PARTIAL_STRIDE;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) po[4 * lane + e] = acc[e];
+        if (lane == 0) {
+            po[128] = mmax;
+            po[129] = l;
+        }
+    }
+    if (!output) return;
+    const int G = num_q_heads / num_kv_heads;
+    const int h = r / G, gq = r - h * G;
+    const float inv_l = l > 0.0f ? 1.0f / l : 1.0f;  // tq_turbo_prod_kernels.cu:561-564
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = acc[e] * inv_l;
+    // inverse rotation: FWHT, * rsqrt(D), * s(i, h)   (tq_turbo_prod_kernels.cu:566-570)
+    float a0 = x[0] + x[1], a1 = x[0] - x[1], a2 = x[2] + x[3], a3 = x[2] - x[3];
+    x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float ov = __shfl_xor_sync(0xffffffffu, x[e], m);
+            x[e] = (lane & m) ? ov - x[e] : x[e] + ov;
+        }
+    }
+    const float c = inv_sqrt_dim(head_dim);
+    const float s0 = (h & 1) ? -c : c;  // element 4*lane+e: sign + iff (e+h) even
+    const long long orow = static_cast<long long>(seq) * rows_per_seq +
+                           (ref_layout ? gq * num_kv_heads + h : r);
+    __half2* dst = reinterpret_cast<__half2*>(output + orow * kHeadDim + 4 * lane);
+    dst[0] = __floats2half2_rn(x[0] * s0, x[1] * -s0);
+    dst[1] = __floats2half2_rn(x[2] * s0, x[3] * -s0);
+}
+
+// Dynamic shared memory above 48 KB has to be opted into once per device.
+void set_smem_attr_once() {
+    static bool done[64] = {};
+    int dev = 0;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64 || done[dev]) return;
+    const int bytes = 65536;
+    check_cuda(cudaFuncSetAttribute(decode_kernel<true, 0>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    done[dev] = true;
+}
+
+}  // namespace
+
+int decode_num_splits(int batch, int max_kv_tokens, int num_kv_heads, int block_size) {
+    (void)block_size;
+    if (batch <= 0 || max_kv_tokens <= 0) return 1;
+    const int streams = (num_kv_heads <= 8 && 8 % num_kv_heads == 0) ? 8 / num_kv_heads : 1;
+    const int slots = 2 * sm_count();
+    int splits = slots / batch;
+    const int nblk = (max_kv_tokens + 15) / 16;
+    const int cap = nblk / (streams * 4);
+    if (splits > cap) splits = cap;
+    if (splits < 1) splits = 1;
+    return splits;
+}
+
+size_t decode_workspace_bytes(int batch, int num_q_heads, int num_splits) {
+    return static_cast<size_t>(batch) * num_splits * num_q_heads * TQ_PARTIAL_STRIDE * sizeof(float);
+}
+
+void launch_merge(const float* partials, int num_parts, void* output, float* partials_out,
+                  int rows, int num_q_heads, int num_kv_heads, int ref_query_layout,
+                  int head_dim, cudaStream_t stream) {
+    if (rows <= 0) return;
+    // parts laid out [num_parts, rows, 130]
+    const long long part_stride = static_cast<long long>(rows) * TQ_PARTIAL_STRIDE;
+    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
+        partials, num_parts, part_stride, static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE,
+        num_q_heads, static_cast<__half*>(output), partials_out, rows, num_q_heads, num_kv_heads,
+        ref_query_layout, head_dim);
+    check_launch("merge_partials");
+}
+
+void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
+    const int H = a.geo.num_kv_heads;
+    if (H < 1 || H > kMaxHeads) throw std::runtime_error("decode: num_kv_heads must be 1..8");
+    if (a.num_q_heads % H != 0)
+        throw std::runtime_error("decode: num_q_heads must be a multiple of num_kv_heads");
+    if (a.batch <= 0 || a.num_q_heads <= 0) return;
+    const bool prod = a.scheme == TQ_SCHEME_TURBO_PROD;
+    const int G = a.num_q_heads / H;
+    const int qgroups = (G + 7) / 8;
+    const int streams = (8 % H == 0) ? 8 / H : 1;
+    const int warps = H * streams;
+    const size_t smem = static_cast<size_t>(warps) * kWarpSmemBytes + H * 8 * kHeadDim * sizeof(__half);
+
+    DecodeParams p{};
+    p.query = static_cast<const __half*>(a.query);
+    p.pool = a.pool;
+    p.slot_mapping = a.slot_mapping;
+    p.block_tables = a.block_tables;
+    p.seq_lens = a.seq_lens;
+    p.logits = a.logits_out;
+    p.geo = a.geo;
+    p.table_stride = a.table_stride;
+    p.head_dim = a.head_dim;
+    p.groups = G;
+    p.ref_layout = a.ref_query_layout;
+    p.max_kv_tokens = a.max_kv_tokens;
+    p.kv_begin = a.kv_begin;
+    p.kv_end = a.kv_end;
+    p.streams = streams;
+    {
+        const int bs = a.geo.block_size;
+        p.bs_shift = -1;
+        if (bs > 0 && (bs & (bs - 1)) == 0)
+            for (int sft = 0; sft < 31; ++sft)
+                if ((1 << sft) == bs) p.bs_shift = sft;
+        p.aligned16 = (reinterpret_cast<uintptr_t>(a.pool) & 15) == 0 && (a.geo.page_size & 15) == 0 &&
+                      (a.geo.k_codes & 15) == 0 && (a.geo.v_codes & 15) == 0;
+    }
+    set_smem_attr_once();
+
+    if (a.logits_out) {
+        if (!prod) throw std::runtime_error("logits: turbo_prod only");
+        int splits = decode_num_splits(a.batch * qgroups, a.max_kv_tokens, H, a.geo.block_size);
+        p.splits = splits;
+        decode_kernel<true, 1><<<dim3(splits, a.batch, qgroups), warps * 32, smem, stream>>>(p);
+        check_launch("turbo_prod fused_attention_logits");
+        return;
+    }
+
+    const int splits = decode_num_splits(a.batch * qgroups, a.max_kv_tokens, H, a.geo.block_size);
+    const size_t need = decode_workspace_bytes(a.batch, a.num_q_heads, splits);
+    float* ws = static_cast<float*>(a.workspace);
+    bool owned = false;
+    if (!ws) {
+        void* tmp = nullptr;
+        check_cuda(cudaMallocAsync(&tmp, need, stream), "cudaMallocAsync(decode workspace)");
+        ws = static_cast<float*>(tmp);
+        owned = true;
+    } else if (a.workspace_bytes < need) {
+        throw std::runtime_error("decode: workspace too small, need " + std::to_string(need) + " bytes");
+    }
+    p.partials = ws;
+    p.splits = splits;
+
+    const dim3 grid(splits, a.batch, qgroups);
+    if (prod)
+        decode_kernel<true, 0><<<grid, warps * 32, smem, stream>>>(p);
+    else
+        decode_kernel<false, 0><<<grid, warps * 32, smem, stream>>>(p);
+    check_launch(prod ? "turbo_prod decode" : "turbo_mse decode");
+
+    // merge the splits of every (sequence, query head) row
+    const int rows = a.batch * a.num_q_heads;
+    const long long part_stride = static_cast<long long>(a.num_q_heads) * TQ_PARTIAL_STRIDE;
+    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
+        ws, splits, part_stride, part_stride * splits, a.num_q_heads,
+        static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
+        a.ref_query_layout, a.head_dim);
+    check_launch("decode merge");
+    if (owned) check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(decode workspace)");
+}
+
+}  // namespace tq

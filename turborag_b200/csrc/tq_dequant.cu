@@ -1,0 +1,149 @@
+// Dequant kernels (compressed pages -> fp16 K/V) for sm_100a.
+//
+// Replaces turbo_prod_dequant_kv_kernel (src/cuda/tq_turbo_prod_kernels.cu:265-341)
+// and turbo_mse_dequant_kv_kernel (src/cuda/tq_turbo_mse_kernels.cu:239-287).  Same
+// register-resident transform as the pack kernels, run in the inverse
+// direction: 8 code bytes per lane are expanded through a bank-replicated
+// shared-memory codebook, stages 1..8 run in registers, one re-deal, stages
+// 16..64, then every lane stores eight half2 values; the eight lanes of a row
+// cover one 32-byte sector per store.  Output is bit-identical to the
+// reference.  An [H, N, D] output order is available for Hugging Face caches.
+#include "tq_common.cuh"
+#include "tq_launch.h"
+
+namespace tq {
+namespace {
+
+constexpr int kDqWarps = 8;
+
+__constant__ float kLevels3[8] = {-2.1513f,  -1.34326f, -0.755526f, -0.244919f,
+                                  0.244919f, 0.755526f, 1.34326f,   2.1513f};
+__constant__ float kLevels4[16] = {-2.7326f, -2.0690f, -1.6180f, -1.2562f, -0.9423f, -0.6568f,
+                                   -0.3880f, -0.1284f, 0.1284f,  0.3880f,  0.6568f,  0.9423f,
+                                   1.2562f,  1.6180f,  2.0690f,  2.7326f};
+
+__device__ __forceinline__ uint2 load_codes(const uint8_t* p, bool aligned8) {
+    if (aligned8) return __ldcs(reinterpret_cast<const uint2*>(p));
+    uint2 v = make_uint2(0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v.x |= static_cast<uint32_t>(p[i]) << (8 * i);
+        v.y |= static_cast<uint32_t>(p[4 + i]) << (8 * i);
+    }
+    return v;
+}
+
+// Inverse rotation of 16 rotated-domain values per lane and fp16 store.
+__device__ __forceinline__ void inverse_and_store(float (&x)[16], float* buf, int lane, float c,
+                                                  int h, __half* dst_row, bool valid) {
+    float y[16];
+    fwht_phase1(x);
+    redeal(x, y, buf, lane);
+    fwht_phase2(y);
+    const int l = lane & 7;
+    // element 2l+b+16j has sign +1 iff (b+h) is even
+    const float s0 = (h & 1) ? -1.0f : 1.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float a = __fmul_rn(__fmul_rn(y[2 * j], c), s0);
+        const float b = __fmul_rn(__fmul_rn(y[2 * j + 1], c), -s0);
+        if (valid)
+            *reinterpret_cast<__half2*>(dst_row + 2 * l + 16 * j) = __floats2half2_rn(a, b);
+    }
+}
+
+template <bool PROD>
+__global__ void __launch_bounds__(kDqWarps * 32)
+dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restrict__ slot_mapping,
+                  __half* __restrict__ out_key, __half* __restrict__ out_value, PageGeom geo,
+                  int head_dim, long long num_rows, long long num_tokens, int hnd,
+                  int pool_aligned8) {
+    __shared__ __align__(16) float xchg[kDqWarps][kXchgWarpFloats];
+    __shared__ float lut3[8 * 32];
+    __shared__ float lut4[16 * 32];
+    for (int i = threadIdx.x; i < 8 * 32; i += blockDim.x) lut3[i] = kLevels3[i >> 5];
+    for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) lut4[i] = kLevels4[i >> 5];
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rr = lane >> 3, l = lane & 7;
+    float* buf = xchg[warp];
+    const int H = geo.num_kv_heads;
+    const float c = inv_sqrt_dim(head_dim);
+    const long long groups = (num_rows + 3) >> 2;
+    const long long warps_total = static_cast<long long>(gridDim.x) * kDqWarps;
+    const bool al = pool_aligned8 != 0;
+
+    for (long long g = static_cast<long long>(blockIdx.x) * kDqWarps + warp; g < groups;
+         g += warps_total) {
+        const long long row_raw = g * 4 + rr;
+        const bool valid = row_raw < num_rows;
+        const long long row = valid ? row_raw : num_rows - 1;
+        const long long tok = row / H;
+        const int h = static_cast<int>(row - tok * H);
+        const int slot = __ldg(slot_mapping + tok);
+        const int blk = slot / geo.block_size;
+        const int tib = slot - blk * geo.block_size;
+        const uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
+        const unsigned int th = static_cast<unsigned int>(tib * H + h);
+
+        const uint2 kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
+        const uint2 vc = load_codes(page + geo.v_codes + th * 64 + 8 * l, al);
+        const float ks = __half2float(*reinterpret_cast<const __half*>(page + geo.k_scales + th * 2));
+        const float vs = __half2float(*reinterpret_cast<const __half*>(page + geo.v_scales + th * 2));
+        float re = 0.0f;
+        if (PROD) re = __half2float(*reinterpret_cast<const __half*>(page + geo.k_res + th * 2));
+
+        const long long out_row = hnd ? (static_cast<long long>(h) * num_tokens + tok) : row;
+        float x[16];
+
+        // K: rotated-domain values (tq_turbo_prod_kernels.cu:315-330 /
+        // tq_turbo_mse_kernels.cu:150-156)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const uint32_t w = e < 8 ? kc.x : kc.y;
+            const uint32_t nib = (w >> (4 * (e & 7))) & 0xFu;
+            if (PROD) {
+                const float lvl = lut3[(nib & 7u) * 32 + lane];
+                const float kval = __fadd_rn(lvl, (nib & 8u) ? re : -re);
+                x[e] = __fmul_rn(kval, ks);
+            } else {
+                x[e] = __fmul_rn(lut4[nib * 32 + lane], ks);
+            }
+        }
+        inverse_and_store(x, buf, lane, c, h, out_key + out_row * kHeadDim, valid);
+
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const uint32_t w = e < 8 ? vc.x : vc.y;
+            const uint32_t nib = (w >> (4 * (e & 7))) & 0xFu;
+            x[e] = __fmul_rn(lut4[nib * 32 + lane], vs);
+        }
+        inverse_and_store(x, buf, lane, c, h, out_value + out_row * kHeadDim, valid);
+    }
+}
+
+}  // namespace
+
+void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* out_key,
+                    void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,
+                    cudaStream_t stream) {
+    if (num_tokens <= 0) return;
+    const long long rows = static_cast<long long>(num_tokens) * geo.num_kv_heads;
+    const long long groups = (rows + 3) / 4;
+    long long blocks = (groups + kDqWarps - 1) / kDqWarps;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
+    if (prod)
+        dequant_kv_kernel<true><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
+            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
+            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+    else
+        dequant_kv_kernel<false><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
+            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
+            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+    check_launch(prod ? "turbo_prod dequant_kv" : "turbo_mse dequant_kv");
+}
+
+}  // namespace tq

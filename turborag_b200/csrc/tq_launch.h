@@ -1,0 +1,59 @@
+// Host-side launch helpers shared by the kernel translation units and the C API.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+// Throws std::runtime_error("<name>: <cuda error>") when the preceding launch
+// was rejected (same contract as TQ_CHECK_LAUNCH, include/tq_cuda_check.h:18-24).
+// With -DTQ_DEBUG_SYNC also synchronises the device and reports execution errors
+// (include/tq_cuda_check.h:26-37).
+void check_launch(const char* name);
+void check_cuda(cudaError_t e, const char* what);
+int sm_count();
+
+void launch_pack(bool prod, const void* key, const void* value, const int32_t* slots,
+                 uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,
+                 cudaStream_t stream);
+
+// hnd: write [H, N, D] instead of [N, H, D].
+void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* out_key,
+                    void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,
+                    cudaStream_t stream);
+
+struct DecodeArgs {
+    int scheme;                   // TQ_SCHEME_*
+    const void* query;            // fp16
+    const uint8_t* pool;
+    const int32_t* slot_mapping;  // per-token slots (reference API) or nullptr
+    const int32_t* block_tables;  // [batch, table_stride] or nullptr
+    int table_stride;
+    const int32_t* seq_lens;      // [batch] or nullptr (then every sequence has max_kv_tokens)
+    void* output;                 // fp16 or nullptr
+    float* partials_out;          // or nullptr
+    float* logits_out;            // turbo_prod logits entry point, or nullptr
+    PageGeom geo;
+    int head_dim;
+    int batch;
+    int num_q_heads;              // query rows per sequence = groups * num_kv_heads
+    int ref_query_layout;         // 1: query/output rows are [g][h] (reference), 0: [h*G+g]
+    int max_kv_tokens;
+    int kv_begin, kv_end;
+    void* workspace;
+    size_t workspace_bytes;
+};
+void launch_decode(const DecodeArgs& a, cudaStream_t stream);
+int decode_num_splits(int batch, int max_kv_tokens, int num_kv_heads, int block_size);
+size_t decode_workspace_bytes(int batch, int num_q_heads, int num_splits);
+void launch_merge(const float* partials, int num_parts, void* output, float* partials_out,
+                  int rows, int num_q_heads, int num_kv_heads, int ref_query_layout,
+                  int head_dim, cudaStream_t stream);
+
+}  // namespace tq

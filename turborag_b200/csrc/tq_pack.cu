@@ -1,0 +1,189 @@
+// Quantize + pack kernels (turbo_prod and turbo_mse) for sm_100a.
+//
+// Replaces turbo_prod_pack_kv_kernel (src/cuda/tq_turbo_prod_kernels.cu:110-260)
+// and turbo_mse_pack_kv_kernel (src/cuda/tq_turbo_mse_kernels.cu:186-237) of the
+// reference with one register-resident design: a warp owns four token-heads at
+// a time (8 lanes x 16 elements each), inputs arrive as 16-byte vector loads,
+// the 128-point transform runs in registers around one shared-memory re-deal,
+// and code bytes leave as 8-byte stores (64 contiguous bytes per token-head).
+// Results are bit-identical to the reference's arithmetic; see tq_common.cuh.
+#include "tq_common.cuh"
+#include "tq_launch.h"
+
+namespace tq {
+namespace {
+
+constexpr int kPackWarps = 8;
+constexpr int kCodeRowBytes = 72;  // 64 code bytes + pad: rows land on distinct banks
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+
+// Move a row's 64 code bytes from "lane l' holds byte l'+8j" to "lane l holds
+// bytes 8l..8l+7" through a per-warp byte buffer, then store them.
+__device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t* code_buf,
+                                            uint8_t* dst, int lane, bool valid, bool aligned8) {
+    const int rr = lane >> 3, l = lane & 7;
+    uint8_t* row = code_buf + rr * kCodeRowBytes;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) row[l + 8 * j] = static_cast<uint8_t>(byte_j[j]);
+    __syncwarp();
+    const uint2 v = *reinterpret_cast<const uint2*>(row + 8 * l);
+    __syncwarp();
+    if (!valid) return;
+    if (aligned8) {
+        *reinterpret_cast<uint2*>(dst + 8 * l) = v;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            dst[8 * l + i] = static_cast<uint8_t>(v.x >> (8 * i));
+            dst[8 * l + 4 + i] = static_cast<uint8_t>(v.y >> (8 * i));
+        }
+    }
+}
+
+template <bool PROD>
+__global__ void __launch_bounds__(kPackWarps * 32)
+pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
+               const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
+               PageGeom geo, int head_dim, long long num_rows, int pool_aligned8) {
+    __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rr = lane >> 3, l = lane & 7;
+    float* buf = xchg[warp];
+    uint8_t* code_buf = reinterpret_cast<uint8_t*>(buf);
+    const int H = geo.num_kv_heads;
+    const float c = inv_sqrt_dim(head_dim);
+    const long long groups = (num_rows + 3) >> 2;
+    const long long warps_total = static_cast<long long>(gridDim.x) * kPackWarps;
+
+    for (long long g = static_cast<long long>(blockIdx.x) * kPackWarps + warp; g < groups;
+         g += warps_total) {
+        const long long row_raw = g * 4 + rr;
+        const bool valid = row_raw < num_rows;
+        const long long row = valid ? row_raw : num_rows - 1;  // keep all lanes converged
+        const long long tok = row / H;
+        const int h = static_cast<int>(row - tok * H);
+        const float cs = (h & 1) ? -c : c;  // odd heads: the whole rotated row is negated
+
+        const uint4* kp = key + row * 16 + 2 * l;
+        const uint4* vp = value + row * 16 + 2 * l;
+        const uint4 k_lo = ld_stream(kp), k_hi = ld_stream(kp + 1);
+        const uint4 v_lo = ld_stream(vp), v_hi = ld_stream(vp + 1);
+        const int slot = __ldg(slot_mapping + tok);
+
+        const int blk = slot / geo.block_size;
+        const int tib = slot - blk * geo.block_size;
+        uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
+        const unsigned int th = static_cast<unsigned int>(tib * H + h);
+
+        float x[16], y[16];
+
+        // ---------------- K ----------------
+        fwht_phase1_from_half(k_lo, k_hi, x);
+        redeal(x, y, buf, lane);
+        fwht_phase2(y);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(y[i], cs);
+
+        uint32_t kbytes[8];
+        if (PROD) {
+            float sq[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sq[i] = __fmul_rn(y[i], y[i]);
+            const float krms = rms_from_sum(tree128(sq));
+            const float kr = __frcp_rn(krms);
+            float e2[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float e0, e1;
+                float kn0 = div_by(y[2 * j], krms, kr);
+                float kn1 = div_by(y[2 * j + 1], krms, kr);
+                kn0 = kn0 < -2.5f ? -2.5f : (kn0 > 2.5f ? 2.5f : kn0);
+                kn1 = kn1 < -2.5f ? -2.5f : (kn1 > 2.5f ? 2.5f : kn1);
+                const uint32_t n0 = quant_k3(kn0, e0), n1 = quant_k3(kn1, e1);
+                kbytes[j] = n0 | (n1 << 4);
+                e2[2 * j] = __fmul_rn(e0, e0);
+                e2[2 * j + 1] = __fmul_rn(e1, e1);
+            }
+            const float rms_e = rms_from_sum(tree128(e2));
+            if (valid && l == 0) {
+                *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
+                *reinterpret_cast<__half*>(page + geo.k_res + th * 2) = __float2half_rn(rms_e);
+            }
+        } else {
+            float pr[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                pr[j] = __fmaf_rn(y[2 * j], y[2 * j], __fmul_rn(y[2 * j + 1], y[2 * j + 1]));
+            const float krms = rms_from_sum(tree64(pr));
+            const float kr = __frcp_rn(krms);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t n0 = quant_v4(div_by(y[2 * j], krms, kr));
+                const uint32_t n1 = quant_v4(div_by(y[2 * j + 1], krms, kr));
+                kbytes[j] = n0 | (n1 << 4);
+            }
+            if (valid && l == 0)
+                *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
+        }
+        store_codes(kbytes, code_buf, page + geo.k_codes + th * 64, lane, valid,
+                    pool_aligned8 != 0);
+
+        // ---------------- V ----------------
+        fwht_phase1_from_half(v_lo, v_hi, x);
+        redeal(x, y, buf, lane);
+        fwht_phase2(y);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(y[i], cs);
+        float vrms;
+        if (PROD) {
+            float sq[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sq[i] = __fmul_rn(y[i], y[i]);
+            vrms = rms_from_sum(tree128(sq));
+        } else {
+            float pr[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                pr[j] = __fmaf_rn(y[2 * j], y[2 * j], __fmul_rn(y[2 * j + 1], y[2 * j + 1]));
+            vrms = rms_from_sum(tree64(pr));
+        }
+        const float vr = __frcp_rn(vrms);
+        uint32_t vbytes[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t n0 = quant_v4(div_by(y[2 * j], vrms, vr));
+            const uint32_t n1 = quant_v4(div_by(y[2 * j + 1], vrms, vr));
+            vbytes[j] = n0 | (n1 << 4);
+        }
+        if (valid && l == 0)
+            *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
+        store_codes(vbytes, code_buf, page + geo.v_codes + th * 64, lane, valid,
+                    pool_aligned8 != 0);
+    }
+}
+
+}  // namespace
+
+void launch_pack(bool prod, const void* key, const void* value, const int32_t* slots,
+                 uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,
+                 cudaStream_t stream) {
+    if (num_tokens <= 0) return;
+    const long long rows = static_cast<long long>(num_tokens) * geo.num_kv_heads;
+    const long long groups = (rows + 3) / 4;
+    long long blocks = (groups + kPackWarps - 1) / kPackWarps;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
+    if (prod)
+        pack_kv_kernel<true><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
+            static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
+            head_dim, rows, aligned);
+    else
+        pack_kv_kernel<false><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
+            static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
+            head_dim, rows, aligned);
+    check_launch(prod ? "turbo_prod pack_kv" : "turbo_mse pack_kv");
+}
+
+}  // namespace tq
