@@ -216,20 +216,16 @@ def decode_paged(scheme: str, query, pool, block_tables, seq_lens, cfg: Config):
     """Batched paged GQA decode: query [B, Hq, D] fp16 -> fp16 [B, Hq, D].
     block_tables int32 [B, max_pages]; token t of sequence b lives in slot
     block_tables[b, t // 16] * 16 + t % 16 (src/tq_block_table.cpp:24-39)."""
-    query = np.ascontiguousarray(query)
-    b, hq, d = query.shape
-    out = np.zeros((b, hq, d), np.float16)
-    bs = cfg.block_size
-    for i in range(b):
-        n = int(seq_lens[i])
-        slots = np.zeros(n, np.int32)
-        lib().orc_build_slot_map(_p(np.ascontiguousarray(block_tables[i], dtype=np.int32)),
-                                 C.c_int(0), C.c_int(n), C.c_int(bs), _p(slots))
-        if n == 0:
-            continue
-        o = attn(scheme, gqa_to_ref_query(query[i], cfg.num_kv_heads), pool, slots, cfg)
-        out[i] = ref_to_gqa_out(o)
-    return out
+    q = _u16(query)
+    b, hq, d = q.shape
+    tables = np.ascontiguousarray(block_tables, dtype=np.int32)
+    lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    lay = layout_for(scheme, cfg)
+    out = np.zeros((b, hq, d), np.uint16)
+    lib().orc_decode_paged(C.c_int(0 if scheme == "turbo_prod" else 1), _p(q), _p(pool), _p(tables),
+                           C.c_int(tables.shape[1]), _p(lens), _p(out), C.byref(lay), C.byref(cfg),
+                           C.c_int(b), C.c_int(hq))
+    return out.view(np.float16)
 
 
 def attention_ref_single_head(q, k_all, v_all):

@@ -36,8 +36,11 @@ uint16_t orc_f2h(float f) { /* round-to-nearest-even, as __float2half */
 #define h2f orc_h2f
 #define f2h orc_f2h
 
-/* rsqrtf(128.f) as the GPU evaluates it; fp32 nearest to 2^-3.5. */
-static uint32_t g_inv_sqrt_d_bits = 0x3DB504F3u;
+/* rsqrtf(128.f) as a B200 evaluates it (rsqrt.approx.f32): one ulp below the
+ * correctly rounded 2^-3.5 = 0x3DB504F3.  Pinned by the golden fixtures: with
+ * this constant the restated dequant reproduces every fp16 output bit of the
+ * reference run; with 0x3DB504F3 a few per thousand differ. */
+static uint32_t g_inv_sqrt_d_bits = 0x3DB504F2u;
 static int g_mse_pair_fma = 1;
 static int g_threads = 0;
 
@@ -565,6 +568,33 @@ void orc_mse_attn(const uint16_t* query, const uint8_t* pool,
             size_t r = (size_t)qi * H + h;
             mse_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv, st);
             attn_finish(st, h, d, out + r * d);
+        }
+}
+
+/* Batched paged GQA decode built from the two single-sequence kernels above:
+ * query/out [batch, hq, d] fp16; token t of sequence b sits in slot
+ * tables[b][t / bs] * bs + t % bs (src/tq_block_table.cpp:24-39); query head j
+ * uses kv head j / (hq / H).  Threads run over (sequence, query head). */
+void orc_decode_paged(int scheme, const uint16_t* query, const uint8_t* pool,
+                      const int32_t* tables, int table_stride,
+                      const int32_t* seq_lens, uint16_t* out, const void* lay,
+                      const OrcConfig* cfg, int batch, int hq) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads, grp = hq / H;
+    const int bs = cfg->block_size;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1) num_threads(nthreads())
+    for (int b = 0; b < batch; ++b)
+        for (int j = 0; j < hq; ++j) {
+            const int n = seq_lens[b], h = j / grp;
+            size_t r = (size_t)b * hq + j;
+            float st[130];
+            int32_t* slots = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n > 0 ? n : 1));
+            orc_build_slot_map(tables + (size_t)b * table_stride, 0, n, bs, slots);
+            if (scheme == 0)
+                prod_attn_state(query + r * d, pool, slots, (const OrcProdLayout*)lay, cfg, h, n, st);
+            else
+                mse_attn_state(query + r * d, pool, slots, (const OrcMseLayout*)lay, cfg, h, n, st);
+            attn_finish(st, h, d, out + r * d);
+            free(slots);
         }
 }
 

@@ -101,6 +101,12 @@ void orc_mse_attn_f32(const uint16_t* query, const uint8_t* pool,
                       const OrcMseLayout* lay, const OrcConfig* cfg, int nq,
                       int nkv);
 
+/* Batched paged GQA decode (scheme 0 = turbo_prod, 1 = turbo_mse). */
+void orc_decode_paged(int scheme, const uint16_t* query, const uint8_t* pool,
+                      const int32_t* tables, int table_stride,
+                      const int32_t* seq_lens, uint16_t* out, const void* lay,
+                      const OrcConfig* cfg, int batch, int hq);
+
 /* src/tq_attention_ref.cpp:10-56 — dense fp32 attention for one head. */
 int orc_attention_ref_single_head(const uint16_t* q, const uint16_t* k_all,
                                   const uint16_t* v_all, int num_tokens,

@@ -28,6 +28,12 @@ constexpr int kMaxHeads = 8;          // kv heads per CTA
 constexpr int kWarpSmemBytes = 4608;  // V tile (4096) or merge record (36*32*4)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+// The fp16 lookup tables hold alpha * level: alpha is chosen so that every
+// scaled level lands within 1.4e-5 (3-bit table) / 9.3e-5 (4-bit table) of an
+// fp16 value, against 4.2e-4 / 3.1e-4 unscaled; 1/alpha is folded into the fp32
+// query scale (K side) and into the per-token V scale.
+#define TQ_ALPHA3 TQF(0x3fa55cec)
+#define TQ_ALPHA4 TQF(0x404c9252)
 
 struct DecodeParams {
     const __half* query;
@@ -215,7 +221,7 @@ __device__ __forceinline__ void load_block(const DecodeParams& p, int b, int h, 
 
 // MODE 0: attention partials, MODE 1: logits only (turbo_prod).
 template <bool PROD, int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 decode_kernel(DecodeParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -235,7 +241,9 @@ decode_kernel(DecodeParams p) {
     // ---- rotate the queries of this pass: q' = FWHT(s .* q) * rsqrt(D) ------------
     // one warp per (kv head, column); lane holds 4 consecutive elements.
     const float c = inv_sqrt_dim(p.head_dim);
-    const float qscale = (MODE == 0) ? c * c * kLog2e : c * c;
+    const float alpha_k = PROD ? TQ_ALPHA3 : TQ_ALPHA4;
+    const float qscale = ((MODE == 0) ? c * c * kLog2e : c * c) / alpha_k;
+    const float inv_alpha_v = 1.0f / TQ_ALPHA4;
     for (int col = stream; col < 8; col += p.streams) {
         float x[4] = {0.f, 0.f, 0.f, 0.f};
         if (col < nq) {
@@ -281,8 +289,12 @@ decode_kernel(DecodeParams p) {
     }
 
     // ---- lookup tables ---------------------------------------------------------
-    const float t3[8] = {-TQ_C3_3, -TQ_C3_2, -TQ_C3_1, -TQ_C3_0, TQ_C3_0, TQ_C3_1, TQ_C3_2, TQ_C3_3};
-    const float t4[8] = {TQ_C4_0, TQ_C4_1, TQ_C4_2, TQ_C4_3, TQ_C4_4, TQ_C4_5, TQ_C4_6, TQ_C4_7};
+    const float t3[8] = {-TQ_C3_3 * TQ_ALPHA3, -TQ_C3_2 * TQ_ALPHA3, -TQ_C3_1 * TQ_ALPHA3,
+                         -TQ_C3_0 * TQ_ALPHA3, TQ_C3_0 * TQ_ALPHA3,  TQ_C3_1 * TQ_ALPHA3,
+                         TQ_C3_2 * TQ_ALPHA3,  TQ_C3_3 * TQ_ALPHA3};
+    const float t4[8] = {TQ_C4_0 * TQ_ALPHA4, TQ_C4_1 * TQ_ALPHA4, TQ_C4_2 * TQ_ALPHA4,
+                         TQ_C4_3 * TQ_ALPHA4, TQ_C4_4 * TQ_ALPHA4, TQ_C4_5 * TQ_ALPHA4,
+                         TQ_C4_6 * TQ_ALPHA4, TQ_C4_7 * TQ_ALPHA4};
     const BytePools pool3 = make_pools(t3);
     const BytePools mag4 = make_pools(t4);
 
@@ -342,7 +354,8 @@ decode_kernel(DecodeParams p) {
         lg[2] = s1[2] * cur.ks1;
         lg[3] = s1[3] * cur.ks1;
         if (PROD) {
-            const float r0 = cur.ks0 * cur.re0, r1 = cur.ks1 * cur.re1;
+            // the sign product shares the 1/alpha-scaled query fragments
+            const float r0 = cur.ks0 * cur.re0 * TQ_ALPHA3, r1 = cur.ks1 * cur.re1 * TQ_ALPHA3;
             lg[0] = fmaf(s2[0], r0, lg[0]);
             lg[1] = fmaf(s2[1], r0, lg[1]);
             lg[2] = fmaf(s2[2], r1, lg[2]);
@@ -391,8 +404,9 @@ decode_kernel(DecodeParams p) {
             }
         }
         // P^T (k = token, n = query), V scale folded in
-        const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * cur.vs0, p1 * cur.vs0));
-        const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * cur.vs1, p3 * cur.vs1));
+        const float w0 = cur.vs0 * inv_alpha_v, w1 = cur.vs1 * inv_alpha_v;
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * w0, p1 * w0));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
 
         // ---- V: unpack this lane's 64 codes into the swizzled tile ---------------
         const uint32_t vw[8] = {cur.v0.x, cur.v0.y, cur.v0.z, cur.v0.w,
