@@ -164,6 +164,29 @@ int tq_decode_paged(int scheme, const tq_half* query, const uint8_t* page_pool,
                     int kv_begin, int kv_end, void* workspace, size_t workspace_bytes,
                     tq_stream_t stream);
 
+/* Has no counterpart in the reference.  tq_decode_paged for callers that must not allocate
+ * device memory: a serving engine that gave the whole GPU to its own memory pool when it
+ * started, a latency-critical loop that cannot risk the synchronisation an allocation may
+ * bring, code running under stream capture.  Same inputs, outputs and results as
+ * tq_decode_paged(..., workspace = NULL) over the whole sequence, but the split-KV scratch is
+ * a fixed array inside the library (TQ_DECODE_STATIC_SCRATCH_BYTES per GPU, held from the
+ * moment the library is loaded on that GPU until the process ends) and the call performs no
+ * cudaMalloc / cudaFree / stream-ordered allocation.
+ *   - A shape whose scratch need, tq_decode_workspace_bytes(batch, num_q_heads,
+ *     tq_decode_num_splits(batch * ceil(group/8), max_kv_tokens, ..)), exceeds the array is
+ *     rejected with -2 and a message; use tq_decode_paged with your own workspace then.
+ *   - The first call on each device looks up the array's device address; make that call
+ *     before starting any stream capture on the device.
+ *   - Every call on a device uses the same array (it keeps the previous call's bytes; no
+ *     part needs clearing, each call rewrites all it reads).  Calls whose kernels may run at
+ *     the same time on one GPU race on it: issue them on one stream or order them yourself. */
+#define TQ_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+int tq_decode_paged_static(int scheme, const tq_half* query, const uint8_t* page_pool,
+                           const int32_t* block_tables, int table_stride,
+                           const int32_t* seq_lens, tq_half* output, const void* layout,
+                           const TQConfig* cfg, int batch, int num_q_heads, int max_kv_tokens,
+                           tq_stream_t stream);
+
 /* Log-sum-exp merge of `num_parts` partial sets laid out
  * [num_parts, rows, TQ_PARTIAL_STRIDE] (e.g. an all-gather over ranks), then
  * normalise, inverse rotation and fp16 store: output [rows, 128] with

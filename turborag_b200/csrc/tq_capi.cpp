@@ -155,6 +155,13 @@ void ref_attention(int scheme, const void* query, const uint8_t* pool, const int
 
 }  // namespace
 
+namespace tq {
+void set_last_error(const char* msg) { set_error(msg); }
+PageGeom geom_from_layout(int scheme, const void* layout, const TQConfig& cfg) {
+    return geom_for(scheme, layout, cfg);
+}
+}  // namespace tq
+
 // ---------------------------------------------------------------------------
 // Part 1 — reference surface
 // ---------------------------------------------------------------------------

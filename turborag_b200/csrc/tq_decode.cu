@@ -18,6 +18,9 @@
 //     per-warp swizzled shared tile and read back with ldmatrix.trans.
 // Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
 // and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
+#include <climits>
+#include <mutex>
+
 #include "tq_common.cuh"
 #include "tq_launch.h"
 
@@ -691,4 +694,100 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (owned) check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(decode workspace)");
 }
 
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation: the split-KV scratch lives in the library image.
+// ---------------------------------------------------------------------------------------
+//
+// Some hosts of this library must not allocate device memory on the decode path: a serving
+// engine that has handed the whole GPU to its own pool at start-up (any later driver
+// allocation can fail or fragment it), a real-time loop that cannot afford the implicit
+// synchronisation an allocation may cause, or code that runs while a CUDA stream is being
+// captured.  tq_decode_paged_static serves them: same arithmetic as tq_decode_paged, but the
+// split-KV partials go to the fixed array below instead of a caller buffer or cudaMallocAsync.
+//
+// The array is part of the loaded module: every GPU that loads the library holds these
+// bytes until the process exits.  All calls on a device share it, and it keeps whatever the
+// previous call wrote.  Nothing in it has to be zero at entry: the decode kernel writes the
+// (acc, m, l) record of every (sequence, split, query head) before the merge kernel reads it.
+// Two calls whose kernels can overlap on the same GPU (different streams, different threads)
+// race on it; serialise them.
+namespace {
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;  // 8 MiB per device
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// Device address of g_decode_scratch for the current device.  In host code the symbol's
+// name is only a handle, not an address a kernel can use; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+void* static_scratch_for_current_device() {
+    static void* ptrs[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64) throw std::runtime_error("decode_paged_static: device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        check_cuda(cudaGetSymbolAddress(&p, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
+        if (!p) throw std::runtime_error("decode_paged_static: scratch symbol has no device address");
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+}  // namespace
 }  // namespace tq
+
+static_assert(tq::kStaticScratchBytes == TQ_DECODE_STATIC_SCRATCH_BYTES, "header and array disagree");
+
+extern "C" int tq_decode_paged_static(int scheme, const tq_half* query, const uint8_t* page_pool,
+                                      const int32_t* block_tables, int table_stride,
+                                      const int32_t* seq_lens, tq_half* output, const void* layout,
+                                      const TQConfig* cfg, int batch, int num_q_heads,
+                                      int max_kv_tokens, tq_stream_t stream) {
+    if (!query || !page_pool || !block_tables || !seq_lens || !output || !layout || !cfg) return -1;
+    try {
+        if (cfg->head_dim != 128 || cfg->block_size < 1 || cfg->num_kv_heads < 1)
+            throw std::runtime_error("decode_paged_static: only head_dim == 128 is supported");
+        if (batch < 0 || num_q_heads < 1 || max_kv_tokens < 0 || table_stride < 0 ||
+            static_cast<long long>(table_stride) * cfg->block_size < max_kv_tokens)
+            throw std::runtime_error("decode_paged_static: bad sizes");
+        if ((reinterpret_cast<uintptr_t>(query) & 7) || (reinterpret_cast<uintptr_t>(output) & 3))
+            throw std::runtime_error("decode_paged_static: query must be 8-byte and output 4-byte aligned");
+        const int H = cfg->num_kv_heads;
+        if (H > 8 || num_q_heads % H != 0)
+            throw std::runtime_error("decode_paged_static: num_kv_heads must be 1..8 and divide num_q_heads");
+        const int qgroups = (num_q_heads / H + 7) / 8;
+        const int splits = tq::decode_num_splits(batch * qgroups, max_kv_tokens, H, cfg->block_size);
+        const size_t need = tq::decode_workspace_bytes(batch, num_q_heads, splits);
+        if (need > tq::kStaticScratchBytes)
+            throw std::runtime_error(
+                "decode_paged_static: this shape needs " + std::to_string(need) +
+                " bytes of split-KV scratch, the built-in array holds " +
+                std::to_string(tq::kStaticScratchBytes) + "; use tq_decode_paged with a workspace");
+        tq::DecodeArgs a{};
+        a.scheme = scheme;
+        a.query = query;
+        a.pool = page_pool;
+        a.block_tables = block_tables;
+        a.table_stride = table_stride;
+        a.seq_lens = seq_lens;
+        a.output = output;
+        a.geo = tq::geom_from_layout(scheme, layout, *cfg);
+        a.head_dim = cfg->head_dim;
+        a.batch = batch;
+        a.num_q_heads = num_q_heads;
+        a.ref_query_layout = 0;
+        a.max_kv_tokens = max_kv_tokens;
+        a.kv_begin = 0;
+        a.kv_end = INT_MAX;
+        a.workspace = tq::static_scratch_for_current_device();
+        a.workspace_bytes = tq::kStaticScratchBytes;
+        tq::launch_decode(a, static_cast<cudaStream_t>(stream));
+        return 0;
+    } catch (const std::exception& e) {
+        tq::set_last_error(e.what());
+        return -2;
+    } catch (...) {
+        tq::set_last_error("unknown error");
+        return -2;
+    }
+}

@@ -18,6 +18,11 @@ namespace tq {
 void check_launch(const char* name);
 void check_cuda(cudaError_t e, const char* what);
 int sm_count();
+// Stores a message for tq_last_error() of the calling thread.
+void set_last_error(const char* msg);
+// Page geometry from a TQTurboProdPageLayout* / TQTurbomsePageLayout* (throws on a layout that
+// does not belong to head_dim 128).
+PageGeom geom_from_layout(int scheme, const void* layout, const TQConfig& cfg);
 
 void launch_pack(bool prod, const void* key, const void* value, const int32_t* slots,
                  uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,

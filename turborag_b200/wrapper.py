@@ -69,6 +69,8 @@ SIGNATURES = {
     "tq_decode_workspace_bytes": (C.c_size_t, [C.c_int] * 3),
     "tq_decode_paged": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _P, _P, _CFG, C.c_int,
                                   C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P]),
+    "tq_decode_paged_static": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _P, _CFG, C.c_int,
+                                         C.c_int, C.c_int, _P]),
     "tq_merge_partials": (C.c_int, [_P, C.c_int, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tq_dequant_kv_hnd": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _CFG, C.c_int, _P]),
     "tq_mse_prefill_paged": (C.c_int, [_P, _P, _P, C.c_int, _P, _P, _P, _P, _MSE, _CFG, C.c_int,
@@ -271,6 +273,25 @@ class TurboQuantWrapper:
                    0 if workspace is None else workspace.numel() * workspace.element_size(),
                    C.c_void_p(stream))
         return output if output is not None else partials_out
+
+    def decode_paged_static(self, scheme: str, query, page_pool, block_tables, seq_lens, layout,
+                            cfg, output=None, max_kv_tokens: int | None = None, stream: int = 0):
+        """``decode_paged`` for hosts that cannot allocate device memory while decoding (an
+        engine whose own pool owns the GPU, a capture in progress): the split-KV scratch is a
+        fixed 8 MiB array inside the library, nothing is allocated or freed.  Shapes that need
+        more scratch raise; calls that may overlap on one GPU must be ordered by the caller."""
+        _cuda(query, page_pool, block_tables, seq_lens, output)
+        b, hq, _ = query.shape
+        if output is None:
+            output = torch.empty_like(query)
+        if max_kv_tokens is None:
+            max_kv_tokens = block_tables.shape[1] * cfg.block_size
+        self._call(scheme, "decode_paged_static", self._lib.tq_decode_paged_static,
+                   SCHEME_ID[scheme], _ptr(query), _ptr(page_pool), _ptr(block_tables),
+                   block_tables.shape[1], _ptr(seq_lens), _ptr(output),
+                   C.cast(C.byref(layout), C.c_void_p), C.byref(cfg), b, hq, max_kv_tokens,
+                   C.c_void_p(stream))
+        return output
 
     def merge_partials(self, partials, output, num_q_heads: int, num_kv_heads: int,
                        stream: int = 0):
