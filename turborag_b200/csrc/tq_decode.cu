@@ -222,37 +222,184 @@ __device__ __forceinline__ void load_block(const DecodeParams& p, int b, int h, 
     }
 }
 
-// MODE 0: attention partials, MODE 1: logits only (turbo_prod).
+// Everything a warp keeps across the blocks of its stream.
+struct WarpState {
+    float o[8][4];      // O^T accumulators: 8 tiles of 16 dims x 8 queries
+    float m_run[2], l_run[2];
+};
+
+struct BlockCtx {
+    uint32_t qf[8][2];  // B fragments of the rotated, pre-scaled queries
+    BytePools pool3, mag4;
+    float inv_alpha_v;
+    uint8_t* warp_smem;
+    uint32_t tile_addr;
+    int lane, g, tig, rv, hb, h, H, nq, gq0;
+};
+
+// One 16-token block for one kv head: QK^T (+ residual-sign product), online softmax,
+// V unpack into the shared tile, PV.  MODE 1 writes logits instead.
 template <bool PROD, int MODE>
-__global__ void __launch_bounds__(256, 2)
-decode_kernel(DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+__device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
+                                              const BlockRaw& cur, int tb, int t_end,
+                                              WarpState& st) {
+    const int g = c.g, tig = c.tig, lane = c.lane, rv = c.rv, hb = c.hb, h = c.h, H = c.H;
+    const int nq = c.nq, gq0 = c.gq0;
+    const BytePools& pool3 = c.pool3;
+    const BytePools& mag4 = c.mag4;
+    const float inv_alpha_v = c.inv_alpha_v;
+    uint8_t* warp_smem = c.warp_smem;
+    const uint32_t tile_addr = c.tile_addr;
+    float (&o)[8][4] = st.o;
+    float (&m_run)[2] = st.m_run;
+    float (&l_run)[2] = st.l_run;
+    const uint32_t (&qf)[8][2] = c.qf;
+    // ---- S = K_hat Q'^T (rows = tokens g, g+8; cols = queries 2tig, 2tig+1) ----
+    float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
+    const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        uint32_t a[4], bq[4];
+        if (PROD) {
+            unpack_k3(kw0[wi], pool3, a);
+            unpack_k3(kw1[wi], pool3, bq);
+        } else {
+            unpack_c4(kw0[wi], mag4, a);
+            unpack_c4(kw1[wi], mag4, bq);
+        }
+        mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+        mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+        if (PROD) {
+            unpack_sign(kw0[wi], a);
+            unpack_sign(kw1[wi], bq);
+            mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+            mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+        }
+    }
+    const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
+    float lg[4];
+    lg[0] = s1[0] * cur.ks0;
+    lg[1] = s1[1] * cur.ks0;
+    lg[2] = s1[2] * cur.ks1;
+    lg[3] = s1[3] * cur.ks1;
+    if (PROD) {
+        // the sign product shares the 1/alpha-scaled query fragments
+        const float r0 = cur.ks0 * cur.re0 * TQ_ALPHA3, r1 = cur.ks1 * cur.re1 * TQ_ALPHA3;
+        lg[0] = fmaf(s2[0], r0, lg[0]);
+        lg[1] = fmaf(s2[1], r0, lg[1]);
+        lg[2] = fmaf(s2[2], r1, lg[2]);
+        lg[3] = fmaf(s2[3], r1, lg[3]);
+    }
+
+    if (MODE == 1) {
+        // logits[(q*H + h)*N + t]  (tq_turbo_prod_kernels.cu:428-431)
+        const long long nkv = p.max_kv_tokens;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = 2 * tig + (e & 1);
+            const int t = tb + g + 8 * (e >> 1);
+            if (col < nq && t < t_end)
+                p.logits[(static_cast<long long>(gq0 + col) * H + h) * nkv + t] = lg[e];
+        }
+        return;
+    }
+
+    if (!ok0) lg[0] = lg[1] = -INFINITY;
+    if (!ok1) lg[2] = lg[3] = -INFINITY;
+
+    // ---- online softmax over the 16 tokens of the block ---------------------
+    float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
+#pragma unroll
+    for (int msk = 4; msk < 32; msk <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, msk));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
+    }
+    const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+    const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+    m_run[0] = mn0;
+    m_run[1] = mn1;
+    const float p0 = ex2(lg[0] - mn0), p1 = ex2(lg[1] - mn1);
+    const float p2 = ex2(lg[2] - mn0), p3 = ex2(lg[3] - mn1);
+    l_run[0] = fmaf(l_run[0], al0, p0 + p2);
+    l_run[1] = fmaf(l_run[1], al1, p1 + p3);
+    if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            o[j][0] *= al0;
+            o[j][1] *= al1;
+            o[j][2] *= al0;
+            o[j][3] *= al1;
+        }
+    }
+    // P^T (k = token, n = query), V scale folded in
+    const float w0 = cur.vs0 * inv_alpha_v, w1 = cur.vs1 * inv_alpha_v;
+    const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * w0, p1 * w0));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
+
+    // ---- V: unpack this lane's 64 codes into the swizzled tile ---------------
+    const uint32_t vw[8] = {cur.v0.x, cur.v0.y, cur.v0.z, cur.v0.w,
+                            cur.v1.x, cur.v1.y, cur.v1.z, cur.v1.w};
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) {
+        uint32_t a[4];
+        unpack_c4(vw[wi], mag4, a);
+        const int unit = 8 * hb + wi;
+        *reinterpret_cast<uint4*>(warp_smem + rv * 256 + ((unit ^ (rv & 7)) << 4)) =
+            make_uint4(a[0], a[1], a[2], a[3]);
+    }
+    __syncwarp();
+    // ---- O^T += V^T P^T -------------------------------------------------------
+    {
+        const int mat = lane >> 3;
+        const int tok = (lane & 7) + 8 * (mat >> 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int unit = 2 * j + (mat & 1);
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, tile_addr + tok * 256 + ((unit ^ (tok & 7)) << 4));
+            mma16816(o[j], a[0], a[1], a[2], a[3], pb0, pb1);
+        }
+    }
+    __syncwarp();
+}
+
+// Per-CTA geometry shared by both kernels.
+struct CtaRange {
+    int split, b, G, rows_per_seq, stream, t_begin, t_end, blk_lo, blk_hi;
+};
+
+// Prologue: rotate this pass's queries (q' = FWHT(s .* q) * rsqrt(D), pre-scaled), build the
+// B fragments and the lookup pools, and work out the CTA's block range.
+template <bool PROD, int MODE>
+__device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* smem_raw,
+                                                int warp_bytes, BlockCtx& ctx, CtaRange& r) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int H = p.geo.num_kv_heads;
     const int h = warp % H, stream = warp / H;
     const int g = lane >> 2, tig = lane & 3;
-    const int split = blockIdx.x, b = blockIdx.y, qg = blockIdx.z;
-    const int G = p.groups;
-    const int gq0 = qg * 8;                // first query of this pass within the group
-    const int nq = min(8, G - gq0);        // live columns
-    const int rows_per_seq = G * H;
-    const bool aligned = p.aligned16 != 0;
+    const int qg = blockIdx.z;
+    r.split = blockIdx.x;
+    r.b = blockIdx.y;
+    r.G = p.groups;
+    r.rows_per_seq = r.G * H;
+    r.stream = stream;
+    const int gq0 = qg * 8;                  // first query of this pass within the group
+    const int nq = min(8, r.G - gq0);        // live columns
 
-    uint8_t* warp_smem = smem_raw + warp * kWarpSmemBytes;
-    __half* qsm = reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * kWarpSmemBytes);
+    uint8_t* warp_smem = smem_raw + warp * warp_bytes;
+    __half* qsm = reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * warp_bytes);
 
-    // ---- rotate the queries of this pass: q' = FWHT(s .* q) * rsqrt(D) ------------
-    // one warp per (kv head, column); lane holds 4 consecutive elements.
+    // one warp per (kv head, column); lane holds 4 consecutive elements
     const float c = inv_sqrt_dim(p.head_dim);
     const float alpha_k = PROD ? TQ_ALPHA3 : TQ_ALPHA4;
     const float qscale = ((MODE == 0) ? c * c * kLog2e : c * c) / alpha_k;
-    const float inv_alpha_v = 1.0f / TQ_ALPHA4;
     for (int col = stream; col < 8; col += p.streams) {
         float x[4] = {0.f, 0.f, 0.f, 0.f};
         if (col < nq) {
             const int gq = gq0 + col;
-            const long long qrow = static_cast<long long>(b) * rows_per_seq +
-                                   (p.ref_layout ? gq * H + h : h * G + gq);
+            const long long qrow = static_cast<long long>(r.b) * r.rows_per_seq +
+                                   (p.ref_layout ? gq * H + h : h * r.G + gq);
             const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.query + qrow * kHeadDim) + lane);
             const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
             const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
@@ -278,7 +425,6 @@ decode_kernel(DecodeParams p) {
     __syncthreads();
 
     // B fragments: column g, dims 32*tig + 8*wi + {2hf, 2hf+4 | 2hf+1, 2hf+5}
-    uint32_t qf[8][2];
     {
         const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
 #pragma unroll
@@ -286,170 +432,64 @@ decode_kernel(DecodeParams p) {
             const int base = 8 * (s >> 1) + 2 * (s & 1);
             const __half2 b01 = __halves2half2(qrow[base], qrow[base + 4]);
             const __half2 b23 = __halves2half2(qrow[base + 1], qrow[base + 5]);
-            qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
-            qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
+            ctx.qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
+            ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
         }
     }
-
-    // ---- lookup tables ---------------------------------------------------------
     const float t3[8] = {-TQ_C3_3 * TQ_ALPHA3, -TQ_C3_2 * TQ_ALPHA3, -TQ_C3_1 * TQ_ALPHA3,
                          -TQ_C3_0 * TQ_ALPHA3, TQ_C3_0 * TQ_ALPHA3,  TQ_C3_1 * TQ_ALPHA3,
                          TQ_C3_2 * TQ_ALPHA3,  TQ_C3_3 * TQ_ALPHA3};
     const float t4[8] = {TQ_C4_0 * TQ_ALPHA4, TQ_C4_1 * TQ_ALPHA4, TQ_C4_2 * TQ_ALPHA4,
                          TQ_C4_3 * TQ_ALPHA4, TQ_C4_4 * TQ_ALPHA4, TQ_C4_5 * TQ_ALPHA4,
                          TQ_C4_6 * TQ_ALPHA4, TQ_C4_7 * TQ_ALPHA4};
-    const BytePools pool3 = make_pools(t3);
-    const BytePools mag4 = make_pools(t4);
+    ctx.pool3 = make_pools(t3);
+    ctx.mag4 = make_pools(t4);
+    ctx.inv_alpha_v = 1.0f / TQ_ALPHA4;
+    ctx.warp_smem = warp_smem;
+    ctx.tile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
+    ctx.lane = lane;
+    ctx.g = g;
+    ctx.tig = tig;
+    ctx.rv = (lane & 7) + 8 * (lane >> 4);
+    ctx.hb = (lane >> 3) & 1;
+    ctx.h = h;
+    ctx.H = H;
+    ctx.nq = nq;
+    ctx.gq0 = gq0;
 
-    // ---- this CTA's token range --------------------------------------------------
-    int n = p.seq_lens ? min(__ldg(p.seq_lens + b), p.max_kv_tokens) : p.max_kv_tokens;
-    const int t_begin = max(p.kv_begin, 0);
-    const int t_end = min(n, p.kv_end);
-    const int nblk = t_end > t_begin ? (t_end - t_begin + 15) >> 4 : 0;
+    const int n = p.seq_lens ? min(__ldg(p.seq_lens + r.b), p.max_kv_tokens) : p.max_kv_tokens;
+    r.t_begin = max(p.kv_begin, 0);
+    r.t_end = min(n, p.kv_end);
+    const int nblk = r.t_end > r.t_begin ? (r.t_end - r.t_begin + 15) >> 4 : 0;
     const int per = (nblk + p.splits - 1) / p.splits;
-    const int blk_lo = split * per, blk_hi = min(nblk, blk_lo + per);
+    r.blk_lo = r.split * per;
+    r.blk_hi = min(nblk, r.blk_lo + per);
+}
 
-    float o[8][4];
+__device__ __forceinline__ void init_state(WarpState& st) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-    float m_run[2] = {kInitMaxLogit, kInitMaxLogit}, l_run[2] = {0.0f, 0.0f};
+    for (int j = 0; j < 8; ++j) st.o[j][0] = st.o[j][1] = st.o[j][2] = st.o[j][3] = 0.0f;
+    st.m_run[0] = st.m_run[1] = kInitMaxLogit;
+    st.l_run[0] = st.l_run[1] = 0.0f;
+}
 
-    const uint32_t tile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
-    const int rv = (lane & 7) + 8 * (lane >> 4), hb = (lane >> 3) & 1;
-
-    BlockRaw cur;
-    int blk = blk_lo + stream;
-    if (blk < blk_hi) load_block<PROD>(p, b, h, t_begin + 16 * blk, t_end, lane, aligned, cur);
-
-    for (; blk < blk_hi; blk += p.streams) {
-        const int tb = t_begin + 16 * blk;
-        BlockRaw nxt = cur;
-        if (blk + p.streams < blk_hi)
-            load_block<PROD>(p, b, h, t_begin + 16 * (blk + p.streams), t_end, lane, aligned, nxt);
-
-        // ---- S = K_hat Q'^T (rows = tokens g, g+8; cols = queries 2tig, 2tig+1) ----
-        float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
-        const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
-#pragma unroll
-        for (int wi = 0; wi < 4; ++wi) {
-            uint32_t a[4], bq[4];
-            if (PROD) {
-                unpack_k3(kw0[wi], pool3, a);
-                unpack_k3(kw1[wi], pool3, bq);
-            } else {
-                unpack_c4(kw0[wi], mag4, a);
-                unpack_c4(kw1[wi], mag4, bq);
-            }
-            mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-            mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-            if (PROD) {
-                unpack_sign(kw0[wi], a);
-                unpack_sign(kw1[wi], bq);
-                mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-                mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-            }
-        }
-        const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
-        float lg[4];
-        lg[0] = s1[0] * cur.ks0;
-        lg[1] = s1[1] * cur.ks0;
-        lg[2] = s1[2] * cur.ks1;
-        lg[3] = s1[3] * cur.ks1;
-        if (PROD) {
-            // the sign product shares the 1/alpha-scaled query fragments
-            const float r0 = cur.ks0 * cur.re0 * TQ_ALPHA3, r1 = cur.ks1 * cur.re1 * TQ_ALPHA3;
-            lg[0] = fmaf(s2[0], r0, lg[0]);
-            lg[1] = fmaf(s2[1], r0, lg[1]);
-            lg[2] = fmaf(s2[2], r1, lg[2]);
-            lg[3] = fmaf(s2[3], r1, lg[3]);
-        }
-
-        if (MODE == 1) {
-            // logits[(q*H + h)*N + t]  (tq_turbo_prod_kernels.cu:428-431)
-            const long long nkv = p.max_kv_tokens;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int col = 2 * tig + (e & 1);
-                const int t = tb + g + 8 * (e >> 1);
-                if (col < nq && t < t_end)
-                    p.logits[(static_cast<long long>(gq0 + col) * H + h) * nkv + t] = lg[e];
-            }
-            cur = nxt;
-            continue;
-        }
-
-        if (!ok0) lg[0] = lg[1] = -INFINITY;
-        if (!ok1) lg[2] = lg[3] = -INFINITY;
-
-        // ---- online softmax over the 16 tokens of the block ---------------------
-        float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
-#pragma unroll
-        for (int msk = 4; msk < 32; msk <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, msk));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
-        }
-        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-        const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-        const float p0 = ex2(lg[0] - mn0), p1 = ex2(lg[1] - mn1);
-        const float p2 = ex2(lg[2] - mn0), p3 = ex2(lg[3] - mn1);
-        l_run[0] = fmaf(l_run[0], al0, p0 + p2);
-        l_run[1] = fmaf(l_run[1], al1, p1 + p3);
-        if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                o[j][0] *= al0;
-                o[j][1] *= al1;
-                o[j][2] *= al0;
-                o[j][3] *= al1;
-            }
-        }
-        // P^T (k = token, n = query), V scale folded in
-        const float w0 = cur.vs0 * inv_alpha_v, w1 = cur.vs1 * inv_alpha_v;
-        const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * w0, p1 * w0));
-        const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
-
-        // ---- V: unpack this lane's 64 codes into the swizzled tile ---------------
-        const uint32_t vw[8] = {cur.v0.x, cur.v0.y, cur.v0.z, cur.v0.w,
-                                cur.v1.x, cur.v1.y, cur.v1.z, cur.v1.w};
-#pragma unroll
-        for (int wi = 0; wi < 8; ++wi) {
-            uint32_t a[4];
-            unpack_c4(vw[wi], mag4, a);
-            const int unit = 8 * hb + wi;
-            *reinterpret_cast<uint4*>(warp_smem + rv * 256 + ((unit ^ (rv & 7)) << 4)) =
-                make_uint4(a[0], a[1], a[2], a[3]);
-        }
-        __syncwarp();
-        // ---- O^T += V^T P^T -------------------------------------------------------
-        {
-            const int mat = lane >> 3;
-            const int tok = (lane & 7) + 8 * (mat >> 1);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int unit = 2 * j + (mat & 1);
-                uint32_t a[4];
-                ldmatrix_x4_trans(a, tile_addr + tok * 256 + ((unit ^ (tok & 7)) << 4));
-                mma16816(o[j], a[0], a[1], a[2], a[3], pb0, pb1);
-            }
-        }
-        __syncwarp();
-        cur = nxt;
-    }
-
-    if (MODE == 1) return;
-
-    // ---- combine the streams of a kv head, then write the split partial --------
+// Epilogue: combine the streams of a kv head through shared memory (the per-warp regions
+// are dead by now and are reused as records), then write the split partial.
+__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* smem_raw,
+                                                int warp_bytes, const BlockCtx& c,
+                                                const CtaRange& r, WarpState& st) {
+    const int lane = c.lane, g = c.g, tig = c.tig, h = c.h, H = c.H;
+    float (&o)[8][4] = st.o;
+    float (&m_run)[2] = st.m_run;
+    float (&l_run)[2] = st.l_run;
 #pragma unroll
     for (int msk = 4; msk < 32; msk <<= 1) {
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], msk);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], msk);
     }
-    __syncthreads();  // V tiles are dead; reuse the per-warp regions as records
-    float* rec = reinterpret_cast<float*>(warp_smem);
-    if (stream > 0) {
+    __syncthreads();
+    float* rec = reinterpret_cast<float*>(c.warp_smem);
+    if (r.stream > 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -460,37 +500,37 @@ decode_kernel(DecodeParams p) {
         rec[35 * 32 + lane] = l_run[1];
     }
     __syncthreads();
-    if (stream > 0) return;
+    if (r.stream > 0) return;
     for (int s = 1; s < p.streams; ++s) {
-        const float* r = reinterpret_cast<const float*>(smem_raw + (s * H + h) * kWarpSmemBytes);
-        const float ms0 = r[32 * 32 + lane], ms1 = r[33 * 32 + lane];
+        const float* q = reinterpret_cast<const float*>(smem_raw + (s * H + h) * warp_bytes);
+        const float ms0 = q[32 * 32 + lane], ms1 = q[33 * 32 + lane];
         const float mn0 = fmaxf(m_run[0], ms0), mn1 = fmaxf(m_run[1], ms1);
         const float a0 = ex2(m_run[0] - mn0), a1 = ex2(m_run[1] - mn1);
         const float b0 = ex2(ms0 - mn0), b1 = ex2(ms1 - mn1);
-        l_run[0] = l_run[0] * a0 + r[34 * 32 + lane] * b0;
-        l_run[1] = l_run[1] * a1 + r[35 * 32 + lane] * b1;
+        l_run[0] = l_run[0] * a0 + q[34 * 32 + lane] * b0;
+        l_run[1] = l_run[1] * a1 + q[35 * 32 + lane] * b1;
         m_run[0] = mn0;
         m_run[1] = mn1;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            o[j][0] = o[j][0] * a0 + r[(4 * j + 0) * 32 + lane] * b0;
-            o[j][1] = o[j][1] * a1 + r[(4 * j + 1) * 32 + lane] * b1;
-            o[j][2] = o[j][2] * a0 + r[(4 * j + 2) * 32 + lane] * b0;
-            o[j][3] = o[j][3] * a1 + r[(4 * j + 3) * 32 + lane] * b1;
+            o[j][0] = o[j][0] * a0 + q[(4 * j + 0) * 32 + lane] * b0;
+            o[j][1] = o[j][1] * a1 + q[(4 * j + 1) * 32 + lane] * b1;
+            o[j][2] = o[j][2] * a0 + q[(4 * j + 2) * 32 + lane] * b0;
+            o[j][3] = o[j][3] * a1 + q[(4 * j + 3) * 32 + lane] * b1;
         }
     }
     // partial record: acc[128] (natural dim order), m in natural-log units, l
-    float* out = p.partials +
-                 (static_cast<long long>(b) * p.splits + split) * rows_per_seq * TQ_PARTIAL_STRIDE;
+    float* out = p.partials + (static_cast<long long>(r.b) * p.splits + r.split) * r.rows_per_seq *
+                                  TQ_PARTIAL_STRIDE;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
         const int col = 2 * tig + e;
-        if (col >= nq) continue;
-        float* row = out + static_cast<long long>(h * G + gq0 + col) * TQ_PARTIAL_STRIDE;
+        if (col >= c.nq) continue;
+        float* row = out + static_cast<long long>(h * r.G + c.gq0 + col) * TQ_PARTIAL_STRIDE;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            // accumulator rows g (unit 2j) and g+8 (unit 2j+1); position g of a
-            // unit is dim (g>>1) + 4*(g&1)
+            // accumulator rows g (unit 2j) and g+8 (unit 2j+1); position g of a unit is
+            // dim (g>>1) + 4*(g&1)
             const int d = (g >> 1) + 4 * (g & 1);
             row[16 * j + d] = o[j][e];
             row[16 * j + 8 + d] = o[j][2 + e];
@@ -500,6 +540,155 @@ decode_kernel(DecodeParams p) {
             row[129] = l_run[e];
         }
     }
+}
+
+// General kernel: any slot mapping / block size / alignment; one block of register prefetch.
+// MODE 0: attention partials, MODE 1: logits only (turbo_prod).
+template <bool PROD, int MODE>
+__global__ void __launch_bounds__(256, 2)
+decode_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    BlockCtx ctx;
+    CtaRange r;
+    decode_prologue<PROD, MODE>(p, smem_raw, kWarpSmemBytes, ctx, r);
+    WarpState st;
+    init_state(st);
+    const bool aligned = p.aligned16 != 0;
+
+    BlockRaw cur;
+    int blk = r.blk_lo + r.stream;
+    if (blk < r.blk_hi)
+        load_block<PROD>(p, r.b, ctx.h, r.t_begin + 16 * blk, r.t_end, ctx.lane, aligned, cur);
+    for (; blk < r.blk_hi; blk += p.streams) {
+        const int tb = r.t_begin + 16 * blk;
+        BlockRaw nxt = cur;
+        if (blk + p.streams < r.blk_hi)
+            load_block<PROD>(p, r.b, ctx.h, r.t_begin + 16 * (blk + p.streams), r.t_end, ctx.lane,
+                             aligned, nxt);
+        process_block<PROD, MODE>(p, ctx, cur, tb, r.t_end, st);
+        cur = nxt;
+    }
+    if (MODE == 1) return;
+    decode_epilogue(p, smem_raw, kWarpSmemBytes, ctx, r, st);
+}
+
+// ---- paged fast path ----------------------------------------------------------------
+// Block tables with 16-token pages, 16-byte aligned pool: a 16-token block IS a page, so
+// every lane's source offsets inside the page are loop constants.  Code bytes and scales
+// travel global -> shared with cp.async (no registers held while in flight) into a
+// per-warp ring of kStages stages; cp.async.wait_group paces the consumer.
+constexpr int kStages = 3;
+constexpr int kStageCodeBytes = 4 * 32 * 16;   // 4 sixteen-byte chunks per lane
+constexpr int kStageScaleBytes = 3 * 32 * 8;   // three regions of 16*H fp16, H <= 8
+constexpr int kStageBytes = kStageCodeBytes + kStageScaleBytes;
+constexpr int kFastWarpBytes = kWarpSmemBytes + kStages * kStageBytes;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <bool PROD>
+__global__ void __launch_bounds__(256, 2)
+decode_paged16_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    BlockCtx ctx;
+    CtaRange r;
+    decode_prologue<PROD, 0>(p, smem_raw, kFastWarpBytes, ctx, r);
+    WarpState st;
+    init_state(st);
+    const int lane = ctx.lane, g = ctx.g, tig = ctx.tig, h = ctx.h, H = ctx.H;
+
+    uint8_t* ring = ctx.warp_smem + kWarpSmemBytes;
+    const uint32_t ring_addr = ctx.tile_addr + kWarpSmemBytes;
+    // loop-constant source offsets inside a page
+    const uint32_t k_off0 = p.geo.k_codes + ((g * H + h) << 6) + (tig << 4);
+    const uint32_t k_off1 = k_off0 + (H << 9);
+    const uint32_t v_off = p.geo.v_codes + ((ctx.rv * H + h) << 6) + (ctx.hb << 5);
+    // scale regions (16*H fp16 each) are copied in 16-byte pieces spread over the lanes
+    const int pieces_per_region = 2 * H;
+    const int n_regions = PROD ? 3 : 2;
+    uint32_t sc_src[2], sc_dst[2];
+    bool sc_on[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = lane + 32 * k;
+        const int reg = i / pieces_per_region, j = i - reg * pieces_per_region;
+        sc_on[k] = reg < n_regions;
+        const uint32_t base = reg == 0 ? p.geo.k_scales : (reg == 1 ? p.geo.v_scales : p.geo.k_res);
+        sc_src[k] = base + 16 * j;
+        sc_dst[k] = kStageCodeBytes + reg * 256 + 16 * j;
+    }
+    // where this lane's scales sit inside a stage (bytes)
+    const uint32_t s_idx0 = 2 * (g * H + h), s_idx1 = s_idx0 + 16 * H;
+
+    const int page0 = r.t_begin >> 4;
+    const int32_t* table = p.block_tables + static_cast<long long>(r.b) * p.table_stride + page0;
+    const int n_iter = r.blk_hi > r.blk_lo + r.stream
+                           ? (r.blk_hi - r.blk_lo - r.stream + p.streams - 1) / p.streams : 0;
+
+    // page ids of 32 consecutive iterations, one per lane
+    int ids = 0, ids_base = 0;
+    auto refill = [&](int it0) {
+        const int it = it0 + lane;
+        ids = it < n_iter ? __ldg(table + r.blk_lo + r.stream + it * p.streams) : 0;
+        ids_base = it0;
+    };
+    auto issue = [&](int it) {
+        if (it < n_iter) {
+            if (it - ids_base >= 32) refill(it);
+            const int page = __shfl_sync(0xffffffffu, ids, it - ids_base);
+            const uint8_t* src = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
+            const uint32_t dst = ring_addr + (it % kStages) * kStageBytes;
+            cp_async16(dst + (0 * 32 + lane) * 16, src + k_off0);
+            cp_async16(dst + (1 * 32 + lane) * 16, src + k_off1);
+            cp_async16(dst + (2 * 32 + lane) * 16, src + v_off);
+            cp_async16(dst + (3 * 32 + lane) * 16, src + v_off + 16);
+            if (sc_on[0]) cp_async16(dst + sc_dst[0], src + sc_src[0]);
+            if (sc_on[1]) cp_async16(dst + sc_dst[1], src + sc_src[1]);
+        }
+        cp_async_commit();  // one group per iteration, empty or not, keeps the count uniform
+    };
+
+    refill(0);
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(s);
+
+    for (int it = 0; it < n_iter; ++it) {
+        issue(it + kStages - 1);
+        cp_async_wait<kStages - 1>();
+        __syncwarp();  // scale pieces are copied by other lanes
+        const uint8_t* stg = ring + (it % kStages) * kStageBytes;
+        const int blk = r.blk_lo + r.stream + it * p.streams;
+        const int tb = r.t_begin + 16 * blk;
+        BlockRaw cur;
+        cur.k0 = *reinterpret_cast<const uint4*>(stg + (0 * 32 + lane) * 16);
+        cur.k1 = *reinterpret_cast<const uint4*>(stg + (1 * 32 + lane) * 16);
+        cur.v0 = *reinterpret_cast<const uint4*>(stg + (2 * 32 + lane) * 16);
+        cur.v1 = *reinterpret_cast<const uint4*>(stg + (3 * 32 + lane) * 16);
+        const uint8_t* sc = stg + kStageCodeBytes;
+        // rows past the end of the sequence may hold anything: zero their scales so that
+        // P * vs stays finite (their logits are masked to -inf separately)
+        const bool ok0 = tb + g < r.t_end, ok1 = tb + g + 8 < r.t_end;
+        auto ld = [&](uint32_t off, bool ok) {
+            const float v = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sc + off)));
+            return ok ? v : 0.0f;
+        };
+        cur.ks0 = ld(s_idx0, ok0);
+        cur.ks1 = ld(s_idx1, ok1);
+        cur.vs0 = ld(256 + s_idx0, ok0);
+        cur.vs1 = ld(256 + s_idx1, ok1);
+        cur.re0 = PROD ? ld(512 + s_idx0, ok0) : 0.0f;
+        cur.re1 = PROD ? ld(512 + s_idx1, ok1) : 0.0f;
+        process_block<PROD, 0>(p, ctx, cur, tb, r.t_end, st);
+        // process_block ends with __syncwarp: every lane is done with this stage
+    }
+    cp_async_wait<0>();
+    decode_epilogue(p, smem_raw, kFastWarpBytes, ctx, r, st);
 }
 
 // ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
@@ -577,6 +766,11 @@ void set_smem_attr_once() {
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    const int fast_bytes = 8 * kFastWarpBytes + kMaxHeads * 8 * kHeadDim * 2;
+    check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<true>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), "smem attr");
+    check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<false>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), "smem attr");
     done[dev] = true;
 }
 
@@ -677,10 +871,20 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     p.splits = splits;
 
     const dim3 grid(splits, a.batch, qgroups);
-    if (prod)
+    const bool fast = a.block_tables && !a.slot_mapping && a.geo.block_size == 16 && p.aligned16 &&
+                      warps <= 8 && (a.geo.k_scales & 15) == 0 && (a.geo.v_scales & 15) == 0 &&
+                      (!prod || (a.geo.k_res & 15) == 0) && a.kv_begin >= 0 && (a.kv_begin & 15) == 0;
+    if (fast) {
+        const size_t fsmem = static_cast<size_t>(warps) * kFastWarpBytes + H * 8 * kHeadDim * sizeof(__half);
+        if (prod)
+            decode_paged16_kernel<true><<<grid, warps * 32, fsmem, stream>>>(p);
+        else
+            decode_paged16_kernel<false><<<grid, warps * 32, fsmem, stream>>>(p);
+    } else if (prod) {
         decode_kernel<true, 0><<<grid, warps * 32, smem, stream>>>(p);
-    else
+    } else {
         decode_kernel<false, 0><<<grid, warps * 32, smem, stream>>>(p);
+    }
     check_launch(prod ? "turbo_prod decode" : "turbo_mse decode");
 
     // merge the splits of every (sequence, query head) row
