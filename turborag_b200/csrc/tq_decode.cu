@@ -14,8 +14,9 @@
 //     (8-entry signed table for the 3-bit K code, 8-entry magnitude table plus a
 //     sign XOR for the 4-bit codes); the 1-bit residual sign is a second MMA with
 //     +-1 operands, scaled per token column (ks*re) afterwards;
-//   * V^T is the A operand of the second product: unpacked rows are staged in a
-//     per-warp swizzled shared tile and read back with ldmatrix.trans.
+//   * V^T is the A operand of the second product; its k index runs over tokens, so the
+//     lookup selectors are assembled from the same word of two adjacent tokens and the
+//     table values come out already paired along tokens (no shared-memory transpose).
 // Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
 // and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
 #include <climits>
@@ -28,7 +29,7 @@ namespace tq {
 namespace {
 
 constexpr int kMaxHeads = 8;          // kv heads per CTA
-constexpr int kWarpSmemBytes = 4608;  // V tile (4096) or merge record (36*32*4)
+constexpr int kWarpSmemBytes = 4608;  // per-warp merge record: 36 floats x 32 lanes
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 // The fp16 lookup tables hold alpha * level: alpha is chosen so that every
@@ -69,6 +70,21 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
     return (a & b) ^ c;  // one LOP3
 }
+// x >> N as the high word of x * 2^(32-N): runs on the multiply-add pipe, which the unpack
+// leaves idle, instead of the half-rate integer/logic pipe that limits this kernel.
+template <int N>
+__device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
+    uint32_t d;
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(d) : "r"(x), "r"(1u << (32 - N)));
+    return d;
+}
+// x << N on the same pipe.
+template <int N>
+__device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
+    uint32_t d;
+    asm("mul.lo.u32 %0, %1, %2;" : "=r"(d) : "r"(x), "r"(1u << N));
+    return d;
+}
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -81,11 +97,6 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
     return d;
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_addr));
 }
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -122,7 +133,7 @@ __device__ __forceinline__ BytePools make_pools(const float (&t)[8]) {
 // half2 registers holding the table values of nibble pairs (0,4) (1,5) (2,6) (3,7).
 __device__ __forceinline__ void lookup8(uint32_t sel, const BytePools& t, uint32_t (&out)[4]) {
     const uint32_t y = prmt(sel, sel, 0x3120u);  // nibbles 0,1,4,5 | 2,3,6,7
-    const uint32_t yh = y >> 16;
+    const uint32_t yh = shr_mul<16>(y);
     const uint32_t h_lo = prmt(t.hi_a, t.hi_b, y), l_lo = prmt(t.lo_a, t.lo_b, y);
     const uint32_t h_hi = prmt(t.hi_a, t.hi_b, yh), l_hi = prmt(t.lo_a, t.lo_b, yh);
     out[0] = prmt(l_lo, h_lo, 0x6240u);
@@ -137,23 +148,52 @@ __device__ __forceinline__ void unpack_k3(uint32_t w, const BytePools& t, uint32
 }
 // Residual sign bits (bit 3 of every nibble) -> +-1.0 halves, same pairing.
 __device__ __forceinline__ void unpack_sign(uint32_t w, uint32_t (&out)[4]) {
-    out[0] = lop3_and_xor(w << 12, 0x80008000u, 0xBC00BC00u);
-    out[1] = lop3_and_xor(w << 8, 0x80008000u, 0xBC00BC00u);
-    out[2] = lop3_and_xor(w << 4, 0x80008000u, 0xBC00BC00u);
+    out[0] = lop3_and_xor(shl_mul<12>(w), 0x80008000u, 0xBC00BC00u);
+    out[1] = lop3_and_xor(shl_mul<8>(w), 0x80008000u, 0xBC00BC00u);
+    out[2] = lop3_and_xor(shl_mul<4>(w), 0x80008000u, 0xBC00BC00u);
     out[3] = lop3_and_xor(w, 0x80008000u, 0xBC00BC00u);
 }
-// 4-bit code n -> cb4[n]: magnitude index is n-8 for n >= 8 and 7-n below, the
-// sign bit is set when bit 3 of the nibble is clear.
+// 4-bit code n -> cb4[n]: magnitude index is n-8 for n >= 8 and 7-n below, the sign bit is
+// set when bit 3 of the nibble is clear.  `neg` gets bit 3 of every negative nibble,
+// `sel` the 3-bit magnitude selectors.
+__device__ __forceinline__ void c4_selectors(uint32_t w, uint32_t& sel, uint32_t& neg) {
+    neg = ~w & 0x88888888u;
+    uint32_t flip;  // 7 in every negative nibble: (neg * 7) >> 3 as one high multiply
+    asm("mul.hi.u32 %0, %1, %2;" : "=r"(flip) : "r"(neg), "r"(0xE0000000u));
+    sel = (w ^ flip) & 0x77777777u;
+}
+// One word of one token: pairs are nibbles (0,4) (1,5) (2,6) (3,7) (K operand of turbo_mse).
 __device__ __forceinline__ void unpack_c4(uint32_t w, const BytePools& mag, uint32_t (&out)[4]) {
-    const uint32_t s = w & 0x88888888u;
-    const uint32_t t = s - (s >> 3);  // 7 in every nibble whose bit 3 is set
-    const uint32_t sel = (w ^ t ^ 0x77777777u) & 0x77777777u;  // one LOP3
+    uint32_t sel, neg;
+    c4_selectors(w, sel, neg);
     lookup8(sel, mag, out);
-    const uint32_t sn = s ^ 0x88888888u;  // bit 3 set where the value is negative
-    out[0] = lop3_and_xor(sn << 12, 0x80008000u, out[0]);
-    out[1] = lop3_and_xor(sn << 8, 0x80008000u, out[1]);
-    out[2] = lop3_and_xor(sn << 4, 0x80008000u, out[2]);
-    out[3] = lop3_and_xor(sn, 0x80008000u, out[3]);
+    out[0] = lop3_and_xor(shl_mul<12>(neg), 0x80008000u, out[0]);
+    out[1] = lop3_and_xor(shl_mul<8>(neg), 0x80008000u, out[1]);
+    out[2] = lop3_and_xor(shl_mul<4>(neg), 0x80008000u, out[2]);
+    out[3] = lop3_and_xor(neg, 0x80008000u, out[3]);
+}
+// The same word of two tokens A and B: out[d] = half2(level of A's nibble d, level of B's
+// nibble d), d = 0..7 -- pairs run along tokens, which is what the k index of the V^T
+// operand needs, so V never goes through a shared-memory transpose.
+__device__ __forceinline__ void unpack_c4_token_pair(uint32_t wa, uint32_t wb, const BytePools& t,
+                                                     uint32_t (&out)[8]) {
+    uint32_t sa, sb, na, nb;
+    c4_selectors(wa, sa, na);
+    c4_selectors(wb, sb, nb);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        // bytes [A.b(2h), B.b(2h), A.b(2h+1), B.b(2h+1)]: 16 selector bits per nibble pair
+        const uint32_t y = prmt(sa, sb, half ? 0x7362u : 0x5140u);
+        const uint32_t yh = shr_mul<16>(y);
+        const uint32_t h0 = prmt(t.hi_a, t.hi_b, y), l0 = prmt(t.lo_a, t.lo_b, y);
+        const uint32_t h1 = prmt(t.hi_a, t.hi_b, yh), l1 = prmt(t.lo_a, t.lo_b, yh);
+        // sign bits of A's nibbles 4h..4h+3 in the low half-word, of B's in the high one
+        const uint32_t z = prmt(na, nb, half ? 0x7632u : 0x5410u);
+        out[4 * half + 0] = lop3_and_xor(shl_mul<12>(z), 0x80008000u, prmt(l0, h0, 0x6240u));
+        out[4 * half + 1] = lop3_and_xor(shl_mul<8>(z), 0x80008000u, prmt(l0, h0, 0x7351u));
+        out[4 * half + 2] = lop3_and_xor(shl_mul<4>(z), 0x80008000u, prmt(l1, h1, 0x6240u));
+        out[4 * half + 3] = lop3_and_xor(z, 0x80008000u, prmt(l1, h1, 0x7351u));
+    }
 }
 
 // Slot of token t of sequence b.
@@ -189,27 +229,36 @@ __device__ __forceinline__ float ld_scale(const uint8_t* p) {
     return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(p))));
 }
 
-// Raw (still packed) data of one 16-token block for one warp.
+__device__ __forceinline__ uint2 ld8(const uint8_t* p, bool aligned) {
+    if (aligned) return __ldg(reinterpret_cast<const uint2*>(p));
+    uint32_t v[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i >> 2] |= static_cast<uint32_t>(p[i]) << (8 * (i & 3));
+    return make_uint2(v[0], v[1]);
+}
+
+// Raw (still packed) data of one 16-token block for one lane (g = lane/4, tig = lane%4).
 struct BlockRaw {
-    uint4 k0, k1;        // K codes of token rows g and g+8, 16-byte chunk tig
-    uint4 v0, v1;        // V codes of token row rv, bytes [32*hb, 32*hb+32)
-    float ks0, ks1, re0, re1, vs0, vs1;
+    uint4 k0, k1;  // K codes of token rows g and g+8, bytes [16 tig, 16 tig + 16)
+    uint2 v[4];    // V codes of token rows 2tig, 2tig+1, 2tig+8, 2tig+9, bytes [8g, 8g+8)
+    float ks0, ks1, re0, re1, vs0, vs1;  // scales of token rows g and g+8
 };
 
 template <bool PROD>
 __device__ __forceinline__ void load_block(const DecodeParams& p, int b, int h, int tb, int t_end,
                                            int lane, bool aligned, BlockRaw& r) {
     const int g = lane >> 2, tig = lane & 3;
-    const int rv = (lane & 7) + 8 * (lane >> 4), hb = (lane >> 3) & 1;
-    const int last = t_end - 1;
-    const int t0 = min(tb + g, last), t1 = min(tb + g + 8, last), tv = min(tb + rv, last);
-    const Cell c0 = token_cell(p, token_slot(p, b, t0), h);
-    const Cell c1 = token_cell(p, token_slot(p, b, t1), h);
-    const Cell cv = token_cell(p, token_slot(p, b, tv), h);
+    const int last = t_end - 1;  // rows past the end re-read the last token (masked later)
+    const Cell c0 = token_cell(p, token_slot(p, b, min(tb + g, last)), h);
+    const Cell c1 = token_cell(p, token_slot(p, b, min(tb + g + 8, last)), h);
     r.k0 = ld16(c0.page + p.geo.k_codes + c0.th * 64 + 16 * tig, aligned);
     r.k1 = ld16(c1.page + p.geo.k_codes + c1.th * 64 + 16 * tig, aligned);
-    r.v0 = ld16(cv.page + p.geo.v_codes + cv.th * 64 + 32 * hb, aligned);
-    r.v1 = ld16(cv.page + p.geo.v_codes + cv.th * 64 + 32 * hb + 16, aligned);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = tb + 2 * tig + (i & 1) + 8 * (i >> 1);
+        const Cell cv = token_cell(p, token_slot(p, b, min(t, last)), h);
+        r.v[i] = ld8(cv.page + p.geo.v_codes + cv.th * 64 + 8 * g, aligned);
+    }
     r.ks0 = ld_scale(c0.page + p.geo.k_scales + c0.th * 2);
     r.ks1 = ld_scale(c1.page + p.geo.k_scales + c1.th * 2);
     r.vs0 = ld_scale(c0.page + p.geo.v_scales + c0.th * 2);
@@ -232,24 +281,22 @@ struct BlockCtx {
     uint32_t qf[8][2];  // B fragments of the rotated, pre-scaled queries
     BytePools pool3, mag4;
     float inv_alpha_v;
-    uint8_t* warp_smem;
-    uint32_t tile_addr;
-    int lane, g, tig, rv, hb, h, H, nq, gq0;
+    uint8_t* warp_smem;   // per-warp shared region (merge record at the end; fast path: ring)
+    uint32_t warp_smem_addr;
+    int lane, g, tig, h, H, nq, gq0;
 };
 
-// One 16-token block for one kv head: QK^T (+ residual-sign product), online softmax,
-// V unpack into the shared tile, PV.  MODE 1 writes logits instead.
+// One 16-token block for one kv head: QK^T (+ residual-sign product), online softmax, PV.
+// MODE 1 writes logits instead.
 template <bool PROD, int MODE>
 __device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
                                               const BlockRaw& cur, int tb, int t_end,
                                               WarpState& st) {
-    const int g = c.g, tig = c.tig, lane = c.lane, rv = c.rv, hb = c.hb, h = c.h, H = c.H;
+    const int g = c.g, tig = c.tig, h = c.h, H = c.H;
     const int nq = c.nq, gq0 = c.gq0;
     const BytePools& pool3 = c.pool3;
     const BytePools& mag4 = c.mag4;
     const float inv_alpha_v = c.inv_alpha_v;
-    uint8_t* warp_smem = c.warp_smem;
-    const uint32_t tile_addr = c.tile_addr;
     float (&o)[8][4] = st.o;
     float (&m_run)[2] = st.m_run;
     float (&l_run)[2] = st.l_run;
@@ -305,8 +352,10 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         return;
     }
 
-    if (!ok0) lg[0] = lg[1] = -INFINITY;
-    if (!ok1) lg[2] = lg[3] = -INFINITY;
+    if (tb + 16 > t_end) {  // only the last block of a sequence can be ragged
+        if (!ok0) lg[0] = lg[1] = -INFINITY;
+        if (!ok1) lg[2] = lg[3] = -INFINITY;
+    }
 
     // ---- online softmax over the 16 tokens of the block ---------------------
     float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
@@ -337,31 +386,16 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * w0, p1 * w0));
     const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
 
-    // ---- V: unpack this lane's 64 codes into the swizzled tile ---------------
-    const uint32_t vw[8] = {cur.v0.x, cur.v0.y, cur.v0.z, cur.v0.w,
-                            cur.v1.x, cur.v1.y, cur.v1.z, cur.v1.w};
+    // ---- O^T += V^T P^T: A = V^T (rows = this lane's dims 16g + 2j + {0,1}, k = tokens) ----
 #pragma unroll
-    for (int wi = 0; wi < 8; ++wi) {
-        uint32_t a[4];
-        unpack_c4(vw[wi], mag4, a);
-        const int unit = 8 * hb + wi;
-        *reinterpret_cast<uint4*>(warp_smem + rv * 256 + ((unit ^ (rv & 7)) << 4)) =
-            make_uint4(a[0], a[1], a[2], a[3]);
-    }
-    __syncwarp();
-    // ---- O^T += V^T P^T -------------------------------------------------------
-    {
-        const int mat = lane >> 3;
-        const int tok = (lane & 7) + 8 * (mat >> 1);
+    for (int i = 0; i < 2; ++i) {
+        uint32_t ab[8], cd[8];
+        unpack_c4_token_pair(i ? cur.v[0].y : cur.v[0].x, i ? cur.v[1].y : cur.v[1].x, mag4, ab);
+        unpack_c4_token_pair(i ? cur.v[2].y : cur.v[2].x, i ? cur.v[3].y : cur.v[3].x, mag4, cd);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int unit = 2 * j + (mat & 1);
-            uint32_t a[4];
-            ldmatrix_x4_trans(a, tile_addr + tok * 256 + ((unit ^ (tok & 7)) << 4));
-            mma16816(o[j], a[0], a[1], a[2], a[3], pb0, pb1);
-        }
+        for (int dd = 0; dd < 4; ++dd)
+            mma16816(o[4 * i + dd], ab[2 * dd], ab[2 * dd + 1], cd[2 * dd], cd[2 * dd + 1], pb0, pb1);
     }
-    __syncwarp();
 }
 
 // Per-CTA geometry shared by both kernels.
@@ -446,12 +480,10 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     ctx.mag4 = make_pools(t4);
     ctx.inv_alpha_v = 1.0f / TQ_ALPHA4;
     ctx.warp_smem = warp_smem;
-    ctx.tile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
+    ctx.warp_smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
     ctx.lane = lane;
     ctx.g = g;
     ctx.tig = tig;
-    ctx.rv = (lane & 7) + 8 * (lane >> 4);
-    ctx.hb = (lane >> 3) & 1;
     ctx.h = h;
     ctx.H = H;
     ctx.nq = nq;
@@ -529,11 +561,9 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* 
         float* row = out + static_cast<long long>(h * r.G + c.gq0 + col) * TQ_PARTIAL_STRIDE;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            // accumulator rows g (unit 2j) and g+8 (unit 2j+1); position g of a unit is
-            // dim (g>>1) + 4*(g&1)
-            const int d = (g >> 1) + 4 * (g & 1);
-            row[16 * j + d] = o[j][e];
-            row[16 * j + 8 + d] = o[j][2 + e];
+            // accumulator rows g and g+8 of tile j are dims 16g + 2j and 16g + 2j + 1
+            row[16 * g + 2 * j] = o[j][e];
+            row[16 * g + 2 * j + 1] = o[j][2 + e];
         }
         if (g == 0) {
             row[128] = m_run[e] * kLn2;
@@ -573,18 +603,23 @@ decode_kernel(DecodeParams p) {
 }
 
 // ---- paged fast path ----------------------------------------------------------------
-// Block tables with 16-token pages, 16-byte aligned pool: a 16-token block IS a page, so
-// every lane's source offsets inside the page are loop constants.  Code bytes and scales
-// travel global -> shared with cp.async (no registers held while in flight) into a
+// Block tables with 16-token pages, 16-byte aligned pool, H in {1,2,4,8}: a 16-token block IS
+// a page, so every lane's source offsets inside the page are loop constants (and, with H a
+// template argument, the distances between a lane's rows are immediates).  Code bytes and
+// scales travel global -> shared with cp.async (no registers held while in flight) into a
 // per-warp ring of kStages stages; cp.async.wait_group paces the consumer.
 constexpr int kStages = 3;
-constexpr int kStageCodeBytes = 4 * 32 * 16;   // 4 sixteen-byte chunks per lane
-constexpr int kStageScaleBytes = 3 * 32 * 8;   // three regions of 16*H fp16, H <= 8
+constexpr int kStageCodeBytes = 2 * 32 * 16 + 4 * 32 * 8;  // K: 2 x 16 B, V: 4 x 8 B per lane
+constexpr int kStageScaleBytes = 3 * 256;                   // three regions of 16*H fp16, H <= 8
 constexpr int kStageBytes = kStageCodeBytes + kStageScaleBytes;
-constexpr int kFastWarpBytes = kWarpSmemBytes + kStages * kStageBytes;
+constexpr int kFastWarpBytes = kStages * kStageBytes;       // 8448 >= kWarpSmemBytes (merge record)
+static_assert(kFastWarpBytes >= kWarpSmemBytes, "the merge record reuses the ring");
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -592,100 +627,107 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <bool PROD>
+template <bool PROD, int H>
 __global__ void __launch_bounds__(256, 2)
 decode_paged16_kernel(DecodeParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    constexpr int kStreams = 8 / H;
     BlockCtx ctx;
     CtaRange r;
     decode_prologue<PROD, 0>(p, smem_raw, kFastWarpBytes, ctx, r);
     WarpState st;
     init_state(st);
-    const int lane = ctx.lane, g = ctx.g, tig = ctx.tig, h = ctx.h, H = ctx.H;
+    const int lane = ctx.lane, g = ctx.g, tig = ctx.tig, h = ctx.h;
 
-    uint8_t* ring = ctx.warp_smem + kWarpSmemBytes;
-    const uint32_t ring_addr = ctx.tile_addr + kWarpSmemBytes;
+    uint8_t* ring = ctx.warp_smem;
+    const uint32_t ring_addr = ctx.warp_smem_addr;
     // loop-constant source offsets inside a page
-    const uint32_t k_off0 = p.geo.k_codes + ((g * H + h) << 6) + (tig << 4);
-    const uint32_t k_off1 = k_off0 + (H << 9);
-    const uint32_t v_off = p.geo.v_codes + ((ctx.rv * H + h) << 6) + (ctx.hb << 5);
+    const uint32_t k_off = p.geo.k_codes + ((g * H + h) << 6) + (tig << 4);          // row g; row g+8: +512H
+    const uint32_t v_off = p.geo.v_codes + ((2 * tig * H + h) << 6) + (g << 3);      // row 2tig
     // scale regions (16*H fp16 each) are copied in 16-byte pieces spread over the lanes
-    const int pieces_per_region = 2 * H;
-    const int n_regions = PROD ? 3 : 2;
+    constexpr int kPiecesPerRegion = 2 * H;
+    constexpr int kRegions = PROD ? 3 : 2;
     uint32_t sc_src[2], sc_dst[2];
     bool sc_on[2];
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         const int i = lane + 32 * k;
-        const int reg = i / pieces_per_region, j = i - reg * pieces_per_region;
-        sc_on[k] = reg < n_regions;
+        const int reg = i / kPiecesPerRegion, j = i - reg * kPiecesPerRegion;
+        sc_on[k] = reg < kRegions;
         const uint32_t base = reg == 0 ? p.geo.k_scales : (reg == 1 ? p.geo.v_scales : p.geo.k_res);
         sc_src[k] = base + 16 * j;
         sc_dst[k] = kStageCodeBytes + reg * 256 + 16 * j;
     }
-    // where this lane's scales sit inside a stage (bytes)
-    const uint32_t s_idx0 = 2 * (g * H + h), s_idx1 = s_idx0 + 16 * H;
+    const uint32_t s_idx = 2 * (g * H + h);  // this lane's row-g scale inside a region; row g+8: +16H
 
-    const int page0 = r.t_begin >> 4;
-    const int32_t* table = p.block_tables + static_cast<long long>(r.b) * p.table_stride + page0;
+    const int32_t* table = p.block_tables + static_cast<long long>(r.b) * p.table_stride +
+                           (r.t_begin >> 4) + r.blk_lo + r.stream;
     const int n_iter = r.blk_hi > r.blk_lo + r.stream
-                           ? (r.blk_hi - r.blk_lo - r.stream + p.streams - 1) / p.streams : 0;
+                           ? (r.blk_hi - r.blk_lo - r.stream + kStreams - 1) / kStreams : 0;
 
     // page ids of 32 consecutive iterations, one per lane
     int ids = 0, ids_base = 0;
     auto refill = [&](int it0) {
         const int it = it0 + lane;
-        ids = it < n_iter ? __ldg(table + r.blk_lo + r.stream + it * p.streams) : 0;
+        ids = it < n_iter ? __ldg(table + it * kStreams) : 0;
         ids_base = it0;
     };
-    auto issue = [&](int it) {
+    auto issue = [&](int it, uint32_t dst) {
         if (it < n_iter) {
             if (it - ids_base >= 32) refill(it);
             const int page = __shfl_sync(0xffffffffu, ids, it - ids_base);
             const uint8_t* src = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
-            const uint32_t dst = ring_addr + (it % kStages) * kStageBytes;
-            cp_async16(dst + (0 * 32 + lane) * 16, src + k_off0);
-            cp_async16(dst + (1 * 32 + lane) * 16, src + k_off1);
-            cp_async16(dst + (2 * 32 + lane) * 16, src + v_off);
-            cp_async16(dst + (3 * 32 + lane) * 16, src + v_off + 16);
+            const uint8_t* ks = src + k_off;
+            const uint8_t* vs = src + v_off;
+            cp_async16(dst + lane * 16, ks);
+            cp_async16(dst + 512 + lane * 16, ks + 512 * H);
+            cp_async8(dst + 1024 + lane * 8, vs);
+            cp_async8(dst + 1280 + lane * 8, vs + 64 * H);
+            cp_async8(dst + 1536 + lane * 8, vs + 512 * H);
+            cp_async8(dst + 1792 + lane * 8, vs + 576 * H);
             if (sc_on[0]) cp_async16(dst + sc_dst[0], src + sc_src[0]);
-            if (sc_on[1]) cp_async16(dst + sc_dst[1], src + sc_src[1]);
+            if (kRegions * kPiecesPerRegion > 32 && sc_on[1]) cp_async16(dst + sc_dst[1], src + sc_src[1]);
         }
         cp_async_commit();  // one group per iteration, empty or not, keeps the count uniform
     };
 
     refill(0);
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue(s);
+    for (int s = 0; s < kStages - 1; ++s) issue(s, ring_addr + s * kStageBytes);
 
+    int stage = 0;  // stage holding iteration `it`
     for (int it = 0; it < n_iter; ++it) {
-        issue(it + kStages - 1);
+        const int fill = stage == 0 ? kStages - 1 : stage - 1;  // (it + kStages - 1) % kStages
+        issue(it + kStages - 1, ring_addr + fill * kStageBytes);
         cp_async_wait<kStages - 1>();
         __syncwarp();  // scale pieces are copied by other lanes
-        const uint8_t* stg = ring + (it % kStages) * kStageBytes;
-        const int blk = r.blk_lo + r.stream + it * p.streams;
-        const int tb = r.t_begin + 16 * blk;
+        const uint8_t* stg = ring + stage * kStageBytes;
+        const int tb = r.t_begin + 16 * (r.blk_lo + r.stream + it * kStreams);
         BlockRaw cur;
-        cur.k0 = *reinterpret_cast<const uint4*>(stg + (0 * 32 + lane) * 16);
-        cur.k1 = *reinterpret_cast<const uint4*>(stg + (1 * 32 + lane) * 16);
-        cur.v0 = *reinterpret_cast<const uint4*>(stg + (2 * 32 + lane) * 16);
-        cur.v1 = *reinterpret_cast<const uint4*>(stg + (3 * 32 + lane) * 16);
-        const uint8_t* sc = stg + kStageCodeBytes;
-        // rows past the end of the sequence may hold anything: zero their scales so that
-        // P * vs stays finite (their logits are masked to -inf separately)
-        const bool ok0 = tb + g < r.t_end, ok1 = tb + g + 8 < r.t_end;
-        auto ld = [&](uint32_t off, bool ok) {
-            const float v = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sc + off)));
-            return ok ? v : 0.0f;
+        cur.k0 = *reinterpret_cast<const uint4*>(stg + lane * 16);
+        cur.k1 = *reinterpret_cast<const uint4*>(stg + 512 + lane * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            cur.v[i] = *reinterpret_cast<const uint2*>(stg + 1024 + 256 * i + lane * 8);
+        const uint8_t* sc = stg + kStageCodeBytes + s_idx;
+        auto ld = [&](uint32_t off) {
+            return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sc + off)));
         };
-        cur.ks0 = ld(s_idx0, ok0);
-        cur.ks1 = ld(s_idx1, ok1);
-        cur.vs0 = ld(256 + s_idx0, ok0);
-        cur.vs1 = ld(256 + s_idx1, ok1);
-        cur.re0 = PROD ? ld(512 + s_idx0, ok0) : 0.0f;
-        cur.re1 = PROD ? ld(512 + s_idx1, ok1) : 0.0f;
+        cur.ks0 = ld(0);
+        cur.ks1 = ld(16 * H);
+        cur.vs0 = ld(256);
+        cur.vs1 = ld(256 + 16 * H);
+        cur.re0 = PROD ? ld(512) : 0.0f;
+        cur.re1 = PROD ? ld(512 + 16 * H) : 0.0f;
+        if (tb + 16 > r.t_end) {
+            // rows past the end of the sequence may hold anything: zero their scales so that
+            // P * vs stays finite (their logits are masked to -inf in process_block)
+            if (tb + g >= r.t_end) cur.ks0 = cur.vs0 = cur.re0 = 0.0f;
+            if (tb + g + 8 >= r.t_end) cur.ks1 = cur.vs1 = cur.re1 = 0.0f;
+        }
         process_block<PROD, 0>(p, ctx, cur, tb, r.t_end, st);
-        // process_block ends with __syncwarp: every lane is done with this stage
+        __syncwarp();  // every lane is done reading this stage before it is refilled
+        stage = stage == kStages - 1 ? 0 : stage + 1;
     }
     cp_async_wait<0>();
     decode_epilogue(p, smem_raw, kFastWarpBytes, ctx, r, st);
@@ -767,10 +809,13 @@ void set_smem_attr_once() {
     check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     const int fast_bytes = 8 * kFastWarpBytes + kMaxHeads * 8 * kHeadDim * 2;
-    check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), "smem attr");
-    check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), "smem attr");
+#define TQ_FAST_ATTR(PRODV, HV)                                                               \
+    check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<PRODV, HV>,                         \
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), \
+               "smem attr")
+    TQ_FAST_ATTR(true, 1); TQ_FAST_ATTR(true, 2); TQ_FAST_ATTR(true, 4); TQ_FAST_ATTR(true, 8);
+    TQ_FAST_ATTR(false, 1); TQ_FAST_ATTR(false, 2); TQ_FAST_ATTR(false, 4); TQ_FAST_ATTR(false, 8);
+#undef TQ_FAST_ATTR
     done[dev] = true;
 }
 
@@ -872,14 +917,24 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 
     const dim3 grid(splits, a.batch, qgroups);
     const bool fast = a.block_tables && !a.slot_mapping && a.geo.block_size == 16 && p.aligned16 &&
-                      warps <= 8 && (a.geo.k_scales & 15) == 0 && (a.geo.v_scales & 15) == 0 &&
-                      (!prod || (a.geo.k_res & 15) == 0) && a.kv_begin >= 0 && (a.kv_begin & 15) == 0;
+                      (H == 1 || H == 2 || H == 4 || H == 8) && (a.geo.k_scales & 15) == 0 &&
+                      (a.geo.v_scales & 15) == 0 && (!prod || (a.geo.k_res & 15) == 0) &&
+                      a.kv_begin >= 0 && (a.kv_begin & 15) == 0;
     if (fast) {
         const size_t fsmem = static_cast<size_t>(warps) * kFastWarpBytes + H * 8 * kHeadDim * sizeof(__half);
-        if (prod)
-            decode_paged16_kernel<true><<<grid, warps * 32, fsmem, stream>>>(p);
-        else
-            decode_paged16_kernel<false><<<grid, warps * 32, fsmem, stream>>>(p);
+#define TQ_FAST_LAUNCH(PRODV, HV) decode_paged16_kernel<PRODV, HV><<<grid, 256, fsmem, stream>>>(p)
+        if (prod) {
+            if (H == 1) TQ_FAST_LAUNCH(true, 1);
+            else if (H == 2) TQ_FAST_LAUNCH(true, 2);
+            else if (H == 4) TQ_FAST_LAUNCH(true, 4);
+            else TQ_FAST_LAUNCH(true, 8);
+        } else {
+            if (H == 1) TQ_FAST_LAUNCH(false, 1);
+            else if (H == 2) TQ_FAST_LAUNCH(false, 2);
+            else if (H == 4) TQ_FAST_LAUNCH(false, 4);
+            else TQ_FAST_LAUNCH(false, 8);
+        }
+#undef TQ_FAST_LAUNCH
     } else if (prod) {
         decode_kernel<true, 0><<<grid, warps * 32, smem, stream>>>(p);
     } else {

@@ -34,21 +34,21 @@ __device__ __forceinline__ uint2 load_codes(const uint8_t* p, bool aligned8) {
 }
 
 // Inverse rotation of 16 rotated-domain values per lane and fp16 store.
-__device__ __forceinline__ void inverse_and_store(float (&x)[16], float* buf, int lane, float c,
+__device__ __forceinline__ void inverse_and_store(float2 (&x)[8], float* buf, int lane, float c,
                                                   int h, __half* dst_row, bool valid) {
-    float y[16];
+    float2 y[8];
     fwht_phase1(x);
     redeal(x, y, buf, lane);
     fwht_phase2(y);
     const int l = lane & 7;
-    // element 2l+b+16j has sign +1 iff (b+h) is even
-    const float s0 = (h & 1) ? -1.0f : 1.0f;
+    // element 2l+b+16j has sign +1 iff (b+h) is even; (y*c)*s == y*(c*s) exactly
+    const float s0 = (h & 1) ? -c : c;
+    const float2 cs = make_float2(s0, -s0);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        const float a = __fmul_rn(__fmul_rn(y[2 * j], c), s0);
-        const float b = __fmul_rn(__fmul_rn(y[2 * j + 1], c), -s0);
+        const float2 v = mul2(y[j], cs);
         if (valid)
-            *reinterpret_cast<__half2*>(dst_row + 2 * l + 16 * j) = __floats2half2_rn(a, b);
+            *reinterpret_cast<__half2*>(dst_row + 2 * l + 16 * j) = __floats2half2_rn(v.x, v.y);
     }
 }
 
@@ -95,29 +95,26 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         if (PROD) re = __half2float(*reinterpret_cast<const __half*>(page + geo.k_res + th * 2));
 
         const long long out_row = hnd ? (static_cast<long long>(h) * num_tokens + tok) : row;
-        float x[16];
+        float2 x[8];
+        auto level_k = [&](uint32_t nib) {
+            if (PROD) return __fadd_rn(lut3[(nib & 7u) * 32 + lane], (nib & 8u) ? re : -re);
+            return lut4[nib * 32 + lane];
+        };
 
         // K: rotated-domain values (tq_turbo_prod_kernels.cu:315-330 /
         // tq_turbo_mse_kernels.cu:150-156)
+        const float2 ks2 = make_float2(ks, ks), vs2 = make_float2(vs, vs);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const uint32_t w = e < 8 ? kc.x : kc.y;
-            const uint32_t nib = (w >> (4 * (e & 7))) & 0xFu;
-            if (PROD) {
-                const float lvl = lut3[(nib & 7u) * 32 + lane];
-                const float kval = __fadd_rn(lvl, (nib & 8u) ? re : -re);
-                x[e] = __fmul_rn(kval, ks);
-            } else {
-                x[e] = __fmul_rn(lut4[nib * 32 + lane], ks);
-            }
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t b8 = ((k < 4 ? kc.x : kc.y) >> (8 * (k & 3))) & 0xFFu;
+            x[k] = mul2(make_float2(level_k(b8 & 0xFu), level_k(b8 >> 4)), ks2);
         }
         inverse_and_store(x, buf, lane, c, h, out_key + out_row * kHeadDim, valid);
 
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const uint32_t w = e < 8 ? vc.x : vc.y;
-            const uint32_t nib = (w >> (4 * (e & 7))) & 0xFu;
-            x[e] = __fmul_rn(lut4[nib * 32 + lane], vs);
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t b8 = ((k < 4 ? vc.x : vc.y) >> (8 * (k & 3))) & 0xFFu;
+            x[k] = mul2(make_float2(lut4[(b8 & 0xFu) * 32 + lane], lut4[(b8 >> 4) * 32 + lane]), vs2);
         }
         inverse_and_store(x, buf, lane, c, h, out_value + out_row * kHeadDim, valid);
     }

@@ -76,34 +76,34 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
         const unsigned int th = static_cast<unsigned int>(tib * H + h);
 
-        float x[16], y[16];
+        float2 x[8], y[8];
 
         // ---------------- K ----------------
         fwht_phase1_from_half(k_lo, k_hi, x);
         redeal(x, y, buf, lane);
         fwht_phase2(y);
+        const float2 cs2 = make_float2(cs, cs);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(y[i], cs);
+        for (int j = 0; j < 8; ++j) y[j] = mul2(y[j], cs2);
 
         uint32_t kbytes[8];
         if (PROD) {
-            float sq[16];
+            float2 sq[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sq[i] = __fmul_rn(y[i], y[i]);
+            for (int j = 0; j < 8; ++j) sq[j] = mul2(y[j], y[j]);
             const float krms = rms_from_sum(tree128(sq));
             const float kr = __frcp_rn(krms);
-            float e2[16];
+            float2 e2[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 float e0, e1;
-                float kn0 = div_by(y[2 * j], krms, kr);
-                float kn1 = div_by(y[2 * j + 1], krms, kr);
-                kn0 = kn0 < -2.5f ? -2.5f : (kn0 > 2.5f ? 2.5f : kn0);
-                kn1 = kn1 < -2.5f ? -2.5f : (kn1 > 2.5f ? 2.5f : kn1);
+                const float2 kn = div_by2(y[j], krms, kr);
+                const float kn0 = kn.x < -2.5f ? -2.5f : (kn.x > 2.5f ? 2.5f : kn.x);
+                const float kn1 = kn.y < -2.5f ? -2.5f : (kn.y > 2.5f ? 2.5f : kn.y);
                 const uint32_t n0 = quant_k3(kn0, e0), n1 = quant_k3(kn1, e1);
                 kbytes[j] = n0 | (n1 << 4);
-                e2[2 * j] = __fmul_rn(e0, e0);
-                e2[2 * j + 1] = __fmul_rn(e1, e1);
+                const float2 e = make_float2(e0, e1);
+                e2[j] = mul2(e, e);
             }
             const float rms_e = rms_from_sum(tree128(e2));
             if (valid && l == 0) {
@@ -114,14 +114,13 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             float pr[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                pr[j] = __fmaf_rn(y[2 * j], y[2 * j], __fmul_rn(y[2 * j + 1], y[2 * j + 1]));
+                pr[j] = __fmaf_rn(y[j].x, y[j].x, __fmul_rn(y[j].y, y[j].y));
             const float krms = rms_from_sum(tree64(pr));
             const float kr = __frcp_rn(krms);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const uint32_t n0 = quant_v4(div_by(y[2 * j], krms, kr));
-                const uint32_t n1 = quant_v4(div_by(y[2 * j + 1], krms, kr));
-                kbytes[j] = n0 | (n1 << 4);
+                const float2 kn = div_by2(y[j], krms, kr);
+                kbytes[j] = quant_v4(kn.x) | (quant_v4(kn.y) << 4);
             }
             if (valid && l == 0)
                 *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
@@ -134,27 +133,26 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         redeal(x, y, buf, lane);
         fwht_phase2(y);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) y[i] = __fmul_rn(y[i], cs);
+        for (int j = 0; j < 8; ++j) y[j] = mul2(y[j], cs2);
         float vrms;
         if (PROD) {
-            float sq[16];
+            float2 sq[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sq[i] = __fmul_rn(y[i], y[i]);
+            for (int j = 0; j < 8; ++j) sq[j] = mul2(y[j], y[j]);
             vrms = rms_from_sum(tree128(sq));
         } else {
             float pr[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                pr[j] = __fmaf_rn(y[2 * j], y[2 * j], __fmul_rn(y[2 * j + 1], y[2 * j + 1]));
+                pr[j] = __fmaf_rn(y[j].x, y[j].x, __fmul_rn(y[j].y, y[j].y));
             vrms = rms_from_sum(tree64(pr));
         }
         const float vr = __frcp_rn(vrms);
         uint32_t vbytes[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const uint32_t n0 = quant_v4(div_by(y[2 * j], vrms, vr));
-            const uint32_t n1 = quant_v4(div_by(y[2 * j + 1], vrms, vr));
-            vbytes[j] = n0 | (n1 << 4);
+            const float2 vn = div_by2(y[j], vrms, vr);
+            vbytes[j] = quant_v4(vn.x) | (quant_v4(vn.y) << 4);
         }
         if (valid && l == 0)
             *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
