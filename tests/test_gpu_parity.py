@@ -392,3 +392,41 @@ def test_decode_workspace_argument(tq, oracle, dev):
         tq.decode_paged(*args, max_kv_tokens=900, workspace=ws[:128])
     with pytest.raises(RuntimeError, match="narrower"):
         tq.decode_paged(*args, max_kv_tokens=16 * tables.shape[1] + 1)
+
+
+# ---------------------------------------------------------------------------------
+# chunked query prefill over a turbo_mse prefix + causal fp16 chunk
+# ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("hq,h,nq,lens,with_chunk", [
+    (16, 2, 1, [100, 37], True), (16, 2, 20, [333, 64], True), (16, 2, 70, [1000], True),
+    (8, 4, 33, [129, 5], True), (16, 2, 24, [500, 17], False), (4, 2, 130, [64], True),
+    (8, 8, 9, [40], True), (16, 2, 16, [0, 50], True)])
+def test_mse_prefill_vs_oracle(tq, oracle, dev, hq, h, nq, lens, with_chunk):
+    rng = np.random.default_rng(1000 * nq + sum(lens) + hq)
+    pool, tables = build_paged(oracle, "turbo_mse", rng, lens, h)
+    b = len(lens)
+    query = rng.standard_normal((b, nq, hq, 128)).astype(np.float16)
+    ck = rng.standard_normal((b, nq, h, 128)).astype(np.float16) if with_chunk else None
+    cv = rng.standard_normal((b, nq, h, 128)).astype(np.float16) if with_chunk else None
+    if with_chunk:
+        ck[:, :, :, [3, 17]] *= 8
+    cfg, ocfg = cfg_for(tq, h), oracle.make_config(h)
+    lay = tq.make_mse_layout_for(cfg)
+    out = torch.full((b, nq, hq, 128), 3.0, dtype=torch.float16, device=dev)
+    tq.mse_prefill_paged(h16(query, dev), torch.from_numpy(pool).to(dev), torch.from_numpy(tables).to(dev),
+                         torch.tensor(lens, dtype=torch.int32, device=dev),
+                         None if ck is None else h16(ck, dev), None if cv is None else h16(cv, dev),
+                         out, lay, cfg)
+    torch.cuda.synchronize()
+    mine = out.cpu().numpy()
+    for i, n in enumerate(lens):
+        t = np.arange(n)
+        slots = (tables[i][t // 16] * 16 + t % 16).astype(np.int32)
+        if n == 0 and not with_chunk:
+            continue
+        ref = oracle.mse_prefill(query[i], pool, slots, None if ck is None else ck[i],
+                                 None if cv is None else cv[i], ocfg)
+        err = rowwise_rel_err(mine[i], ref)
+        print(f"prefill b={i} n={n} nq={nq}: rel err {err:.2e}")
+        assert err < ATTN_TOL

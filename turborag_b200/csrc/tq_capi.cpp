@@ -393,12 +393,30 @@ extern "C" int tq_dequant_kv_hnd(int scheme, const uint8_t* page_pool, const int
     });
 }
 
-extern "C" int tq_mse_prefill_paged(const tq_half*, const uint8_t*, const int32_t*, int,
-                                    const int32_t*, const tq_half*, const tq_half*, tq_half*,
-                                    const TQTurbomsePageLayout*, const TQConfig*, int, int, int,
-                                    tq_stream_t) {
-    set_error("tq_mse_prefill_paged: not built yet");
-    return -2;
+extern "C" int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_pool,
+                                    const int32_t* block_tables, int table_stride,
+                                    const int32_t* seq_lens, const tq_half* chunk_key,
+                                    const tq_half* chunk_value, tq_half* output,
+                                    const TQTurbomsePageLayout* layout, const TQConfig* cfg,
+                                    int batch, int num_q_tokens, int num_q_heads,
+                                    tq_stream_t stream) {
+    if (!query || !page_pool || !block_tables || !seq_lens || !output || !layout || !cfg) return -1;
+    if ((chunk_key == nullptr) != (chunk_value == nullptr)) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "mse_prefill_paged");
+        check_align(query, 8, "query");
+        check_align(output, 4, "output");
+        if (chunk_key) {
+            check_align(chunk_key, 8, "chunk_key");
+            check_align(chunk_value, 8, "chunk_value");
+        }
+        if (batch < 0 || num_q_tokens < 0 || num_q_heads < 1 || table_stride < 0)
+            throw std::runtime_error("mse_prefill_paged: negative size");
+        if (cfg->num_kv_heads > 8) throw std::runtime_error("mse_prefill_paged: num_kv_heads must be 1..8");
+        tq::launch_prefill(query, page_pool, block_tables, table_stride, seq_lens, chunk_key, chunk_value,
+                           output, geom_mse(*layout, *cfg), cfg->head_dim, batch, num_q_tokens,
+                           num_q_heads, table_stride * cfg->block_size, static_cast<cudaStream_t>(stream));
+    });
 }
 
 // ---- host page allocator + block table -------------------------------------

@@ -87,7 +87,7 @@ __device__ __forceinline__ uint32_t shl_mul(uint32_t x) {
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -302,7 +302,9 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     float (&l_run)[2] = st.l_run;
     const uint32_t (&qf)[8][2] = c.qf;
     // ---- S = K_hat Q'^T (rows = tokens g, g+8; cols = queries 2tig, 2tig+1) ----
+    // two independent accumulators per product: halves the dependent HMMA chains
     float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+    float s1b[4] = {0.f, 0.f, 0.f, 0.f}, s2b[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
     const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
 #pragma unroll
@@ -316,13 +318,18 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             unpack_c4(kw1[wi], mag4, bq);
         }
         mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-        mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+        mma16816(s1b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
         if (PROD) {
             unpack_sign(kw0[wi], a);
             unpack_sign(kw1[wi], bq);
             mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-            mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+            mma16816(s2b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
         }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        s1[e] += s1b[e];
+        s2[e] += s2b[e];
     }
     const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
     float lg[4];
@@ -627,8 +634,11 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+#ifndef TQ_FAST_CTAS
+#define TQ_FAST_CTAS 2
+#endif
 template <bool PROD, int H>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, TQ_FAST_CTAS)
 decode_paged16_kernel(DecodeParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int kStreams = 8 / H;
@@ -849,6 +859,16 @@ void launch_merge(const float* partials, int num_parts, void* output, float* par
         num_q_heads, static_cast<__half*>(output), partials_out, rows, num_q_heads, num_kv_heads,
         ref_query_layout, head_dim);
     check_launch("merge_partials");
+}
+
+void launch_merge_splits(const float* partials, int splits, void* output, int rows, int num_q_heads,
+                         int num_kv_heads, int head_dim, cudaStream_t stream) {
+    if (rows <= 0) return;
+    const long long part_stride = static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE;
+    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(partials, splits, part_stride, part_stride * splits,
+                                                   num_q_heads, static_cast<__half*>(output), nullptr,
+                                                   rows, num_q_heads, num_kv_heads, 0, head_dim);
+    check_launch("merge splits");
 }
 
 void launch_decode(const DecodeArgs& a, cudaStream_t stream) {

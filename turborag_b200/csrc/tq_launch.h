@@ -61,4 +61,14 @@ void launch_merge(const float* partials, int num_parts, void* output, float* par
                   int rows, int num_q_heads, int num_kv_heads, int ref_query_layout,
                   int head_dim, cudaStream_t stream);
 
+// Merge of split partials laid out [sequence][split][num_q_heads][130] (what the decode and
+// prefill kernels write), rows = sequences * num_q_heads.
+void launch_merge_splits(const float* partials, int splits, void* output, int rows, int num_q_heads,
+                         int num_kv_heads, int head_dim, cudaStream_t stream);
+
+void launch_prefill(const void* query, const uint8_t* pool, const int32_t* block_tables,
+                    int table_stride, const int32_t* seq_lens, const void* chunk_key,
+                    const void* chunk_value, void* output, const PageGeom& geo, int head_dim,
+                    int batch, int nq, int hq, int max_prefix_tokens, cudaStream_t stream);
+
 }  // namespace tq
