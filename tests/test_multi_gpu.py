@@ -1,0 +1,82 @@
+"""KV-sequence split across GPUs: every rank decodes its page-aligned token range of every
+sequence, ONE NCCL all-gather brings the (acc, m, l) partials into local memory and the local
+merge kernel finishes (turborag_b200.parallel.decode_kv_split).  Needs >= 2 GPUs; skipped on a
+single-GPU box (the host-side logic is covered on CPU ranks by test_kv_split_gloo.py)."""
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import os
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import torch.distributed as dist
+
+    import turborag_b200
+    from oracle import oracle as O
+    from tests.golden.cases import make_kv
+    from turborag_b200.parallel import decode_kv_split
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        tq = turborag_b200.TurboQuantWrapper()
+        rng = np.random.default_rng(77)  # identical data on every rank
+        lens, hq, h = [3000, 1234], 28, 4
+        res = {}
+        for scheme in ("turbo_prod", "turbo_mse"):
+            ocfg = O.make_config(h)
+            lay_o = O.layout_for(scheme, ocfg)
+            maxpages = (max(lens) + 15) // 16
+            total = len(lens) * maxpages + 1
+            tables = rng.permutation(total).astype(np.int32)[:len(lens) * maxpages].reshape(len(lens), maxpages)
+            pool = np.zeros(total * lay_o.page_size_bytes, np.uint8)
+            for i, n in enumerate(lens):
+                k, v = make_kv(rng, n, h)
+                t = np.arange(n)
+                O.pack(scheme, k, v, (tables[i][t // 16] * 16 + t % 16).astype(np.int32), ocfg, pool=pool)
+            query = rng.standard_normal((len(lens), hq, 128)).astype(np.float16)
+            cfg = tq.default_config()
+            cfg.num_kv_heads = h
+            lay = tq.layout_for_scheme(scheme, cfg)
+            out = torch.zeros(len(lens), hq, 128, dtype=torch.float16, device=dev)
+            decode_kv_split(tq, scheme, torch.from_numpy(query.view(np.int16)).to(dev).view(torch.float16),
+                            torch.from_numpy(pool).to(dev), torch.from_numpy(tables).to(dev),
+                            torch.tensor(lens, dtype=torch.int32, device=dev), lay, cfg,
+                            max_kv_tokens=max(lens), output=out)
+            torch.cuda.synchronize()
+            ref = O.decode_paged(scheme, query, pool, tables, lens, ocfg).astype(np.float32)
+            got = out.cpu().numpy().astype(np.float32)
+            res[scheme] = float((np.abs(got - ref).max(-1) / np.abs(ref).max(-1)).max())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, res)
+        if rank == 0:
+            q.put(gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_split_across_gpus():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + int(np.random.default_rng().integers(0, 2000))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in res:
+        assert r["turbo_prod"] < 2e-3 and r["turbo_mse"] < 2e-3, res
