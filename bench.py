@@ -1,7 +1,9 @@
 """Benchmark of the compressed-KV hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--layers L --batch B --kv-tokens T]   (the last three shrink the case)
+                    [--workload decode|longctx] [--layers L --batch B --kv-tokens T]
+    (--workload longctx: long-context decode with the KV sequence split across ranks and an
+     NCCL all-gather + log-sum-exp merge per layer; the last three options shrink a case)
 
 Workload: fused decode attention over turbo_prod pages — batch 32
 sequences x 32768 cached tokens, 36 layers, 16 query heads / 2 kv heads, head_dim 128,
@@ -169,8 +171,112 @@ def reference_arm(args):
 
 
 def workload_name(args):
-    return (f"decode_turbo_prod_b{args.batch}_kv{args.kv_tokens}_L{args.layers}"
+    kind = "longctx_kvsplit" if args.workload == "longctx" else "decode"
+    return (f"{kind}_turbo_prod_b{args.batch}_kv{args.kv_tokens}_L{args.layers}"
             f"_q{args.q_heads}kv{args.kv_heads}_d128_page16")
+
+
+# -------------------------------------------------------------------------------------
+# long-context decode with the KV sequence split across ranks (one exchange step per layer)
+# -------------------------------------------------------------------------------------
+
+def longctx(args):
+    """Qwen2.5-7B-shaped decode: 28 layers, 28 q / 4 kv heads, batch 8 x 131072 cached tokens in
+    turbo_prod pages.  Every rank holds the pages of its contiguous, page-aligned token range of
+    every sequence; per layer: local split-KV decode -> (acc, m, l) partials, one NCCL all-gather,
+    local log-sum-exp merge.  Strong scaling: the total work is fixed as ranks are added."""
+    import torch
+    import torch.distributed as dist
+
+    import turborag_b200
+    from turborag_b200.parallel import gather_partials, kv_token_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tq = turborag_b200.TurboQuantWrapper()
+    B, N, L, HQ, H = args.batch, args.kv_tokens, args.layers, args.q_heads, args.kv_heads
+    cfg = tq.default_config()
+    cfg.num_kv_heads = H
+    lay = tq.make_layout_for(cfg)
+    lo, hi = kv_token_range(N, rank, world, 16)
+    local_pages_per_seq = (hi - lo) // 16
+    pages = B * local_pages_per_seq
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99 + rank)
+    # block tables cover the whole sequence; entries outside [lo, hi) are never read
+    tables = torch.zeros(L, B, N // 16, dtype=torch.int32, device=dev)
+    pools = torch.zeros(L, pages * lay.page_size_bytes, dtype=torch.uint8, device=dev)
+    tpos = torch.arange(lo, hi, device=dev)
+    for l in range(L):
+        perm = torch.randperm(pages, device=dev, generator=gen).to(torch.int32).view(B, local_pages_per_seq)
+        tables[l, :, lo // 16:hi // 16] = perm
+        for b in range(B):
+            k, v = synth_kv(torch, hi - lo, H, dev, gen)
+            slots = (tables[l, b][tpos // 16].to(torch.int64) * 16 + tpos % 16).to(torch.int32)
+            tq.pack(k, v, slots, pools[l], lay, cfg)
+    lens = torch.full((B,), N, dtype=torch.int32, device=dev)
+    q = torch.randn(L, B, HQ, 128, device=dev, generator=gen).to(torch.float16)
+    out = torch.zeros(L, B, HQ, 128, dtype=torch.float16, device=dev)
+    part = torch.empty(B * HQ, 130, dtype=torch.float32, device=dev)
+    ws = torch.empty(max(tq.decode_workspace_bytes(B, HQ, N, cfg), 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        for l in range(L):
+            tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
+                            partials_out=part.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo, kv_end=hi,
+                            workspace=ws, stream=stream)
+            allp = gather_partials(part) if world > 1 else part.view(1, B * HQ, 130)
+            tq.merge_partials(allp, out[l].view(B * HQ, 128), HQ, H, stream=stream)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop()
+    ms_per_step = float(t.item()) / args.steps
+    total_bytes = L * B * (N * H * 134 + (N // 16) * 4)  # whole job, all ranks together
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+    peak, peak_kind = peaks()
+    per_rank = total_bytes / world / (ms_per_step * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": workload_name(args), "global_batch": B, "kv_tokens": N, "layers": L,
+                       "parallelism": f"kv sequence split over {world} rank(s), one all-gather of "
+                                      f"{B * HQ * 130 * 4} B per rank per layer, local LSE merge",
+                       "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": per_rank, "peak": peak, "unit": "GB/s",
+                         "frac": per_rank / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "decode_kernel<turbo_prod> + all-gather + merge, per rank"},
+            "gpu_launches": args.steps * L * 3, "clocks": clocks,
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 # -------------------------------------------------------------------------------------
@@ -431,18 +537,25 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=32)
-    ap.add_argument("--kv-tokens", type=int, default=32768)
-    ap.add_argument("--layers", type=int, default=36)
-    ap.add_argument("--q-heads", type=int, default=16)
-    ap.add_argument("--kv-heads", type=int, default=2)
+    ap.add_argument("--workload", default="decode", choices=["decode", "longctx"])
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--kv-tokens", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--q-heads", type=int, default=None)
+    ap.add_argument("--kv-heads", type=int, default=None)
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-secondary", action="store_true")
     args = ap.parse_args()
+    shape = {"decode": (32, 32768, 36, 16, 2), "longctx": (8, 131072, 28, 28, 4)}[args.workload]
+    for name, val in zip(("batch", "kv_tokens", "layers", "q_heads", "kv_heads"), shape):
+        if getattr(args, name) is None:
+            setattr(args, name, val)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload == "longctx":
+        longctx(args)
     else:
         ours(args)
 

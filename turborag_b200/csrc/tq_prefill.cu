@@ -27,6 +27,8 @@ constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLn2P = 0.6931471805599453f;
 constexpr int kTileTokens = 64;
 constexpr int kTileBytes = kTileTokens * 256;  // 64 rows x 128 fp16
+constexpr int kStageBytesP = 2 * kTileBytes + 2 * kTileTokens * 4;  // K tile, V tile, two scale rows
+constexpr int kQTileOff = 2 * kStageBytesP;  // Q tile after the two K/V stages
 constexpr int kPrefillWarps = 8;
 constexpr int kRowsPerCta = kPrefillWarps * 16;
 
@@ -37,7 +39,7 @@ __device__ __forceinline__ uint32_t prmt_p(uint32_t a, uint32_t b, uint32_t sel)
 }
 __device__ __forceinline__ void mma_p(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                       uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -155,13 +157,8 @@ __device__ __forceinline__ uint32_t tile_off(int token, int unit) {
 __global__ void __launch_bounds__(kPrefillWarps * 32, 1)
 prefill_kernel(PrefillParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t* ktile = smem;                 // [64][128] fp16
-    uint8_t* vtile = smem + kTileBytes;
-    float* kscale = reinterpret_cast<float*>(smem + 2 * kTileBytes);  // [64]
-    float* vscale = kscale + kTileTokens;
-    const uint32_t ktile_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ktile));
-    const uint32_t vtile_addr = ktile_addr + kTileBytes;
-
+    // two stages of {K tile, V tile, K scales, V scales}
+    const uint32_t smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int H = p.geo.num_kv_heads, G = p.groups;
@@ -172,20 +169,30 @@ prefill_kernel(PrefillParams p) {
     const int row0 = mt * kRowsPerCta + warp * 16;   // this warp's first row
     const Pools pools = mag_pools();
 
-    // ---- Q fragments: rows row0+g and row0+g+8; row r = (token r / G, query head h*G + r % G) ----
-    uint32_t qf[8][4];
+    // ---- Q tile: the CTA's 128 rows (row r = token r / G, query head h*G + r % G), 32 KB, swizzled
+    // like the K/V tiles; A fragments come from it with ldmatrix, one per k-step
     {
-        const int ra = min(row0 + g, rows_total - 1), rb = min(row0 + g + 8, rows_total - 1);
-        const __half* qa = p.q_rot + ((static_cast<long long>(b) * p.nq + ra / G) * p.hq + h * G + ra % G) * kHeadDim;
-        const __half* qb = p.q_rot + ((static_cast<long long>(b) * p.nq + rb / G) * p.hq + h * G + rb % G) * kHeadDim;
+        const int r = tid >> 1, half = tid & 1;
+        const int rg = min(mt * kRowsPerCta + r, rows_total - 1);
+        const uint4* src = reinterpret_cast<const uint4*>(
+            p.q_rot + ((static_cast<long long>(b) * p.nq + rg / G) * p.hq + h * G + rg % G) * kHeadDim) + 8 * half;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            qf[s][0] = __ldg(reinterpret_cast<const uint32_t*>(qa + 16 * s + 2 * tig));
-            qf[s][1] = __ldg(reinterpret_cast<const uint32_t*>(qb + 16 * s + 2 * tig));
-            qf[s][2] = __ldg(reinterpret_cast<const uint32_t*>(qa + 16 * s + 8 + 2 * tig));
-            qf[s][3] = __ldg(reinterpret_cast<const uint32_t*>(qb + 16 * s + 8 + 2 * tig));
-        }
+        for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<uint4*>(smem + kQTileOff + tile_off(r, 8 * half + u)) = __ldg(src + u);
     }
+    // Per-lane ldmatrix bases.  Every matrix row this lane addresses has (row & 7) == (lane & 7), so the
+    // swizzled unit (u ^ (row & 7)) only needs four pre-XORed offsets per operand; the rest of an address
+    // is an immediate.
+    const int lrow = lane & 7, lmat = lane >> 3;
+    uint32_t offA[4], offB[4];  // offA: unit parity from bit 1 of the matrix index, offB: from bit 0
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {
+        offA[qd] = static_cast<uint32_t>(((2 * qd + (lmat >> 1)) ^ lrow) << 4);
+        offB[qd] = static_cast<uint32_t>(((2 * qd + (lmat & 1)) ^ lrow) << 4);
+    }
+    const uint32_t q_base = smem_addr + kQTileOff + (warp * 16 + lrow + 8 * (lmat & 1)) * 256;  // + offA
+    const uint32_t k_row = (lrow + 8 * (lmat >> 1)) * 256;                                   // + offB
+    const uint32_t v_row = (lrow + 8 * (lmat & 1)) * 256;                                    // + offA
     const int tok_a = (row0 + g) / G, tok_b = (row0 + g + 8) / G;  // chunk positions of the two rows
 
     float o[16][4];
@@ -205,19 +212,35 @@ prefill_kernel(PrefillParams p) {
 
     const int ut = tid & 63, uh = tid >> 6;  // unpack role: token ut of the tile, 16-byte code chunk uh (of 4)
     const int32_t* table = p.block_tables + static_cast<long long>(b) * p.table_stride;
+    const int n_pref = max(tile_hi - tile_lo, 0);
 
-    for (int it = 0; it < n_tiles; ++it) {
-        const bool is_chunk = it >= tile_hi - tile_lo;
-        const int t0 = is_chunk ? (it - (tile_hi - tile_lo)) * kTileTokens : (tile_lo + it) * kTileTokens;
-        __syncthreads();  // previous tile fully consumed
-        if (!is_chunk) {
-            const int t = min(t0 + ut, n_prefix - 1);
-            const int page = __ldg(table + (t >> 4));
-            const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
-            const unsigned th = static_cast<unsigned>((t & 15) * H + h);
-            const uint4 kc = __ldg(reinterpret_cast<const uint4*>(pg + p.geo.k_codes + th * 64 + 16 * uh));
-            const uint4 vc = __ldg(reinterpret_cast<const uint4*>(pg + p.geo.v_codes + th * 64 + 16 * uh));
-            const uint32_t kw[4] = {kc.x, kc.y, kc.z, kc.w}, vw[4] = {vc.x, vc.y, vc.z, vc.w};
+    // Raw codes of one prefix tile for this thread, fetched one tile ahead of their use.
+    struct Raw {
+        uint4 kc, vc;
+        float ks, vs;
+    };
+    auto fetch = [&](int it, Raw& r) {
+        if (it >= n_pref) return;  // chunk tiles are copied directly in fill()
+        const int t = min((tile_lo + it) * kTileTokens + ut, n_prefix - 1);
+        const int page = __ldg(table + (t >> 4));
+        const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
+        const unsigned th = static_cast<unsigned>((t & 15) * H + h);
+        r.kc = __ldg(reinterpret_cast<const uint4*>(pg + p.geo.k_codes + th * 64 + 16 * uh));
+        r.vc = __ldg(reinterpret_cast<const uint4*>(pg + p.geo.v_codes + th * 64 + 16 * uh));
+        if (uh == 0) {
+            r.ks = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.k_scales + th * 2))));
+            r.vs = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.v_scales + th * 2))));
+        }
+    };
+    // Unpack (prefix) or copy (chunk) tile `it` into stage `st`.
+    auto fill = [&](int it, int st, const Raw& r) {
+        uint8_t* ktile = smem + st * kStageBytesP;
+        uint8_t* vtile = ktile + kTileBytes;
+        float* kscale = reinterpret_cast<float*>(ktile + 2 * kTileBytes);
+        float* vscale = kscale + kTileTokens;
+        if (it < n_pref) {
+            const int t0 = (tile_lo + it) * kTileTokens;
+            const uint32_t kw[4] = {r.kc.x, r.kc.y, r.kc.z, r.kc.w}, vw[4] = {r.vc.x, r.vc.y, r.vc.z, r.vc.w};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 *reinterpret_cast<uint4*>(ktile + tile_off(ut, 4 * uh + wi)) = unpack_word(kw[wi], pools);
@@ -225,12 +248,11 @@ prefill_kernel(PrefillParams p) {
             }
             if (uh == 0) {
                 const bool ok = t0 + ut < n_prefix;
-                const float ks = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.k_scales + th * 2))));
-                const float vs = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.v_scales + th * 2))));
-                kscale[ut] = ok ? ks : 0.0f;
-                vscale[ut] = ok ? vs * (1.0f / TQ_ALPHA4P) : 0.0f;
+                kscale[ut] = ok ? r.ks : 0.0f;
+                vscale[ut] = ok ? r.vs * (1.0f / TQ_ALPHA4P) : 0.0f;
             }
         } else {
+            const int t0 = (it - n_pref) * kTileTokens;
             const int t = min(t0 + ut, p.nq - 1);
             const long long rowi = (static_cast<long long>(b) * p.nq + t) * H + h;
             const uint4* ks = reinterpret_cast<const uint4*>(p.ck_rot + rowi * kHeadDim) + 4 * uh;
@@ -246,23 +268,55 @@ prefill_kernel(PrefillParams p) {
                 vscale[ut] = ok ? 1.0f / TQ_ALPHA4P : 0.0f;
             }
         }
-        __syncthreads();
+    };
+
+    Raw raw;
+    raw.ks = raw.vs = 0.0f;
+    raw.kc = raw.vc = make_uint4(0u, 0u, 0u, 0u);
+    if (n_tiles > 0) {
+        fetch(0, raw);
+        fill(0, 0, raw);
+        fetch(1, raw);
+    }
+    __syncthreads();
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int st = it & 1;
+        // next tile: unpack into the other stage (ALU work that overlaps other warps' MMAs), then
+        // start the loads of the tile after it; they stay in flight during the MMAs below
+        if (it + 1 < n_tiles) fill(it + 1, st ^ 1, raw);
+        if (it + 2 < n_tiles) fetch(it + 2, raw);
+
+        const bool is_chunk = it >= n_pref;
+        const int t0 = is_chunk ? (it - n_pref) * kTileTokens : (tile_lo + it) * kTileTokens;
+        const uint32_t ktile_addr = smem_addr + st * kStageBytesP;
+        const uint32_t vtile_addr = ktile_addr + kTileBytes;
+        const float* kscale = reinterpret_cast<const float*>(smem + st * kStageBytesP + 2 * kTileBytes);
+        const float* vscale = kscale + kTileTokens;
 
         // ---- S = Q K^T: 8 n-tiles of 8 tokens ----
         float s[8][4];
 #pragma unroll
         for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+        {
+            uint32_t kb[4];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+            for (int qd = 0; qd < 4; ++qd) kb[qd] = ktile_addr + k_row + offB[qd];
+            uint32_t bf[2][4], af[4];
+            ldsm4(bf[0], kb[0]);
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {
-                // matrices: (tokens 16np..+7, unit 2ks), (same, unit 2ks+1), (tokens +8.., 2ks), (+8.., 2ks+1)
-                const int mat = lane >> 3;
-                const int tok = 16 * np + (lane & 7) + 8 * (mat >> 1);
-                uint32_t bf[4];
-                ldsm4(bf, ktile_addr + tile_off(tok, 2 * ks + (mat & 1)));
-                mma_p(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], bf[0], bf[1]);
-                mma_p(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], bf[2], bf[3]);
+            for (int ks = 0; ks < 8; ++ks) {
+                // A: (rows 0-7, unit 2ks), (rows 8-15, 2ks), (rows 0-7, 2ks+1), (rows 8-15, 2ks+1)
+                ldsm4(af, q_base + offA[ks & 3] + 128 * (ks >> 2));
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    // B: (tokens 16np..+7, unit 2ks), (same, 2ks+1), (tokens +8.., 2ks), (+8.., 2ks+1)
+                    const int idx = 4 * ks + np, nx = idx + 1;
+                    if (nx < 32)
+                        ldsm4(bf[nx & 1], kb[(nx >> 2) & 3] + 128 * (nx >> 4) + 4096 * (nx & 3));
+                    mma_p(s[2 * np], af[0], af[1], af[2], af[3], bf[idx & 1][0], bf[idx & 1][1]);
+                    mma_p(s[2 * np + 1], af[0], af[1], af[2], af[3], bf[idx & 1][2], bf[idx & 1][3]);
+                }
             }
         }
         // ---- scale by the per-token K scale, mask, online softmax ----
@@ -270,21 +324,32 @@ prefill_kernel(PrefillParams p) {
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
+            const float2 ksc = *reinterpret_cast<const float2*>(kscale + 8 * n + 2 * tig);
+            s[n][0] *= ksc.x;
+            s[n][1] *= ksc.y;
+            s[n][2] *= ksc.x;
+            s[n][3] *= ksc.y;
+        }
+        if (is_chunk || t0 + kTileTokens > n_valid) {  // only ragged or causal tiles need masks
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int tl = 8 * n + 2 * tig + e;  // token inside the tile
-                const float ksc = kscale[tl];
-                const int t = t0 + tl;
-                bool va = t < n_valid, vb = va;
-                if (is_chunk) {
-                    va = va && t <= tok_a;
-                    vb = vb && t <= tok_b;
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int t = t0 + 8 * n + 2 * tig + e;
+                    bool va = t < n_valid, vb = va;
+                    if (is_chunk) {
+                        va = va && t <= tok_a;
+                        vb = vb && t <= tok_b;
+                    }
+                    if (!va) s[n][e] = -INFINITY;
+                    if (!vb) s[n][2 + e] = -INFINITY;
                 }
-                s[n][e] = va ? s[n][e] * ksc : -INFINITY;
-                s[n][2 + e] = vb ? s[n][2 + e] * ksc : -INFINITY;
-                mx0 = fmaxf(mx0, s[n][e]);
-                mx1 = fmaxf(mx1, s[n][2 + e]);
             }
+        }
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -302,33 +367,42 @@ prefill_kernel(PrefillParams p) {
             const float p2 = ex2_p(s[n][2] - mn1), p3 = ex2_p(s[n][3] - mn1);
             ls0 += p0 + p1;
             ls1 += p2 + p3;
-            const float v0 = vscale[8 * n + 2 * tig], v1 = vscale[8 * n + 2 * tig + 1];
-            pa[n >> 1][(n & 1) * 2 + 0] = pack2(p0 * v0, p1 * v1);
-            pa[n >> 1][(n & 1) * 2 + 1] = pack2(p2 * v0, p3 * v1);
+            const float2 vsc = *reinterpret_cast<const float2*>(vscale + 8 * n + 2 * tig);
+            pa[n >> 1][(n & 1) * 2 + 0] = pack2(p0 * vsc.x, p1 * vsc.y);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack2(p2 * vsc.x, p3 * vsc.y);
         }
         l_run[0] = fmaf(l_run[0], al0, ls0);
         l_run[1] = fmaf(l_run[1], al1, ls1);
+        if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            o[j][0] *= al0;
-            o[j][1] *= al0;
-            o[j][2] *= al1;
-            o[j][3] *= al1;
-        }
-        // ---- O += P V: 16 n-tiles of 8 dims (one 16-byte unit each), 4 k-steps of 16 tokens ----
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-#pragma unroll
-            for (int up = 0; up < 8; ++up) {
-                // matrices: (tokens 16kk..+7, unit 2up), (tokens +8.., unit 2up), (tokens 16kk.., 2up+1), (+8.., 2up+1)
-                const int mat = lane >> 3;
-                const int tok = 16 * kk + (lane & 7) + 8 * (mat & 1);
-                uint32_t bf[4];
-                ldsm4_t(bf, vtile_addr + tile_off(tok, 2 * up + (mat >> 1)));
-                mma_p(o[2 * up], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], bf[0], bf[1]);
-                mma_p(o[2 * up + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], bf[2], bf[3]);
+            for (int j = 0; j < 16; ++j) {
+                o[j][0] *= al0;
+                o[j][1] *= al0;
+                o[j][2] *= al1;
+                o[j][3] *= al1;
             }
         }
+        // ---- O += P V: 16 n-tiles of 8 dims (one 16-byte unit each), 4 k-steps of 16 tokens ----
+        {
+            uint32_t vb[4];
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) vb[qd] = vtile_addr + v_row + offA[qd];
+            uint32_t bf[2][4];
+            ldsm4_t(bf[0], vb[0]);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int up = 0; up < 8; ++up) {
+                    // B: (tokens 16kk..+7, unit 2up), (tokens +8.., 2up), (tokens 16kk.., 2up+1), (+8.., 2up+1)
+                    const int idx = 8 * kk + up, nx = idx + 1;
+                    if (nx < 32)
+                        ldsm4_t(bf[nx & 1], vb[nx & 3] + 128 * ((nx >> 2) & 1) + 4096 * (nx >> 3));
+                    mma_p(o[2 * up], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], bf[idx & 1][0], bf[idx & 1][1]);
+                    mma_p(o[2 * up + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], bf[idx & 1][2], bf[idx & 1][3]);
+                }
+            }
+        }
+        __syncthreads();  // stage st is free again, stage st^1 is complete
     }
 
     // ---- write the split partial of every live row: acc (natural dim order), m (natural log), l ----
@@ -377,9 +451,18 @@ void launch_prefill(const void* query, const uint8_t* pool, const int32_t* block
     const int rows_total = nq * G;
     const int mtiles = (rows_total + kRowsPerCta - 1) / kRowsPerCta;
     const int prefix_tiles = (max_prefix_tokens + kTileTokens - 1) / kTileTokens;
-    int splits = (4 * sm_count()) / (mtiles * H * batch);
-    if (splits > prefix_tiles / 8) splits = prefix_tiles / 8;
-    if (splits < 1) splits = 1;
+    // one CTA per SM: pick the split count (up to 8) that fills whole waves best
+    const int base = mtiles * H * batch, sms = sm_count();
+    int splits = 1;
+    double best = 0.0;
+    for (int sp = 1; sp <= 8 && sp <= (prefix_tiles + 7) / 8; ++sp) {
+        const double waves = static_cast<double>(base) * sp / sms;
+        const double eff = waves / static_cast<double>(static_cast<long long>(waves + 0.999999));
+        if (eff > best + 0.02) {
+            best = eff;
+            splits = sp;
+        }
+    }
 
     // workspace: rotated q, rotated chunk k/v, partials
     const size_t q_bytes = static_cast<size_t>(q_rows) * kHeadDim * 2;
@@ -425,7 +508,7 @@ void launch_prefill(const void* query, const uint8_t* pool, const int32_t* block
     p.hq = hq;
     p.groups = G;
     p.splits = splits;
-    const size_t smem = 2 * kTileBytes + 2 * kTileTokens * sizeof(float);
+    const size_t smem = 2 * kStageBytesP + kRowsPerCta * 256;
     static bool attr[64] = {};
     int dev = 0;
     check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
