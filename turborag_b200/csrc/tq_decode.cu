@@ -38,6 +38,14 @@ constexpr float kLn2 = 0.6931471805599453f;
 // query scale (K side) and into the per-token V scale.
 #define TQ_ALPHA3 TQF(0x3fa55cec)
 #define TQ_ALPHA4 TQF(0x404c9252)
+#define TQ_POOL3_HI_A 0xb5bbbec1u
+#define TQ_POOL3_HI_B 0x413e3b35u
+#define TQ_POOL3_LO_A 0x10cff18fu
+#define TQ_POOL3_LO_B 0x8ff1cf10u
+#define TQ_MAG4_HI_A 0x42403c36u
+#define TQ_MAG4_HI_B 0x48464544u
+#define TQ_MAG4_LO_A 0x0633f691u
+#define TQ_MAG4_LO_B 0x5e9d2c04u
 
 struct DecodeParams {
     const __half* query;
@@ -294,8 +302,13 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
                                               WarpState& st) {
     const int g = c.g, tig = c.tig, h = c.h, H = c.H;
     const int nq = c.nq, gq0 = c.gq0;
+#ifdef TQ_RUNTIME_POOLS
     const BytePools& pool3 = c.pool3;
     const BytePools& mag4 = c.mag4;
+#else
+    const BytePools pool3 = {TQ_POOL3_HI_A, TQ_POOL3_HI_B, TQ_POOL3_LO_A, TQ_POOL3_LO_B};
+    const BytePools mag4 = {TQ_MAG4_HI_A, TQ_MAG4_HI_B, TQ_MAG4_LO_A, TQ_MAG4_LO_B};
+#endif
     const float inv_alpha_v = c.inv_alpha_v;
     float (&o)[8][4] = st.o;
     float (&m_run)[2] = st.m_run;
@@ -318,12 +331,20 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             unpack_c4(kw1[wi], mag4, bq);
         }
         mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+#ifdef TQ_SPLIT_ACC
         mma16816(s1b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+#else
+        mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+#endif
         if (PROD) {
             unpack_sign(kw0[wi], a);
             unpack_sign(kw1[wi], bq);
             mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
+#ifdef TQ_SPLIT_ACC
             mma16816(s2b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+#else
+            mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
+#endif
         }
     }
 #pragma unroll
@@ -477,6 +498,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
             ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
         }
     }
+#ifdef TQ_RUNTIME_POOLS
     const float t3[8] = {-TQ_C3_3 * TQ_ALPHA3, -TQ_C3_2 * TQ_ALPHA3, -TQ_C3_1 * TQ_ALPHA3,
                          -TQ_C3_0 * TQ_ALPHA3, TQ_C3_0 * TQ_ALPHA3,  TQ_C3_1 * TQ_ALPHA3,
                          TQ_C3_2 * TQ_ALPHA3,  TQ_C3_3 * TQ_ALPHA3};
@@ -485,6 +507,12 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                          TQ_C4_6 * TQ_ALPHA4, TQ_C4_7 * TQ_ALPHA4};
     ctx.pool3 = make_pools(t3);
     ctx.mag4 = make_pools(t4);
+#else
+    // fp16(alpha * level) split into high-byte and low-byte pools, entries 0-3 | 4-7
+    // (what make_pools() computes; tests/test_abi.py recomputes them from the level tables)
+    ctx.pool3 = BytePools{TQ_POOL3_HI_A, TQ_POOL3_HI_B, TQ_POOL3_LO_A, TQ_POOL3_LO_B};
+    ctx.mag4 = BytePools{TQ_MAG4_HI_A, TQ_MAG4_HI_B, TQ_MAG4_LO_A, TQ_MAG4_LO_B};
+#endif
     ctx.inv_alpha_v = 1.0f / TQ_ALPHA4;
     ctx.warp_smem = warp_smem;
     ctx.warp_smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));

@@ -74,49 +74,65 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
     const long long warps_total = static_cast<long long>(gridDim.x) * kDqWarps;
     const bool al = pool_aligned8 != 0;
 
-    for (long long g = static_cast<long long>(blockIdx.x) * kDqWarps + warp; g < groups;
-         g += warps_total) {
+    // Packed inputs of one row group for this lane; the next group's are fetched before the
+    // current one is expanded so that the dependent slot -> page -> code loads stay hidden.
+    struct Raw {
+        uint2 kc, vc;
+        float ks, vs, re;
+        long long out_row;
+        int h;
+        bool valid;
+    };
+    auto fetch = [&](long long g, Raw& r) {
         const long long row_raw = g * 4 + rr;
-        const bool valid = row_raw < num_rows;
-        const long long row = valid ? row_raw : num_rows - 1;
+        r.valid = row_raw < num_rows;
+        const long long row = r.valid ? row_raw : num_rows - 1;
         const long long tok = row / H;
-        const int h = static_cast<int>(row - tok * H);
+        r.h = static_cast<int>(row - tok * H);
         const int slot = __ldg(slot_mapping + tok);
         const int blk = slot / geo.block_size;
         const int tib = slot - blk * geo.block_size;
         const uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
-        const unsigned int th = static_cast<unsigned int>(tib * H + h);
+        const unsigned int th = static_cast<unsigned int>(tib * H + r.h);
+        r.kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
+        r.vc = load_codes(page + geo.v_codes + th * 64 + 8 * l, al);
+        r.ks = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.k_scales + th * 2)));
+        r.vs = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.v_scales + th * 2)));
+        r.re = PROD ? __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.k_res + th * 2))) : 0.0f;
+        r.out_row = hnd ? (static_cast<long long>(r.h) * num_tokens + tok) : row;
+    };
 
-        const uint2 kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
-        const uint2 vc = load_codes(page + geo.v_codes + th * 64 + 8 * l, al);
-        const float ks = __half2float(*reinterpret_cast<const __half*>(page + geo.k_scales + th * 2));
-        const float vs = __half2float(*reinterpret_cast<const __half*>(page + geo.v_scales + th * 2));
-        float re = 0.0f;
-        if (PROD) re = __half2float(*reinterpret_cast<const __half*>(page + geo.k_res + th * 2));
+    long long g = static_cast<long long>(blockIdx.x) * kDqWarps + warp;
+    Raw cur;
+    if (g < groups) fetch(g, cur);
+    for (; g < groups; g += warps_total) {
+        Raw nxt = cur;
+        if (g + warps_total < groups) fetch(g + warps_total, nxt);
 
-        const long long out_row = hnd ? (static_cast<long long>(h) * num_tokens + tok) : row;
+        const float re = cur.re;
+        const int h = cur.h;
         float2 x[8];
         auto level_k = [&](uint32_t nib) {
             if (PROD) return __fadd_rn(lut3[(nib & 7u) * 32 + lane], (nib & 8u) ? re : -re);
             return lut4[nib * 32 + lane];
         };
-
         // K: rotated-domain values (tq_turbo_prod_kernels.cu:315-330 /
         // tq_turbo_mse_kernels.cu:150-156)
-        const float2 ks2 = make_float2(ks, ks), vs2 = make_float2(vs, vs);
+        const float2 ks2 = make_float2(cur.ks, cur.ks), vs2 = make_float2(cur.vs, cur.vs);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t b8 = ((k < 4 ? kc.x : kc.y) >> (8 * (k & 3))) & 0xFFu;
+            const uint32_t b8 = ((k < 4 ? cur.kc.x : cur.kc.y) >> (8 * (k & 3))) & 0xFFu;
             x[k] = mul2(make_float2(level_k(b8 & 0xFu), level_k(b8 >> 4)), ks2);
         }
-        inverse_and_store(x, buf, lane, c, h, out_key + out_row * kHeadDim, valid);
+        inverse_and_store(x, buf, lane, c, h, out_key + cur.out_row * kHeadDim, cur.valid);
 
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t b8 = ((k < 4 ? vc.x : vc.y) >> (8 * (k & 3))) & 0xFFu;
+            const uint32_t b8 = ((k < 4 ? cur.vc.x : cur.vc.y) >> (8 * (k & 3))) & 0xFFu;
             x[k] = mul2(make_float2(lut4[(b8 & 0xFu) * 32 + lane], lut4[(b8 >> 4) * 32 + lane]), vs2);
         }
-        inverse_and_store(x, buf, lane, c, h, out_value + out_row * kHeadDim, valid);
+        inverse_and_store(x, buf, lane, c, h, out_value + cur.out_row * kHeadDim, cur.valid);
+        cur = nxt;
     }
 }
 

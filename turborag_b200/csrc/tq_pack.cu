@@ -18,6 +18,77 @@ constexpr int kCodeRowBytes = 72;  // 64 code bytes + pad: rows land on distinct
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 
+// ---- nearest-level search through bank-replicated shared tables ---------------------------
+// The threshold search is the kernel's largest cost and runs on the half-rate integer/compare
+// pipe, while the load/store pipe is mostly idle.  |x| (clamped) is cut into 16 cells of
+// width 3/16; each cell holds at most one decision threshold, so a table entry (threshold
+// inside the cell or +inf, code below it) plus ONE compare gives the exact code.  Entries
+// exist per sign class (the thresholds of the negative half differ by an ulp where an exact
+// fp32 tie exists) and are replicated over the 32 lanes, so lookups never conflict.
+constexpr float kCellScale = 16.0f / 3.0f;
+constexpr float kCellMagic = 8388608.0f;  // 2^23: the fma's low mantissa bits are round(|x| * scale)
+constexpr float kCellClamp = 2.8125f;     // 15 cells
+
+struct CellInfo {
+    float t;   // threshold inside the cell, +inf if none
+    int base;  // thresholds below the cell
+};
+template <int N>
+__device__ __forceinline__ CellInfo cell_info(const float (&thr)[N], int cell) {
+    CellInfo c{__int_as_float(0x7f800000), 0};
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+        const int cj = __float2int_rn(thr[j] * kCellScale);
+        if (cj < cell) ++c.base;
+        if (cj == cell) c.t = thr[j];
+    }
+    return c;
+}
+
+// lutV[(sign*16 + cell)*32 + lane] = (threshold, code if below it; +1 when (above == positive))
+// lutK[...]                       = (threshold, level below, level above, code as for lutV)
+__device__ void build_luts(float4* lutK, float2* lutV, bool need_k) {
+    const float k3m[3] = {TQ_K3_M1, TQ_K3_M2, TQ_K3_M3}, k3n[3] = {TQ_K3_N1, TQ_K3_N2, TQ_K3_N3};
+    const float v4m[7] = {TQ_V4_M1, TQ_V4_M2, TQ_V4_M3, TQ_V4_M4, TQ_V4_M5, TQ_V4_M6, TQ_V4_M7};
+    const float v4n[7] = {TQ_V4_N1, TQ_V4_N2, TQ_V4_N3, TQ_V4_N4, TQ_V4_N5, TQ_V4_N6, TQ_V4_N7};
+    const float lv3[4] = {TQ_C3_0, TQ_C3_1, TQ_C3_2, TQ_C3_3};
+    for (int i = threadIdx.x; i < 2 * 16 * 32; i += blockDim.x) {
+        const int cell = (i >> 5) & 15;
+        const bool neg = (i >> 9) != 0;
+        const CellInfo v = neg ? cell_info(v4n, cell) : cell_info(v4m, cell);
+        lutV[i] = make_float2(v.t, __int_as_float(neg ? 6 - v.base : 8 + v.base));
+        if (need_k) {
+            const CellInfo k = neg ? cell_info(k3n, cell) : cell_info(k3m, cell);
+            const int hi = k.base < 3 ? k.base + 1 : 3;
+            lutK[i] = make_float4(k.t, lv3[k.base], lv3[hi], __int_as_float(neg ? 2 - k.base : 4 + k.base));
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t cell_index(float a, float x) {
+    const float u = __fmaf_rn(a, kCellScale, kCellMagic);
+    return (__float_as_uint(u) & 31u) + (x >= TQ_TMID ? 0u : 16u);
+}
+
+// 4-bit code (nearest_v4_idx / nearest_codebook_idx of the reference), exact.
+__device__ __forceinline__ uint32_t quant_v4_lut(float x, const float2* lutV, int lane) {
+    const float a = fabsf(x);
+    const bool pos = x >= TQ_TMID;
+    const float2 e = lutV[cell_index(fminf(a, kCellClamp), x) * 32 + lane];
+    return __float_as_uint(e.y) + (((a >= e.x) == pos) ? 1u : 0u);
+}
+
+// K nibble = residual sign << 3 | 3-bit code, and the residual e = clamp(kn) - level.
+__device__ __forceinline__ uint32_t quant_k3_lut(float kn, const float4* lutK, int lane, float& e) {
+    const float a = fminf(fabsf(kn), 2.5f);  // |clamp(kn, -2.5, 2.5)|
+    const bool pos = kn >= TQ_TMID;
+    const float4 t = lutK[cell_index(a, kn) * 32 + lane];
+    const bool above = a >= t.x;
+    const float lvl = above ? t.z : t.y;
+    e = __fadd_rn(copysignf(a, kn), pos ? -lvl : lvl);
+    return (__float_as_uint(t.w) + ((above == pos) ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
+}
+
 // Move a row's 64 code bytes from "lane l' holds byte l'+8j" to "lane l holds
 // bytes 8l..8l+7" through a per-warp byte buffer, then store them.
 __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t* code_buf,
@@ -47,6 +118,10 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, int head_dim, long long num_rows, int pool_aligned8) {
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
+    __shared__ __align__(16) float4 lutK[PROD ? 2 * 16 * 32 : 1];
+    __shared__ __align__(16) float2 lutV[2 * 16 * 32];
+    build_luts(lutK, lutV, PROD);
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rr = lane >> 3, l = lane & 7;
     float* buf = xchg[warp];
@@ -98,9 +173,8 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             for (int j = 0; j < 8; ++j) {
                 float e0, e1;
                 const float2 kn = div_by2(y[j], krms, kr);
-                const float kn0 = kn.x < -2.5f ? -2.5f : (kn.x > 2.5f ? 2.5f : kn.x);
-                const float kn1 = kn.y < -2.5f ? -2.5f : (kn.y > 2.5f ? 2.5f : kn.y);
-                const uint32_t n0 = quant_k3(kn0, e0), n1 = quant_k3(kn1, e1);
+                const uint32_t n0 = quant_k3_lut(kn.x, lutK, lane, e0);
+                const uint32_t n1 = quant_k3_lut(kn.y, lutK, lane, e1);
                 kbytes[j] = n0 | (n1 << 4);
                 const float2 e = make_float2(e0, e1);
                 e2[j] = mul2(e, e);
@@ -120,7 +194,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float2 kn = div_by2(y[j], krms, kr);
-                kbytes[j] = quant_v4(kn.x) | (quant_v4(kn.y) << 4);
+                kbytes[j] = quant_v4_lut(kn.x, lutV, lane) | (quant_v4_lut(kn.y, lutV, lane) << 4);
             }
             if (valid && l == 0)
                 *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
@@ -152,7 +226,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float2 vn = div_by2(y[j], vrms, vr);
-            vbytes[j] = quant_v4(vn.x) | (quant_v4(vn.y) << 4);
+            vbytes[j] = quant_v4_lut(vn.x, lutV, lane) | (quant_v4_lut(vn.y, lutV, lane) << 4);
         }
         if (valid && l == 0)
             *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
