@@ -61,7 +61,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -75,7 +75,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                 "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -456,15 +456,78 @@ def ours(args):
     }
 
     if rank == 0:
-        if not args.skip_secondary:
-            line["secondary"] = store_numbers(torch, tq, dev, gen, peak)
         if world == 1 and not args.skip_cpu:
             line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(
                 torch, tq, args, pools, tables, q_dev, out_dev, lay)
+        if not args.skip_secondary:
+            line["secondary"] = store_numbers(torch, tq, dev, gen, peak)
+            if world == 1:
+                pools = staging = host_pool = None  # free 10+ GB before the prefill case
+                torch.cuda.empty_cache()
+                line["secondary"]["prefill_turbo_mse"] = prefill_numbers(torch, tq, dev, gen)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def prefill_numbers(torch, tq, dev, gen, batch=8, nq=256, n=32768, hq=16, h=2, iters=5):
+    """Chunked query prefill (turbo_mse prefix + causal fp16 chunk): 256 query tokens attend to a
+    32768-token compressed prefix, batch 8, 16 q / 2 kv heads.  TFLOP/s over 4*B*Hq*Nq*Nkv*D
+    (prefix) + 2*B*Hq*Nq^2*D (causal chunk) flops, against the measured bf16 tensor peak."""
+    cfg = tq.default_config()
+    cfg.num_kv_heads = h
+    lay = tq.make_mse_layout_for(cfg)
+    pages = batch * n // 16
+    pool = torch.zeros(pages * lay.page_size_bytes, dtype=torch.uint8, device=dev)
+    tables = torch.randperm(pages, device=dev, generator=gen).to(torch.int32).view(batch, n // 16).contiguous()
+    t = torch.arange(n, device=dev)
+    for b in range(batch):
+        k, v = synth_kv(torch, n, h, dev, gen)
+        tq.mse_pack(k, v, (tables[b][t // 16].to(torch.int64) * 16 + t % 16).to(torch.int32), pool, lay, cfg)
+    q = torch.randn(batch, nq, hq, 128, device=dev, generator=gen).to(torch.float16)
+    ck, cv = synth_kv(torch, batch * nq, h, dev, gen)
+    ck, cv = ck.view(batch, nq, h, 128), cv.view(batch, nq, h, 128)
+    lens = torch.full((batch,), n, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+    for _ in range(3):
+        tq.mse_prefill_paged(q, pool, tables, lens, ck, cv, out, lay, cfg)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        tq.mse_prefill_paged(q, pool, tables, lens, ck, cv, out, lay, cfg)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    flops = 4.0 * batch * hq * nq * n * 128 + 2.0 * batch * hq * nq * nq * 128
+    tensor_peak = 1655.3
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        tensor_peak = float(json.loads(pk.read_text())["bf16_tflops"])
+    return {"value": flops / ms / 1e9, "unit": "TFLOP/s", "ms": ms, "frac_of_tensor_peak": flops / ms / 1e9 / tensor_peak,
+            "shape": f"b{batch}_q{nq}_kv{n}_q{hq}kv{h}", "note": "mma.sync tensor tiles (not tcgen05)"}
+
+
+def side_workload(args):
+    """--workload store | prefill: the secondary kernels alone (used for ncu captures)."""
+    import torch
+
+    import turborag_b200
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    tq = turborag_b200.TurboQuantWrapper()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    peak, _ = peaks()
+    if args.workload == "store":
+        res = store_numbers(torch, tq, dev, gen, peak)
+        print(json.dumps({"metric": "quantize-pack GB/s", "value": res["pack_turbo_prod"]["value"], "unit": "GB/s",
+                          "n_gpus": 1, "config": {"workload": "store_16docs_x8192_L1_kv2_d128"}, "secondary": res}))
+    else:
+        res = prefill_numbers(torch, tq, dev, gen, batch=args.batch or 8, iters=max(1, args.steps))
+        print(json.dumps({"metric": "chunk prefill TFLOP/s", "value": res["value"], "unit": "TFLOP/s", "n_gpus": 1,
+                          "config": {"workload": "prefill_turbo_mse_" + res["shape"]}, "secondary": res}))
 
 
 def store_numbers(torch, tq, dev, gen, peak):
@@ -537,7 +600,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "longctx"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "longctx", "store", "prefill"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--kv-tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None)
@@ -546,6 +609,9 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-secondary", action="store_true")
     args = ap.parse_args()
+    if args.workload in ("store", "prefill"):
+        side_workload(args)
+        return
     shape = {"decode": (32, 32768, 36, 16, 2), "longctx": (8, 131072, 28, 28, 4)}[args.workload]
     for name, val in zip(("batch", "kv_tokens", "layers", "q_heads", "kv_heads"), shape):
         if getattr(args, name) is None:
