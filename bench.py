@@ -47,9 +47,11 @@ if str(ROOT) not in sys.path:
 METRIC = "fused compressed-KV decode attn GB/s"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode-kernel launch at the full
-# per-layer shape (ncu capture summarised under profiles/); None until measured.
-DECODE_DRAM_TRAFFIC_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-kernel launch at the default
+# per-layer shape. Captured with ncu at half the batch (141.07 MB read + 4.11 MB written for
+# 140.6 MB of pages) and scaled by the pages one launch reads: every page is read once, so
+# traffic grows in proportion. Only valid for the default shape; other shapes report null.
+DECODE_DRAM_TRAFFIC_PER_LAUNCH = 2 * (141.07e6 + 4.11e6)
 OUTLIERS = (3, 17, 64, 101)
 
 
@@ -347,6 +349,8 @@ def ours(args):
 
     bytes_per_launch = B * (N * H * 134 + pages_per_seq * 4)
     bytes_per_step = bytes_per_launch * L
+    default_shape = (B, N, H, HQ) == (32, 32768, 2, 16)
+    traffic = DECODE_DRAM_TRAFFIC_PER_LAUNCH if default_shape else None
 
     # ---- value: pages resident, device-timed ------------------------------------------
     for _ in range(args.warmup):
@@ -438,8 +442,8 @@ def ours(args):
                    "l2": "inputs larger than L2 (281 MB of pages per launch)",
                    "pct_of_measured_hbm": 100.0 * achieved / peak},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": DECODE_DRAM_TRAFFIC_PER_LAUNCH,
-                     "peak_kind": peak_kind, "kernel": "decode_kernel<turbo_prod>",
+                     "frac": achieved / peak, "traffic": traffic,
+                     "peak_kind": peak_kind, "kernel": "decode_paged16_kernel<turbo_prod,2>",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
                      "launch_ms": launch_ms,
                      "note": "launch_ms = timed region / decode launches; includes the merge kernel and launch gaps"},
