@@ -63,7 +63,8 @@ struct DecodeParams {
     int max_kv_tokens;
     int kv_begin, kv_end;
     int splits;
-    int streams;       // warps per kv head inside a CTA
+    int batch;
+    int streams;       // warps per kv head inside a group
     int bs_shift;      // log2(block_size) or -1
     int aligned16;     // every code row starts on a 16-byte boundary
 };
@@ -291,12 +292,72 @@ struct BlockCtx {
     float inv_alpha_v;
     uint8_t* warp_smem;   // per-warp shared region (merge record at the end; fast path: ring)
     uint32_t warp_smem_addr;
+    const uint8_t* lut;   // byte -> operand tables in shared memory (fast path only)
+    uint32_t lane_k, lane_v;  // this lane's replica offsets inside a table row
+    uint8_t* group_smem;  // first per-warp region of this warp's group (merge records)
+    int bar_id, bar_threads;  // barrier shared by the warps that work on one (sequence, split)
     int lane, g, tig, h, H, nq, gq0;
 };
 
+// ---- shared-memory operand tables (paged fast path) -----------------------------------
+// Turning a code byte (two 4-bit fields) into MMA operands with byte permutes costs about two
+// integer-pipe instructions per element, and that pipe bounds the kernel.  The fast path looks
+// the byte up instead: row r (256 bytes) of the table belongs to byte value r,
+//   bytes   0..127: 16 replicas of {half2 levels of the two 3-bit K codes, half2 +-1 of the two
+//                   residual-sign bits}; lane l reads replica l % 16 with one 8-byte load (the
+//                   two half-warps of a 64-bit load are separate wavefronts, so no conflicts),
+//   bytes 128..255: 32 replicas of the half2 levels of the two 4-bit codes; lane l reads
+//                   replica l (4-byte load, conflict-free).
+// The address is one byte permute: byte 1 = the code byte, byte 0 = the lane's replica offset.
+constexpr int kLutBytes = 256 * 256;
+
+__device__ __forceinline__ uint32_t pool_entry(uint32_t hi_a, uint32_t hi_b, uint32_t lo_a,
+                                               uint32_t lo_b, uint32_t e) {
+    const uint32_t sh = 8u * (e & 3u);
+    const uint32_t hi = ((e < 4u ? hi_a : hi_b) >> sh) & 0xFFu;
+    const uint32_t lo = ((e < 4u ? lo_a : lo_b) >> sh) & 0xFFu;
+    return (hi << 8) | lo;
+}
+// fp16 bits of alpha3 * (signed 3-bit level), alpha4 * (signed 4-bit level)
+__device__ __forceinline__ uint32_t level3_bits(uint32_t code) {
+    return pool_entry(TQ_POOL3_HI_A, TQ_POOL3_HI_B, TQ_POOL3_LO_A, TQ_POOL3_LO_B, code & 7u);
+}
+__device__ __forceinline__ uint32_t level4_bits(uint32_t n) {
+    const uint32_t mag = n >= 8u ? n - 8u : 7u - n;
+    return pool_entry(TQ_MAG4_HI_A, TQ_MAG4_HI_B, TQ_MAG4_LO_A, TQ_MAG4_LO_B, mag) |
+           (n >= 8u ? 0u : 0x8000u);
+}
+// All threads of the CTA; the caller synchronises afterwards.
+__device__ __forceinline__ void build_operand_lut(uint8_t* lut) {
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+        const uint32_t row = i >> 1, part = i & 1;
+        const uint32_t n0 = row & 15u, n1 = row >> 4;
+        const uint32_t lv3 = level3_bits(n0) | (level3_bits(n1) << 16);
+        const uint32_t sg = ((n0 & 8u) ? 0x3C00u : 0xBC00u) | ((n1 & 8u) ? 0x3C000000u : 0xBC000000u);
+        const uint32_t lv4 = level4_bits(n0) | (level4_bits(n1) << 16);
+        uint4* dk = reinterpret_cast<uint4*>(lut + row * 256 + part * 64);
+        uint4* dv = reinterpret_cast<uint4*>(lut + row * 256 + 128 + part * 64);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            dk[k] = make_uint4(lv3, sg, lv3, sg);
+            dv[k] = make_uint4(lv4, lv4, lv4, lv4);
+        }
+    }
+}
+__device__ __forceinline__ uint2 lut_k(const uint8_t* lut, uint32_t word, uint32_t lane_k, uint32_t sel) {
+    return *reinterpret_cast<const uint2*>(lut + prmt(word, lane_k, sel));
+}
+__device__ __forceinline__ uint32_t lut_v(const uint8_t* lut, uint32_t word, uint32_t lane_v, uint32_t sel) {
+    return *reinterpret_cast<const uint32_t*>(lut + prmt(word, lane_v, sel));
+}
+__device__ __forceinline__ void group_sync(int bar_id, int nthreads) {
+    if (bar_id == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+}
+
 // One 16-token block for one kv head: QK^T (+ residual-sign product), online softmax, PV.
 // MODE 1 writes logits instead.
-template <bool PROD, int MODE>
+template <bool PROD, int MODE, bool LUT = false>
 __device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
                                               const BlockRaw& cur, int tb, int t_end,
                                               WarpState& st) {
@@ -320,6 +381,28 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     float s1b[4] = {0.f, 0.f, 0.f, 0.f}, s2b[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
     const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
+    if constexpr (LUT) {
+        // MMA n covers bytes 2n, 2n+1 of this lane's 16 code bytes: dims 32 tig + 4n + {0,1 | 2,3}
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int wi = n >> 1;
+            const uint32_t sa = (n & 1) ? 0x5524u : 0x5504u, sb = (n & 1) ? 0x5534u : 0x5514u;
+            if (PROD) {
+                const uint2 e00 = lut_k(c.lut, kw0[wi], c.lane_k, sa);
+                const uint2 e10 = lut_k(c.lut, kw1[wi], c.lane_k, sa);
+                const uint2 e01 = lut_k(c.lut, kw0[wi], c.lane_k, sb);
+                const uint2 e11 = lut_k(c.lut, kw1[wi], c.lane_k, sb);
+                mma16816(s1, e00.x, e10.x, e01.x, e11.x, qf[n][0], qf[n][1]);
+                mma16816(s2, e00.y, e10.y, e01.y, e11.y, qf[n][0], qf[n][1]);
+            } else {
+                const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_v, sa);
+                const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_v, sa);
+                const uint32_t e01 = lut_v(c.lut, kw0[wi], c.lane_v, sb);
+                const uint32_t e11 = lut_v(c.lut, kw1[wi], c.lane_v, sb);
+                mma16816(s1, e00, e10, e01, e11, qf[n][0], qf[n][1]);
+            }
+        }
+    } else {
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
         uint32_t a[4], bq[4];
@@ -346,6 +429,7 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
 #endif
         }
+    }
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -415,6 +499,20 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
 
     // ---- O^T += V^T P^T: A = V^T (rows = this lane's dims 16g + 2j + {0,1}, k = tokens) ----
+    if constexpr (LUT) {
+        // tile j = byte j of the lane's 8 V bytes: a looked-up half2 holds dims 2j, 2j+1 of one
+        // token; two permutes re-pair the same dim of two adjacent tokens
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t sel = 0x5504u | (static_cast<uint32_t>(j & 3) << 4);
+            const uint32_t e0 = lut_v(c.lut, j < 4 ? cur.v[0].x : cur.v[0].y, c.lane_v, sel);
+            const uint32_t e1 = lut_v(c.lut, j < 4 ? cur.v[1].x : cur.v[1].y, c.lane_v, sel);
+            const uint32_t e2 = lut_v(c.lut, j < 4 ? cur.v[2].x : cur.v[2].y, c.lane_v, sel);
+            const uint32_t e3 = lut_v(c.lut, j < 4 ? cur.v[3].x : cur.v[3].y, c.lane_v, sel);
+            mma16816(o[j], prmt(e0, e1, 0x5410u), prmt(e0, e1, 0x7632u), prmt(e2, e3, 0x5410u),
+                     prmt(e2, e3, 0x7632u), pb0, pb1);
+        }
+    } else {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         uint32_t ab[8], cd[8];
@@ -423,6 +521,7 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
 #pragma unroll
         for (int dd = 0; dd < 4; ++dd)
             mma16816(o[4 * i + dd], ab[2 * dd], ab[2 * dd + 1], cd[2 * dd], cd[2 * dd + 1], pb0, pb1);
+    }
     }
 }
 
@@ -433,24 +532,29 @@ struct CtaRange {
 
 // Prologue: rotate this pass's queries (q' = FWHT(s .* q) * rsqrt(D), pre-scaled), build the
 // B fragments and the lookup pools, and work out the CTA's block range.
-template <bool PROD, int MODE>
-__device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* smem_raw,
-                                                int warp_bytes, BlockCtx& ctx, CtaRange& r) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// A "group" is the set of warps (H kv heads x p.streams streams) that works on one (sequence,
+// split): the whole CTA in the general kernel, one half of the CTA in the paged fast path.
+// `group_smem` is the group's first per-warp region, `qsm` a scratch of H*8*128 halves that is
+// dead once the fragments are built, `warp` the warp's index inside the group.
+template <bool PROD, int MODE, bool LUT = false>
+__device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* group_smem,
+                                                int warp_bytes, __half* qsm, int warp, int seq,
+                                                int split, int bar_id, int bar_threads,
+                                                BlockCtx& ctx, CtaRange& r) {
+    const int lane = threadIdx.x & 31;
     const int H = p.geo.num_kv_heads;
     const int h = warp % H, stream = warp / H;
     const int g = lane >> 2, tig = lane & 3;
     const int qg = blockIdx.z;
-    r.split = blockIdx.x;
-    r.b = blockIdx.y;
+    r.split = split;
+    r.b = seq;
     r.G = p.groups;
     r.rows_per_seq = r.G * H;
     r.stream = stream;
     const int gq0 = qg * 8;                  // first query of this pass within the group
     const int nq = min(8, r.G - gq0);        // live columns
 
-    uint8_t* warp_smem = smem_raw + warp * warp_bytes;
-    __half* qsm = reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * warp_bytes);
+    uint8_t* warp_smem = group_smem + warp * warp_bytes;
 
     // one warp per (kv head, column); lane holds 4 consecutive elements
     const float c = inv_sqrt_dim(p.head_dim);
@@ -484,18 +588,25 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
         dst[0] = __floats2half2_rn(x[0], x[1]);
         dst[1] = __floats2half2_rn(x[2], x[3]);
     }
-    __syncthreads();
+    group_sync(bar_id, bar_threads);
 
-    // B fragments: column g, dims 32*tig + 8*wi + {2hf, 2hf+4 | 2hf+1, 2hf+5}
     {
         const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const int base = 8 * (s >> 1) + 2 * (s & 1);
-            const __half2 b01 = __halves2half2(qrow[base], qrow[base + 4]);
-            const __half2 b23 = __halves2half2(qrow[base + 1], qrow[base + 5]);
-            ctx.qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
-            ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
+            if (LUT) {
+                // B fragments: column g, dims 32*tig + 4*s + {0,1 | 2,3}
+                const uint2 q4 = *reinterpret_cast<const uint2*>(qrow + 4 * s);
+                ctx.qf[s][0] = q4.x;
+                ctx.qf[s][1] = q4.y;
+            } else {
+                // B fragments: column g, dims 32*tig + 8*wi + {2hf, 2hf+4 | 2hf+1, 2hf+5}
+                const int base = 8 * (s >> 1) + 2 * (s & 1);
+                const __half2 b01 = __halves2half2(qrow[base], qrow[base + 4]);
+                const __half2 b23 = __halves2half2(qrow[base + 1], qrow[base + 5]);
+                ctx.qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
+                ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
+            }
         }
     }
 #ifdef TQ_RUNTIME_POOLS
@@ -516,6 +627,12 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     ctx.inv_alpha_v = 1.0f / TQ_ALPHA4;
     ctx.warp_smem = warp_smem;
     ctx.warp_smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
+    ctx.lut = nullptr;
+    ctx.lane_k = static_cast<uint32_t>(lane & 15) * 8u;
+    ctx.lane_v = 128u + static_cast<uint32_t>(lane) * 4u;
+    ctx.group_smem = group_smem;
+    ctx.bar_id = bar_id;
+    ctx.bar_threads = bar_threads;
     ctx.lane = lane;
     ctx.g = g;
     ctx.tig = tig;
@@ -542,9 +659,10 @@ __device__ __forceinline__ void init_state(WarpState& st) {
 
 // Epilogue: combine the streams of a kv head through shared memory (the per-warp regions
 // are dead by now and are reused as records), then write the split partial.
-__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* smem_raw,
-                                                int warp_bytes, const BlockCtx& c,
-                                                const CtaRange& r, WarpState& st) {
+__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int warp_bytes,
+                                                const BlockCtx& c, const CtaRange& r,
+                                                WarpState& st) {
+    uint8_t* smem_raw = c.group_smem;
     const int lane = c.lane, g = c.g, tig = c.tig, h = c.h, H = c.H;
     float (&o)[8][4] = st.o;
     float (&m_run)[2] = st.m_run;
@@ -554,7 +672,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* 
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], msk);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], msk);
     }
-    __syncthreads();
+    group_sync(c.bar_id, c.bar_threads);
     float* rec = reinterpret_cast<float*>(c.warp_smem);
     if (r.stream > 0) {
 #pragma unroll
@@ -566,7 +684,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* 
         rec[34 * 32 + lane] = l_run[0];
         rec[35 * 32 + lane] = l_run[1];
     }
-    __syncthreads();
+    group_sync(c.bar_id, c.bar_threads);
     if (r.stream > 0) return;
     for (int s = 1; s < p.streams; ++s) {
         const float* q = reinterpret_cast<const float*>(smem_raw + (s * H + h) * warp_bytes);
@@ -612,10 +730,12 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, uint8_t* 
 template <bool PROD, int MODE>
 __global__ void __launch_bounds__(256, 2)
 decode_kernel(DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     BlockCtx ctx;
     CtaRange r;
-    decode_prologue<PROD, MODE>(p, smem_raw, kWarpSmemBytes, ctx, r);
+    decode_prologue<PROD, MODE>(p, smem_raw, kWarpSmemBytes,
+                                reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * kWarpSmemBytes),
+                                threadIdx.x >> 5, blockIdx.y, blockIdx.x, 0, 0, ctx, r);
     WarpState st;
     init_state(st);
     const bool aligned = p.aligned16 != 0;
@@ -634,7 +754,7 @@ decode_kernel(DecodeParams p) {
         cur = nxt;
     }
     if (MODE == 1) return;
-    decode_epilogue(p, smem_raw, kWarpSmemBytes, ctx, r, st);
+    decode_epilogue(p, kWarpSmemBytes, ctx, r, st);
 }
 
 // ---- paged fast path ----------------------------------------------------------------
@@ -662,17 +782,35 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-#ifndef TQ_FAST_CTAS
-#define TQ_FAST_CTAS 2
-#endif
+// One CTA per SM, 16 warps = two groups of 8; each group works on its own (sequence, split)
+// exactly like an 8-warp CTA would, the two share the operand tables.
+constexpr int kFastGroupWarps = 8;
+constexpr int kFastGroups = 2;
+constexpr int kFastGroupBytes = kFastGroupWarps * kFastWarpBytes;
+constexpr int kFastSmemBytes = kLutBytes + kFastGroups * kFastGroupBytes;
+static_assert(kFastGroupBytes >= kMaxHeads * 8 * kHeadDim * 2, "the query scratch reuses the ring");
+
 template <bool PROD, int H>
-__global__ void __launch_bounds__(256, TQ_FAST_CTAS)
+__global__ void __launch_bounds__(kFastGroups * kFastGroupWarps * 32, 1)
 decode_paged16_kernel(DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    constexpr int kStreams = 8 / H;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int kStreams = kFastGroupWarps / H;
+    build_operand_lut(smem_raw);
+    __syncthreads();
+    // work items (sequence, split) are numbered sequence-major; a CTA takes two neighbours
+    const int group = threadIdx.x / (kFastGroupWarps * 32);
+    const int item = blockIdx.x * kFastGroups + group;
+    if (item >= p.batch * p.splits) return;  // odd item count: the last CTA runs one group
+    const int seq = item / p.splits, split = item - seq * p.splits;
+    uint8_t* group_smem = smem_raw + kLutBytes + group * kFastGroupBytes;
+    const int bar_id = 1 + group, bar_threads = kFastGroupWarps * 32;
     BlockCtx ctx;
     CtaRange r;
-    decode_prologue<PROD, 0>(p, smem_raw, kFastWarpBytes, ctx, r);
+    decode_prologue<PROD, 0, true>(p, group_smem, kFastWarpBytes, reinterpret_cast<__half*>(group_smem),
+                                   (threadIdx.x >> 5) % kFastGroupWarps, seq, split, bar_id,
+                                   bar_threads, ctx, r);
+    ctx.lut = smem_raw;
+    group_sync(bar_id, bar_threads);  // the query scratch is dead: the ring may be filled
     WarpState st;
     init_state(st);
     const int lane = ctx.lane, g = ctx.g, tig = ctx.tig, h = ctx.h;
@@ -763,12 +901,12 @@ decode_paged16_kernel(DecodeParams p) {
             if (tb + g >= r.t_end) cur.ks0 = cur.vs0 = cur.re0 = 0.0f;
             if (tb + g + 8 >= r.t_end) cur.ks1 = cur.vs1 = cur.re1 = 0.0f;
         }
-        process_block<PROD, 0>(p, ctx, cur, tb, r.t_end, st);
+        process_block<PROD, 0, true>(p, ctx, cur, tb, r.t_end, st);
         __syncwarp();  // every lane is done reading this stage before it is refilled
         stage = stage == kStages - 1 ? 0 : stage + 1;
     }
     cp_async_wait<0>();
-    decode_epilogue(p, smem_raw, kFastWarpBytes, ctx, r, st);
+    decode_epilogue(p, kFastWarpBytes, ctx, r, st);
 }
 
 // ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
@@ -846,7 +984,7 @@ void set_smem_attr_once() {
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
-    const int fast_bytes = 8 * kFastWarpBytes + kMaxHeads * 8 * kHeadDim * 2;
+    const int fast_bytes = kFastSmemBytes;
 #define TQ_FAST_ATTR(PRODV, HV)                                                               \
     check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<PRODV, HV>,                         \
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), \
@@ -928,6 +1066,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     p.kv_begin = a.kv_begin;
     p.kv_end = a.kv_end;
     p.streams = streams;
+    p.batch = a.batch;
     {
         const int bs = a.geo.block_size;
         p.bs_shift = -1;
@@ -969,8 +1108,10 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
                       (a.geo.v_scales & 15) == 0 && (!prod || (a.geo.k_res & 15) == 0) &&
                       a.kv_begin >= 0 && (a.kv_begin & 15) == 0;
     if (fast) {
-        const size_t fsmem = static_cast<size_t>(warps) * kFastWarpBytes + H * 8 * kHeadDim * sizeof(__half);
-#define TQ_FAST_LAUNCH(PRODV, HV) decode_paged16_kernel<PRODV, HV><<<grid, 256, fsmem, stream>>>(p)
+        const dim3 fgrid((a.batch * splits + kFastGroups - 1) / kFastGroups, 1, qgroups);
+#define TQ_FAST_LAUNCH(PRODV, HV)                                                                \
+    decode_paged16_kernel<PRODV, HV><<<fgrid, kFastGroups * kFastGroupWarps * 32, kFastSmemBytes, \
+                                       stream>>>(p)
         if (prod) {
             if (H == 1) TQ_FAST_LAUNCH(true, 1);
             else if (H == 2) TQ_FAST_LAUNCH(true, 2);
