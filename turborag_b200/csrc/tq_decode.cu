@@ -303,11 +303,12 @@ struct BlockCtx {
 // Turning a code byte (two 4-bit fields) into MMA operands with byte permutes costs about two
 // integer-pipe instructions per element, and that pipe bounds the kernel.  The fast path looks
 // the byte up instead: row r (256 bytes) of the table belongs to byte value r,
-//   bytes   0..127: 16 replicas of {half2 levels of the two 3-bit K codes, half2 +-1 of the two
-//                   residual-sign bits}; lane l reads replica l % 16 with one 8-byte load (the
-//                   two half-warps of a 64-bit load are separate wavefronts, so no conflicts),
-//   bytes 128..255: 32 replicas of the half2 levels of the two 4-bit codes; lane l reads
-//                   replica l (4-byte load, conflict-free).
+//   bytes   0..127: 32 replicas of the half2 levels of the two 3-bit K codes of turbo_prod,
+//   bytes 128..255: 32 replicas of the half2 levels of the two 4-bit codes;
+// lane l reads replica l with a 4-byte load, so every lookup is one conflict-free wavefront.
+// Shared-memory bandwidth is 4 operand bytes per lane per wavefront whatever the access width,
+// which is why the +-1 residual-sign operands are not looked up: they cost two logic-pipe
+// operations per pair (see sign_pairs), a lookup would double the K lookups' wavefronts.
 // The address is one byte permute: byte 1 = the code byte, byte 0 = the lane's replica offset.
 constexpr int kLutBytes = 256 * 256;
 
@@ -333,19 +334,25 @@ __device__ __forceinline__ void build_operand_lut(uint8_t* lut) {
         const uint32_t row = i >> 1, part = i & 1;
         const uint32_t n0 = row & 15u, n1 = row >> 4;
         const uint32_t lv3 = level3_bits(n0) | (level3_bits(n1) << 16);
-        const uint32_t sg = ((n0 & 8u) ? 0x3C00u : 0xBC00u) | ((n1 & 8u) ? 0x3C000000u : 0xBC000000u);
         const uint32_t lv4 = level4_bits(n0) | (level4_bits(n1) << 16);
         uint4* dk = reinterpret_cast<uint4*>(lut + row * 256 + part * 64);
         uint4* dv = reinterpret_cast<uint4*>(lut + row * 256 + 128 + part * 64);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            dk[k] = make_uint4(lv3, sg, lv3, sg);
+            dk[k] = make_uint4(lv3, lv3, lv3, lv3);
             dv[k] = make_uint4(lv4, lv4, lv4, lv4);
         }
     }
 }
-__device__ __forceinline__ uint2 lut_k(const uint8_t* lut, uint32_t word, uint32_t lane_k, uint32_t sel) {
-    return *reinterpret_cast<const uint2*>(lut + prmt(word, lane_k, sel));
+// Residual-sign bits of one code word (bit 3 of every nibble) -> four half2 of +-1.0, pair p =
+// nibbles 2p, 2p+1 (the pairing of the table lookups): a permute puts byte p of w << 4 under
+// bit 15 and byte p of w under bit 31, one logic op keeps those two bits and adds 1.0.
+__device__ __forceinline__ void sign_pairs(uint32_t w, uint32_t (&out)[4]) {
+    const uint32_t ws = shl_mul<4>(w);
+    out[0] = lop3_and_xor(prmt(ws, w, 0x4400u), 0x80008000u, 0xBC00BC00u);
+    out[1] = lop3_and_xor(prmt(ws, w, 0x5511u), 0x80008000u, 0xBC00BC00u);
+    out[2] = lop3_and_xor(prmt(ws, w, 0x6622u), 0x80008000u, 0xBC00BC00u);
+    out[3] = lop3_and_xor(prmt(ws, w, 0x7733u), 0x80008000u, 0xBC00BC00u);
 }
 __device__ __forceinline__ uint32_t lut_v(const uint8_t* lut, uint32_t word, uint32_t lane_v, uint32_t sel) {
     return *reinterpret_cast<const uint32_t*>(lut + prmt(word, lane_v, sel));
@@ -383,17 +390,23 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
     if constexpr (LUT) {
         // MMA n covers bytes 2n, 2n+1 of this lane's 16 code bytes: dims 32 tig + 4n + {0,1 | 2,3}
+        uint32_t sg0[4], sg1[4];
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             const int wi = n >> 1;
             const uint32_t sa = (n & 1) ? 0x5524u : 0x5504u, sb = (n & 1) ? 0x5534u : 0x5514u;
             if (PROD) {
-                const uint2 e00 = lut_k(c.lut, kw0[wi], c.lane_k, sa);
-                const uint2 e10 = lut_k(c.lut, kw1[wi], c.lane_k, sa);
-                const uint2 e01 = lut_k(c.lut, kw0[wi], c.lane_k, sb);
-                const uint2 e11 = lut_k(c.lut, kw1[wi], c.lane_k, sb);
-                mma16816(s1, e00.x, e10.x, e01.x, e11.x, qf[n][0], qf[n][1]);
-                mma16816(s2, e00.y, e10.y, e01.y, e11.y, qf[n][0], qf[n][1]);
+                const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_k, sa);
+                const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_k, sa);
+                const uint32_t e01 = lut_v(c.lut, kw0[wi], c.lane_k, sb);
+                const uint32_t e11 = lut_v(c.lut, kw1[wi], c.lane_k, sb);
+                mma16816(s1, e00, e10, e01, e11, qf[n][0], qf[n][1]);
+                if ((n & 1) == 0) {
+                    sign_pairs(kw0[wi], sg0);
+                    sign_pairs(kw1[wi], sg1);
+                }
+                mma16816(s2, sg0[2 * (n & 1)], sg1[2 * (n & 1)], sg0[2 * (n & 1) + 1],
+                         sg1[2 * (n & 1) + 1], qf[n][0], qf[n][1]);
             } else {
                 const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_v, sa);
                 const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_v, sa);
@@ -628,7 +641,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     ctx.warp_smem = warp_smem;
     ctx.warp_smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
     ctx.lut = nullptr;
-    ctx.lane_k = static_cast<uint32_t>(lane & 15) * 8u;
+    ctx.lane_k = static_cast<uint32_t>(lane) * 4u;
     ctx.lane_v = 128u + static_cast<uint32_t>(lane) * 4u;
     ctx.group_smem = group_smem;
     ctx.bar_id = bar_id;
@@ -819,7 +832,23 @@ decode_paged16_kernel(DecodeParams p) {
     const uint32_t ring_addr = ctx.warp_smem_addr;
     // loop-constant source offsets inside a page
     const uint32_t k_off = p.geo.k_codes + ((g * H + h) << 6) + (tig << 4);          // row g; row g+8: +512H
-    const uint32_t v_off = p.geo.v_codes + ((2 * tig * H + h) << 6) + (g << 3);      // row 2tig
+    // V travels in 16-byte pieces (token t, chunk c of 4): an 8-byte copy costs the load/store
+    // unit as many wavefronts as a 16-byte one.  Piece (t, c) lands where the later 8-byte
+    // fragment reads (lane (g, tig): chunk g/2, half g%2 of tokens 2tig + {0, 1, 8, 9}) are
+    // conflict-free: the four tokens of one read instruction differ in (t >> 1) & 3.
+    auto v_piece = [](int t, int c) {
+        return 1024 + 128 * ((t & 1) + 2 * (t >> 3) + 4 * (c >> 1)) + 32 * ((t >> 1) & 3) + 16 * (c & 1);
+    };
+    uint32_t v_src[2], v_dst[2], v_rd[4];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int i = lane + 32 * k, t = i >> 2, c = i & 3;
+        v_src[k] = p.geo.v_codes + ((t * H + h) << 6) + (c << 4);
+        v_dst[k] = v_piece(t, c);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v_rd[j] = v_piece(2 * tig + (j & 1) + 8 * (j >> 1), g >> 1) + 8 * (g & 1);
     // scale regions (16*H fp16 each) are copied in 16-byte pieces spread over the lanes
     constexpr int kPiecesPerRegion = 2 * H;
     constexpr int kRegions = PROD ? 3 : 2;
@@ -854,13 +883,10 @@ decode_paged16_kernel(DecodeParams p) {
             const int page = __shfl_sync(0xffffffffu, ids, it - ids_base);
             const uint8_t* src = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
             const uint8_t* ks = src + k_off;
-            const uint8_t* vs = src + v_off;
             cp_async16(dst + lane * 16, ks);
             cp_async16(dst + 512 + lane * 16, ks + 512 * H);
-            cp_async8(dst + 1024 + lane * 8, vs);
-            cp_async8(dst + 1280 + lane * 8, vs + 64 * H);
-            cp_async8(dst + 1536 + lane * 8, vs + 512 * H);
-            cp_async8(dst + 1792 + lane * 8, vs + 576 * H);
+            cp_async16(dst + v_dst[0], src + v_src[0]);
+            cp_async16(dst + v_dst[1], src + v_src[1]);
             if (sc_on[0]) cp_async16(dst + sc_dst[0], src + sc_src[0]);
             if (kRegions * kPiecesPerRegion > 32 && sc_on[1]) cp_async16(dst + sc_dst[1], src + sc_src[1]);
         }
@@ -884,7 +910,7 @@ decode_paged16_kernel(DecodeParams p) {
         cur.k1 = *reinterpret_cast<const uint4*>(stg + 512 + lane * 16);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-            cur.v[i] = *reinterpret_cast<const uint2*>(stg + 1024 + 256 * i + lane * 8);
+            cur.v[i] = *reinterpret_cast<const uint2*>(stg + v_rd[i]);
         const uint8_t* sc = stg + kStageCodeBytes + s_idx;
         auto ld = [&](uint32_t off) {
             return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(sc + off)));
