@@ -335,11 +335,17 @@ __device__ __forceinline__ void build_operand_lut(uint8_t* lut) {
         const uint32_t n0 = row & 15u, n1 = row >> 4;
         const uint32_t lv3 = level3_bits(n0) | (level3_bits(n1) << 16);
         const uint32_t lv4 = level4_bits(n0) | (level4_bits(n1) << 16);
+        const uint32_t sgn = ((n0 & 8u) ? 0x3C00u : 0xBC00u) | ((n1 & 8u) ? 0x3C000000u : 0xBC000000u);
+        (void)sgn;
         uint4* dk = reinterpret_cast<uint4*>(lut + row * 256 + part * 64);
         uint4* dv = reinterpret_cast<uint4*>(lut + row * 256 + 128 + part * 64);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
+#ifdef TQ_SIGN_LUT
+            dk[k] = make_uint4(lv3, sgn, lv3, sgn);
+#else
             dk[k] = make_uint4(lv3, lv3, lv3, lv3);
+#endif
             dv[k] = make_uint4(lv4, lv4, lv4, lv4);
         }
     }
@@ -395,6 +401,17 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         for (int n = 0; n < 8; ++n) {
             const int wi = n >> 1;
             const uint32_t sa = (n & 1) ? 0x5524u : 0x5504u, sb = (n & 1) ? 0x5534u : 0x5514u;
+#ifdef TQ_SIGN_LUT
+            if (PROD) {
+                const uint32_t lk = (c.lane_k & 0x3Cu) << 1;  // (lane % 16) * 8
+                const uint2 e00 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw0[wi], lk, sa));
+                const uint2 e10 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw1[wi], lk, sa));
+                const uint2 e01 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw0[wi], lk, sb));
+                const uint2 e11 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw1[wi], lk, sb));
+                mma16816(s1, e00.x, e10.x, e01.x, e11.x, qf[n][0], qf[n][1]);
+                mma16816(s2, e00.y, e10.y, e01.y, e11.y, qf[n][0], qf[n][1]);
+            } else
+#endif
             if (PROD) {
                 const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_k, sa);
                 const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_k, sa);

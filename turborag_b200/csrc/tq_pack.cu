@@ -18,75 +18,95 @@ constexpr int kCodeRowBytes = 72;  // 64 code bytes + pad: rows land on distinct
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 
-// ---- nearest-level search through bank-replicated shared tables ---------------------------
-// The threshold search is the kernel's largest cost and runs on the half-rate integer/compare
-// pipe, while the load/store pipe is mostly idle.  |x| (clamped) is cut into 16 cells of
-// width 3/16; each cell holds at most one decision threshold, so a table entry (threshold
-// inside the cell or +inf, code below it) plus ONE compare gives the exact code.  Entries
-// exist per sign class (the thresholds of the negative half differ by an ulp where an exact
-// fp32 tie exists) and are replicated over the 32 lanes, so lookups never conflict.
+// ---- nearest-level search through replicated shared tables --------------------------------
+// The reference scans the levels for the smallest distance (first index wins ties).  That is
+// the same as counting the decision thresholds that are <= x, where the thresholds are exact
+// fp32 numbers: M_j on the positive side, TMID at the centre and, on the negative side, the
+// float just above -N_j (there the scan moves up for x > -N_j).  x * 16/3 + magic rounds x to
+// a cell of width 3/16 in the low mantissa bits; thresholds are further apart than that, so a
+// cell holds at most one.  A table row per cell gives (threshold in the cell or +inf, number
+// of thresholds below the cell): code = base + (x >= threshold) -- one fma, two integer ops,
+// one load, one compare, one add, and no sign handling.  Rows are 128 bytes of replicas: 16
+// x 8 bytes for the 4-bit table (the two half-warps of a 64-bit load are separate wavefronts),
+// 8 x 16 bytes for the 3-bit table, so no lookup ever conflicts.
 constexpr float kCellScale = 16.0f / 3.0f;
-constexpr float kCellMagic = 8388608.0f;  // 2^23: the fma's low mantissa bits are round(|x| * scale)
-constexpr float kCellClamp = 2.8125f;     // 15 cells
+constexpr int kCellsV = 128, kCellsK = 32;          // |x| <= sqrt(128) -> |cell| <= 61; K is clamped to 2.5
+constexpr float kMagicV = 8388608.0f + 64.0f;       // low 7 mantissa bits = cell + 64
+constexpr float kMagicK = 8388608.0f + 16.0f;       // low 5 mantissa bits = cell + 16
+constexpr int kLutRowBytes = 128;
 
-struct CellInfo {
-    float t;   // threshold inside the cell, +inf if none
-    int base;  // thresholds below the cell
-};
-template <int N>
-__device__ __forceinline__ CellInfo cell_info(const float (&thr)[N], int cell) {
-    CellInfo c{__int_as_float(0x7f800000), 0};
+__device__ __forceinline__ uint32_t cell_v(float x) {
+    return __float_as_uint(__fmaf_rn(x, kCellScale, kMagicV)) & (kCellsV - 1);
+}
+__device__ __forceinline__ uint32_t cell_k(float x) {
+    return __float_as_uint(__fmaf_rn(x, kCellScale, kMagicK)) & (kCellsK - 1);
+}
+__device__ __forceinline__ float next_up_of_negated(float n) {  // smallest float above -n, n > 0
+    return -__uint_as_float(__float_as_uint(n) - 1u);
+}
+
+// lutV row c: 16 x (threshold, code below it); lutK row c: 8 x (threshold, level below, level
+// above, code below).
+__device__ void build_luts(uint8_t* lutK, uint8_t* lutV, bool need_k) {
+    const float v4[15] = {next_up_of_negated(TQ_V4_N7), next_up_of_negated(TQ_V4_N6),
+                          next_up_of_negated(TQ_V4_N5), next_up_of_negated(TQ_V4_N4),
+                          next_up_of_negated(TQ_V4_N3), next_up_of_negated(TQ_V4_N2),
+                          next_up_of_negated(TQ_V4_N1), TQ_TMID, TQ_V4_M1, TQ_V4_M2, TQ_V4_M3,
+                          TQ_V4_M4, TQ_V4_M5, TQ_V4_M6, TQ_V4_M7};
+    const float k3[7] = {next_up_of_negated(TQ_K3_N3), next_up_of_negated(TQ_K3_N2),
+                         next_up_of_negated(TQ_K3_N1), TQ_TMID, TQ_K3_M1, TQ_K3_M2, TQ_K3_M3};
+    const float lv3[8] = {-TQ_C3_3, -TQ_C3_2, -TQ_C3_1, -TQ_C3_0, TQ_C3_0, TQ_C3_1, TQ_C3_2, TQ_C3_3};
+    const float inf = __int_as_float(0x7f800000);
+    for (int c = threadIdx.x; c < kCellsV; c += blockDim.x) {
+        float t = inf;
+        int base = 0;
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-        const int cj = __float2int_rn(thr[j] * kCellScale);
-        if (cj < cell) ++c.base;
-        if (cj == cell) c.t = thr[j];
-    }
-    return c;
-}
-
-// lutV[(sign*16 + cell)*32 + lane] = (threshold, code if below it; +1 when (above == positive))
-// lutK[...]                       = (threshold, level below, level above, code as for lutV)
-__device__ void build_luts(float4* lutK, float2* lutV, bool need_k) {
-    const float k3m[3] = {TQ_K3_M1, TQ_K3_M2, TQ_K3_M3}, k3n[3] = {TQ_K3_N1, TQ_K3_N2, TQ_K3_N3};
-    const float v4m[7] = {TQ_V4_M1, TQ_V4_M2, TQ_V4_M3, TQ_V4_M4, TQ_V4_M5, TQ_V4_M6, TQ_V4_M7};
-    const float v4n[7] = {TQ_V4_N1, TQ_V4_N2, TQ_V4_N3, TQ_V4_N4, TQ_V4_N5, TQ_V4_N6, TQ_V4_N7};
-    const float lv3[4] = {TQ_C3_0, TQ_C3_1, TQ_C3_2, TQ_C3_3};
-    for (int i = threadIdx.x; i < 2 * 16 * 32; i += blockDim.x) {
-        const int cell = (i >> 5) & 15;
-        const bool neg = (i >> 9) != 0;
-        const CellInfo v = neg ? cell_info(v4n, cell) : cell_info(v4m, cell);
-        lutV[i] = make_float2(v.t, __int_as_float(neg ? 6 - v.base : 8 + v.base));
-        if (need_k) {
-            const CellInfo k = neg ? cell_info(k3n, cell) : cell_info(k3m, cell);
-            const int hi = k.base < 3 ? k.base + 1 : 3;
-            lutK[i] = make_float4(k.t, lv3[k.base], lv3[hi], __int_as_float(neg ? 2 - k.base : 4 + k.base));
+        for (int j = 0; j < 15; ++j) {
+            const int cj = static_cast<int>(cell_v(v4[j]));
+            if (cj < c) ++base;
+            if (cj == c) t = v4[j];
         }
+        float2* row = reinterpret_cast<float2*>(lutV + c * kLutRowBytes);
+        for (int r = 0; r < 16; ++r) row[r] = make_float2(t, __int_as_float(base));
     }
-}
-
-__device__ __forceinline__ uint32_t cell_index(float a, float x) {
-    const float u = __fmaf_rn(a, kCellScale, kCellMagic);
-    return (__float_as_uint(u) & 31u) + (x >= TQ_TMID ? 0u : 16u);
+    if (!need_k) return;
+    for (int c = threadIdx.x; c < kCellsK; c += blockDim.x) {
+        float t = inf;
+        int base = 0;
+#pragma unroll
+        for (int j = 0; j < 7; ++j) {
+            const int cj = static_cast<int>(cell_k(k3[j]));
+            if (cj < c) ++base;
+            if (cj == c) t = k3[j];
+        }
+        float lo = lv3[0], hi = lv3[0];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (j == base) lo = lv3[j];
+            if (j == (base < 7 ? base + 1 : 7)) hi = lv3[j];
+        }
+        float4* row = reinterpret_cast<float4*>(lutK + c * kLutRowBytes);
+        for (int r = 0; r < 8; ++r) row[r] = make_float4(t, lo, hi, __int_as_float(base));
+    }
 }
 
 // 4-bit code (nearest_v4_idx / nearest_codebook_idx of the reference), exact.
-__device__ __forceinline__ uint32_t quant_v4_lut(float x, const float2* lutV, int lane) {
-    const float a = fabsf(x);
-    const bool pos = x >= TQ_TMID;
-    const float2 e = lutV[cell_index(fminf(a, kCellClamp), x) * 32 + lane];
-    return __float_as_uint(e.y) + (((a >= e.x) == pos) ? 1u : 0u);
+// `rep` = (lane % 16) * 8, this lane's replica inside a row.
+__device__ __forceinline__ uint32_t quant_v4_lut(float x, const uint8_t* lutV, uint32_t rep) {
+    const uint32_t u = __float_as_uint(__fmaf_rn(x, kCellScale, kMagicV));
+    const float2 e = *reinterpret_cast<const float2*>(lutV + (((u << 7) & ((kCellsV - 1) << 7)) | rep));
+    return __float_as_uint(e.y) + (x >= e.x ? 1u : 0u);
 }
 
 // K nibble = residual sign << 3 | 3-bit code, and the residual e = clamp(kn) - level.
-__device__ __forceinline__ uint32_t quant_k3_lut(float kn, const float4* lutK, int lane, float& e) {
-    const float a = fminf(fabsf(kn), 2.5f);  // |clamp(kn, -2.5, 2.5)|
-    const bool pos = kn >= TQ_TMID;
-    const float4 t = lutK[cell_index(a, kn) * 32 + lane];
-    const bool above = a >= t.x;
-    const float lvl = above ? t.z : t.y;
-    e = __fadd_rn(copysignf(a, kn), pos ? -lvl : lvl);
-    return (__float_as_uint(t.w) + ((above == pos) ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
+// `rep` = (lane % 8) * 16.
+__device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK, uint32_t rep, float& e) {
+    const float xc = fminf(fmaxf(kn, -2.5f), 2.5f);
+    const uint32_t u = __float_as_uint(__fmaf_rn(xc, kCellScale, kMagicK));
+    const float4 t = *reinterpret_cast<const float4*>(lutK + (((u << 7) & ((kCellsK - 1) << 7)) | rep));
+    const bool above = xc >= t.x;
+    e = __fsub_rn(xc, above ? t.z : t.y);
+    return (__float_as_uint(t.w) + (above ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
 }
 
 // Move a row's 64 code bytes from "lane l' holds byte l'+8j" to "lane l holds
@@ -118,12 +138,13 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, int head_dim, long long num_rows, int pool_aligned8) {
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
-    __shared__ __align__(16) float4 lutK[PROD ? 2 * 16 * 32 : 1];
-    __shared__ __align__(16) float2 lutV[2 * 16 * 32];
+    __shared__ __align__(128) uint8_t lutK[PROD ? kCellsK * kLutRowBytes : 16];
+    __shared__ __align__(128) uint8_t lutV[kCellsV * kLutRowBytes];
     build_luts(lutK, lutV, PROD);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rr = lane >> 3, l = lane & 7;
+    const uint32_t rep_v = (lane & 15) * 8, rep_k = (lane & 7) * 16;
     float* buf = xchg[warp];
     uint8_t* code_buf = reinterpret_cast<uint8_t*>(buf);
     const int H = geo.num_kv_heads;
@@ -173,8 +194,8 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             for (int j = 0; j < 8; ++j) {
                 float e0, e1;
                 const float2 kn = div_by2(y[j], krms, kr);
-                const uint32_t n0 = quant_k3_lut(kn.x, lutK, lane, e0);
-                const uint32_t n1 = quant_k3_lut(kn.y, lutK, lane, e1);
+                const uint32_t n0 = quant_k3_lut(kn.x, lutK, rep_k, e0);
+                const uint32_t n1 = quant_k3_lut(kn.y, lutK, rep_k, e1);
                 kbytes[j] = n0 | (n1 << 4);
                 const float2 e = make_float2(e0, e1);
                 e2[j] = mul2(e, e);
@@ -194,7 +215,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float2 kn = div_by2(y[j], krms, kr);
-                kbytes[j] = quant_v4_lut(kn.x, lutV, lane) | (quant_v4_lut(kn.y, lutV, lane) << 4);
+                kbytes[j] = quant_v4_lut(kn.x, lutV, rep_v) | (quant_v4_lut(kn.y, lutV, rep_v) << 4);
             }
             if (valid && l == 0)
                 *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
@@ -226,7 +247,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float2 vn = div_by2(y[j], vrms, vr);
-            vbytes[j] = quant_v4_lut(vn.x, lutV, lane) | (quant_v4_lut(vn.y, lutV, lane) << 4);
+            vbytes[j] = quant_v4_lut(vn.x, lutV, rep_v) | (quant_v4_lut(vn.y, lutV, rep_v) << 4);
         }
         if (valid && l == 0)
             *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
