@@ -210,6 +210,10 @@ int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_pool,
                          const tq_half* chunk_value, tq_half* output,
                          const TQTurbomsePageLayout* layout, const TQConfig* cfg, int batch,
                          int num_q_tokens, int num_q_heads, tq_stream_t stream);
+/* Status word of the prefill kernel on the current device (synchronises it): 0 when no bounded
+ * wait inside the kernel ever ran out, else the code of the wait that did (results of that
+ * launch are then undefined); negative on a CUDA error.  No reference counterpart. */
+int tq_mse_prefill_status(void);
 
 /* Host-side page allocator and block table (LIFO free list and the slot
  * formula of src/tq_allocator.cpp:5-31, src/tq_block_table.cpp:7-39; the pool

@@ -430,3 +430,4 @@ def test_mse_prefill_vs_oracle(tq, oracle, dev, hq, h, nq, lens, with_chunk):
         err = rowwise_rel_err(mine[i], ref)
         print(f"prefill b={i} n={n} nq={nq}: rel err {err:.2e}")
         assert err < ATTN_TOL
+    assert tq.mse_prefill_status() == 0, "a bounded wait inside the prefill kernel ran out"

@@ -4,6 +4,7 @@
 // arguments -> -1, any failure in a launch helper -> -2 with the text kept in a
 // thread-local buffer returned by tq_last_error(), no C++ exception ever
 // crosses the boundary, no synchronisation.
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include <climits>
@@ -413,10 +414,18 @@ extern "C" int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_po
         if (batch < 0 || num_q_tokens < 0 || num_q_heads < 1 || table_stride < 0)
             throw std::runtime_error("mse_prefill_paged: negative size");
         if (cfg->num_kv_heads > 8) throw std::runtime_error("mse_prefill_paged: num_kv_heads must be 1..8");
-        tq::launch_prefill(query, page_pool, block_tables, table_stride, seq_lens, chunk_key, chunk_value,
-                           output, geom_mse(*layout, *cfg), cfg->head_dim, batch, num_q_tokens,
-                           num_q_heads, table_stride * cfg->block_size, static_cast<cudaStream_t>(stream));
+        static const bool legacy = std::getenv("TQ_PREFILL_MMA_SYNC") != nullptr;
+        (legacy ? tq::launch_prefill : tq::launch_prefill_tc)(
+            query, page_pool, block_tables, table_stride, seq_lens, chunk_key, chunk_value, output,
+            geom_mse(*layout, *cfg), cfg->head_dim, batch, num_q_tokens, num_q_heads,
+            table_stride * cfg->block_size, static_cast<cudaStream_t>(stream));
     });
+}
+
+extern "C" int tq_mse_prefill_status(void) {
+    int v = -1;
+    const int rc = guarded([&] { v = tq::prefill_tc_status(); });
+    return rc != 0 ? rc : v;
 }
 
 // ---- host page allocator + block table -------------------------------------

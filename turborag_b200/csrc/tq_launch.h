@@ -70,5 +70,12 @@ void launch_prefill(const void* query, const uint8_t* pool, const int32_t* block
                     int table_stride, const int32_t* seq_lens, const void* chunk_key,
                     const void* chunk_value, void* output, const PageGeom& geo, int head_dim,
                     int batch, int nq, int hq, int max_prefix_tokens, cudaStream_t stream);
+// Same contract on the tcgen05 tensor cores; prefill_tc_status() returns the device status word
+// of that kernel (0 = no bounded wait ever ran out; synchronises the device).
+void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* block_tables,
+                       int table_stride, const int32_t* seq_lens, const void* chunk_key,
+                       const void* chunk_value, void* output, const PageGeom& geo, int head_dim,
+                       int batch, int nq, int hq, int max_prefix_tokens, cudaStream_t stream);
+int prefill_tc_status();
 
 }  // namespace tq

@@ -1,0 +1,603 @@
+// Chunked query prefill over a turbo_mse-compressed prefix plus a causal fp16 chunk on the
+// 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// The reference has no such kernel: its fused kernel (src/cuda/tq_turbo_mse_kernels.cu:302-417)
+// takes one query row per kv head and walks the tokens serially.  Here the rows (token, query
+// head) that share a kv head form the M dimension of a flash-attention tile loop; arithmetic
+// follows the reference's rotated-domain formulation (q' = R(q), logits <q', k'>/sqrt(D), V
+// accumulated in the rotated domain, inverse rotation in the merge kernel).
+//
+// One CTA = 128 query rows of one (sequence, kv head, prefix split), 9 warps in three roles:
+//   warps 0-3  softmax: thread i owns row i, which is TMEM lane i.  Per 64-token tile it reads its
+//              S row from TMEM (tcgen05.ld), applies the per-token K scale, the causal / length
+//              mask and the online softmax, and writes P * (V scale) as fp16 into a shared tile
+//              laid out as the A operand of the second product.  When a row maximum grows by more
+//              than 2^8 the O accumulator (TMEM) is rescaled in place (tcgen05.ld / st).
+//   warps 4-7  unpack: fetch the page bytes of the next tile (one tile ahead, in registers), turn
+//              every code byte into two fp16 operands with one shared-memory table lookup, and store
+//              K and V tiles in the 128-byte-swizzled canonical operand layout; chunk tiles (fp16,
+//              rotated by a pre-pass) are copied instead.
+//   warp 8     one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128: 8 instructions, A and
+//              B K-major) into one of two TMEM buffers, and O += P V (M 128, N 128, K 64: 4
+//              instructions, V as MN-major B operand) into TMEM; tcgen05.commit arrives on
+//              mbarriers.  S of tile j+1 is issued before P V of tile j, so the tensor pipe works
+//              on the next scores while the softmax warps work on the current ones.
+// Synchronisation is all mbarriers (two K/V stages, two S buffers, two P buffers); every wait is
+// bounded: after kWaitLimit polls a thread records a status code, stops working and goes to
+// the common exit, where the TMEM allocation is released.
+#include <climits>
+#include <cstring>
+
+#include "tq_common.cuh"
+#include "tq_launch.h"
+
+namespace tq {
+namespace {
+
+constexpr float kLog2eT = 1.4426950408889634f;
+constexpr float kLn2T = 0.6931471805599453f;
+constexpr int kTileTok = 64;
+constexpr int kRowsCta = 128;
+constexpr int kThreadsTc = 288;
+constexpr int kWaitLimit = 1 << 20;
+constexpr float kRescaleLag = 8.0f;  // log2 units a row maximum may run ahead of the one in use
+
+// shared-memory map (bytes); every operand tile starts on a 1024-byte boundary
+constexpr int kOffLut = 0;                      // 256 rows of 256 B: 32 replicas x half2 in the first 128 B
+constexpr int kOffQ = 65536;                    // [2 dim chunks][128 rows][128 B]
+constexpr int kOffKV = 98304;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
+constexpr int kOffP = 163840;                   // 2 x [128 rows][128 B]
+constexpr int kOffScale = 196608;               // kscale[2][64], vscale[2][64] (fp32)
+constexpr int kOffBar = kOffScale + 1024;       // mbarriers, TMEM base
+constexpr int kSmemTc = kOffBar + 128;
+
+// fp16(alpha4 * |level|) of the 4-bit codebook as byte pools (entries 0-3 | 4-7), and alpha4
+#define TQ_ALPHA4T TQF(0x404c9252)
+constexpr uint32_t kMagHiA = 0x42403c36u, kMagHiB = 0x48464544u, kMagLoA = 0x0633f691u, kMagLoB = 0x5e9d2c04u;
+
+__device__ __forceinline__ uint32_t level4_half_bits(uint32_t n) {
+    const uint32_t mag = n >= 8u ? n - 8u : 7u - n;
+    const uint32_t sh = 8u * (mag & 3u);
+    const uint32_t hi = ((mag < 4u ? kMagHiA : kMagHiB) >> sh) & 0xFFu;
+    const uint32_t lo = ((mag < 4u ? kMagLoA : kMagLoB) >> sh) & 0xFFu;
+    return (hi << 8) | lo | (n >= 8u ? 0u : 0x8000u);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint32_t prmt_t(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ float ex2_t(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Byte offset of 16-byte unit `unit` (0..7) of row `row` inside a [rows][128 B] operand chunk:
+// groups of 8 rows are 1024 bytes, the unit index is XOR-ed with row % 8 (128-byte swizzle).
+__device__ __forceinline__ uint32_t sw128(int row, int unit) {
+    return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 + ((unit ^ (row & 7)) << 4));
+}
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte units),
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) |
+           (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptors (kind::f16): fp32 accumulate, fp16 A/B, M = 128.
+constexpr uint32_t kIdescS = (1u << 4) | (8u << 17) | (8u << 24);                // N = 64, A and B K-major
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 16) | (16u << 17) | (8u << 24);  // N = 128, B MN-major
+
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait for the phase with the given parity to complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < kWaitLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// The same for a whole warp: every lane gets the same answer, so warp-collective instructions
+// that follow are executed by all lanes or by none.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    uint32_t r[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+// Status word of the last prefill launches on this device: 0 = every wait was satisfied.
+__device__ int g_prefill_tc_status = 0;
+
+// ---- pre-pass: R(x) * scale for fp16 rows of 128, natural dim order --------------------------
+__global__ void __launch_bounds__(128)
+rotate_rows_tc_kernel(const __half* __restrict__ src, __half* __restrict__ dst, long long rows,
+                      int heads_mod, int group, float scale, int head_dim) {
+    const int lane = threadIdx.x & 31;
+    const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int h = static_cast<int>(row % heads_mod) / group;
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src + row * kHeadDim) + lane);
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    float x[4];
+    const float a0 = f0.x - f0.y, a1 = f0.x + f0.y, a2 = f1.x - f1.y, a3 = f1.x + f1.y;
+    x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float o = __shfl_xor_sync(0xffffffffu, x[e], m);
+            x[e] = (lane & m) ? o - x[e] : x[e] + o;
+        }
+    }
+    const float c = inv_sqrt_dim(head_dim);
+    const float sc = ((h & 1) ? -c : c) * scale;
+    __half2* out = reinterpret_cast<__half2*>(dst + row * kHeadDim + 4 * lane);
+    out[0] = __floats2half2_rn(x[0] * sc, x[1] * sc);
+    out[1] = __floats2half2_rn(x[2] * sc, x[3] * sc);
+}
+
+struct PrefillTcParams {
+    const __half* q_rot;      // [B, Nq, Hq, 128] rotated, scaled
+    const __half* ck_rot;     // [B, Nq, H, 128] or nullptr
+    const __half* cv_rot;
+    const uint8_t* pool;
+    const int32_t* block_tables;
+    const int32_t* seq_lens;
+    float* partials;          // [B*Nq, splits, Hq, 130]
+    PageGeom geo;
+    int table_stride, nq, hq, groups, splits;
+};
+
+__global__ void __launch_bounds__(kThreadsTc, 1)
+prefill_tc_kernel(PrefillTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = p.geo.num_kv_heads, G = p.groups;
+    const int mt = blockIdx.x;
+    const int h = blockIdx.y % H, split = blockIdx.y / H;
+    const int b = blockIdx.z;
+    const int rows_total = p.nq * G;
+
+    // barriers: kv_full[2] (128 arrivals), s_full[2] (1), p_full[2] (128), pv_done[2] (1): the
+    // barrier with index j % 2 serves tile j, its phase number is j / 2
+    const uint32_t bar0 = sbase + kOffBar;
+    const uint32_t bar_kv_full = bar0, bar_s_full = bar0 + 16, bar_p_full = bar0 + 32, bar_pv_done = bar0 + 48;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 96);
+
+    // ---- tile schedule of this CTA (identical in every role) ----
+    const int n_prefix = __ldg(p.seq_lens + b);
+    const int prefix_tiles = (n_prefix + kTileTok - 1) / kTileTok;
+    const int per = (prefix_tiles + p.splits - 1) / p.splits;
+    const int tile_lo = split * per, tile_hi = min(prefix_tiles, tile_lo + per);
+    const int n_pref = max(tile_hi - tile_lo, 0);
+    const int last_tok = min((mt * kRowsCta + kRowsCta - 1) / G, p.nq - 1);
+    const int chunk_tiles = (p.ck_rot && split == p.splits - 1) ? last_tok / kTileTok + 1 : 0;
+    const int n_tiles = n_pref + chunk_tiles;
+
+    // ---- set-up: table, Q tile, barriers, TMEM ----
+    for (int i = tid; i < 256 * 8; i += kThreadsTc) {
+        const uint32_t row = i >> 3, n0 = row & 15u, n1 = row >> 4;
+        const uint32_t e = level4_half_bits(n0) | (level4_half_bits(n1) << 16);
+        *reinterpret_cast<uint4*>(smem + kOffLut + row * 256 + (i & 7) * 16) = make_uint4(e, e, e, e);
+    }
+    for (int i = tid; i < kRowsCta * 16; i += kThreadsTc) {
+        const int r = i >> 4, u = i & 15;
+        const int rg = min(mt * kRowsCta + r, rows_total - 1);
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+            p.q_rot + ((static_cast<long long>(b) * p.nq + rg / G) * p.hq + h * G + rg % G) * kHeadDim) + u);
+        *reinterpret_cast<uint4*>(smem + kOffQ + (u >> 3) * 16384 + sw128(r, u & 7)) = v;
+    }
+    fence_async_smem();
+    if (tid == 0) {
+        mbar_init(bar_kv_full, 128);
+        mbar_init(bar_kv_full + 8, 128);
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_s_full + 8, 1);
+        mbar_init(bar_p_full, 128);
+        mbar_init(bar_p_full + 8, 128);
+        mbar_init(bar_pv_done, 1);
+        mbar_init(bar_pv_done + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;          // columns 0-63 / 64-127: S buffers, 128-255: O
+    const uint32_t tmem_o = tmem + 128;
+    int fail = 0;
+
+    if (warp >= 4 && warp < 8) {
+        // =========================== unpack warps ===========================
+        const int u = tid - 128;
+        const int ut = u & 63, uh = u >> 6;   // token of the tile, 32-byte half of its 64 code bytes
+        const uint32_t lane_v = static_cast<uint32_t>(lane) * 4u;
+        const int32_t* table = p.block_tables + static_cast<long long>(b) * p.table_stride;
+        struct Raw {
+            uint4 k0, k1, v0, v1;
+            float ks, vs;
+        } raw;
+        raw.k0 = raw.k1 = raw.v0 = raw.v1 = make_uint4(0u, 0u, 0u, 0u);
+        raw.ks = raw.vs = 0.0f;
+        auto fetch = [&](int it) {
+            if (it >= n_pref) return;
+            const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
+            const int page = __ldg(table + (t >> 4));
+            const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
+            const unsigned th = static_cast<unsigned>((t & 15) * H + h);
+            const uint4* kc = reinterpret_cast<const uint4*>(pg + p.geo.k_codes + th * 64 + 32 * uh);
+            const uint4* vc = reinterpret_cast<const uint4*>(pg + p.geo.v_codes + th * 64 + 32 * uh);
+            raw.k0 = __ldg(kc);
+            raw.k1 = __ldg(kc + 1);
+            raw.v0 = __ldg(vc);
+            raw.v1 = __ldg(vc + 1);
+            if (uh == 0) {
+                raw.ks = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.k_scales + th * 2))));
+                raw.vs = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.v_scales + th * 2))));
+            }
+        };
+        // one code word (8 codes) -> 8 fp16 operands = one 16-byte unit
+        auto unpack_word = [&](uint32_t w) {
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5504u));
+            o.y = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5514u));
+            o.z = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5524u));
+            o.w = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5534u));
+            return o;
+        };
+        fetch(0);
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it & 1;
+            if (it >= 2 && !warp_wait(bar_pv_done + 8 * st, ((it >> 1) - 1) & 1)) { fail = 1; break; }
+            uint8_t* ktile = smem + kOffKV + st * 32768;
+            uint8_t* vtile = ktile + 16384;
+            float* kscale = reinterpret_cast<float*>(smem + kOffScale) + st * 64;
+            float* vscale = kscale + 128;
+            if (it < n_pref) {
+                const uint32_t kw[8] = {raw.k0.x, raw.k0.y, raw.k0.z, raw.k0.w, raw.k1.x, raw.k1.y, raw.k1.z, raw.k1.w};
+                const uint32_t vw[8] = {raw.v0.x, raw.v0.y, raw.v0.z, raw.v0.w, raw.v1.x, raw.v1.y, raw.v1.z, raw.v1.w};
+                const float ks = raw.ks, vs = raw.vs;
+                const int t0 = (tile_lo + it) * kTileTok;
+                fetch(it + 1);  // next tile's bytes travel while this one is unpacked
+#pragma unroll
+                for (int wi = 0; wi < 8; ++wi) {
+                    // unit 8 uh + wi of the 16 of a row: dim chunk uh, unit wi inside the chunk
+                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = unpack_word(kw[wi]);
+                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = unpack_word(vw[wi]);
+                }
+                if (uh == 0) {
+                    const bool ok = t0 + ut < n_prefix;
+                    kscale[ut] = ok ? ks : 0.0f;
+                    vscale[ut] = ok ? vs * (1.0f / TQ_ALPHA4T) : 0.0f;
+                }
+            } else {
+                const int t0 = (it - n_pref) * kTileTok;
+                const int t = min(t0 + ut, p.nq - 1);
+                const long long rowi = (static_cast<long long>(b) * p.nq + t) * H + h;
+                const uint4* ks = reinterpret_cast<const uint4*>(p.ck_rot + rowi * kHeadDim) + 8 * uh;
+                const uint4* vs = reinterpret_cast<const uint4*>(p.cv_rot + rowi * kHeadDim) + 8 * uh;
+#pragma unroll
+                for (int wi = 0; wi < 8; ++wi) {
+                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = __ldg(ks + wi);
+                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = __ldg(vs + wi);
+                }
+                if (uh == 0) {
+                    const bool ok = t0 + ut < p.nq;
+                    kscale[ut] = ok ? 1.0f : 0.0f;
+                    vscale[ut] = ok ? 1.0f / TQ_ALPHA4T : 0.0f;
+                }
+            }
+            fence_async_smem();
+            mbar_arrive(bar_kv_full + 8 * st);
+        }
+    } else if (warp == 8) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) {
+            const uint32_t q_addr = sbase + kOffQ;
+            auto issue_s = [&](int it) {
+                const int st = it & 1;
+                if (!mbar_wait(bar_kv_full + 8 * st, (it >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = sbase + kOffKV + st * 32768;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_f16_ss(tmem + 64 * (it & 1),
+                               make_desc(q_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                               make_desc(k_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS, ks > 0);
+                mma_commit(bar_s_full + 8 * (it & 1));
+                return true;
+            };
+            if (n_tiles > 0 && !issue_s(0)) fail = 2;
+            for (int it = 0; it < n_tiles && !fail; ++it) {
+                if (it + 1 < n_tiles && !issue_s(it + 1)) { fail = 2; break; }
+                if (!mbar_wait(bar_p_full + 8 * (it & 1), (it >> 1) & 1)) { fail = 3; break; }
+                tc_fence_after();
+                const uint32_t p_addr = sbase + kOffP + (it & 1) * 16384;
+                const uint32_t v_addr = sbase + kOffKV + (it & 1) * 32768 + 16384;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_f16_ss(tmem_o, make_desc(p_addr + ks * 32, 16, 1024),
+                               make_desc(v_addr + ks * 2048, 8192, 1024), kIdescPV, (it > 0 || ks > 0) ? 1u : 0u);
+                mma_commit(bar_pv_done + 8 * (it & 1));
+            }
+        }
+    } else {
+        // =========================== softmax warps ===========================
+        const int r = tid;                               // row of the tile = TMEM lane
+        const int rg = mt * kRowsCta + r;                // row of this (sequence, kv head)
+        const int tok = min(rg, rows_total - 1) / G;     // chunk position of the row's token
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        float m_use = kInitMaxLogit, l_run = 0.0f;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it & 1;
+            const bool is_chunk = it >= n_pref;
+            const int t0 = is_chunk ? (it - n_pref) * kTileTok : (tile_lo + it) * kTileTok;
+            const int n_valid = is_chunk ? p.nq : n_prefix;
+            if (!warp_wait(bar_s_full + 8 * st, (it >> 1) & 1)) { fail = 4; break; }
+            tc_fence_after();
+            const float* kscale = reinterpret_cast<const float*>(smem + kOffScale) + st * 64;
+            const float* vscale = kscale + 128;
+            float s[64];
+            {
+                float part[32];
+                tmem_ld32(tmem + lane_base + 64 * st, part);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s[j] = part[j];
+                tmem_ld32(tmem + lane_base + 64 * st + 32, part);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
+            }
+            const bool need_mask = is_chunk || t0 + kTileTok > n_valid;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+                const float4 kc = *reinterpret_cast<const float4*>(kscale + j);
+                s[j] *= kc.x;
+                s[j + 1] *= kc.y;
+                s[j + 2] *= kc.z;
+                s[j + 3] *= kc.w;
+            }
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const int t = t0 + j;
+                    const bool ok = t < n_valid && (!is_chunk || t <= tok);
+                    if (!ok) s[j] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 64; ++j) mx = fmaxf(mx, s[j]);
+            // keep the maximum in use until the true one runs ahead by more than kRescaleLag
+            const float m_true = fmaxf(m_use, mx);
+            const bool grow = m_true > m_use + kRescaleLag || (it == 0);
+            const float m_new = grow ? m_true : m_use;
+            if (it > 0 && __any_sync(0xffffffffu, grow)) {
+                // O *= 2^(m_use - m_new): the previous P V must have landed first
+                if (!warp_wait(bar_pv_done + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1)) { fail = 5; break; }
+                tc_fence_after();
+                const float al = ex2_t(m_use - m_new);
+                l_run *= al;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_base + c0, o);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= al;
+                    tmem_st32(tmem_o + lane_base + c0, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            m_use = m_new;
+            float ls = 0.0f;
+            uint8_t* ptile = smem + kOffP + st * 16384;
+#pragma unroll
+            for (int u8 = 0; u8 < 8; ++u8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int j = 8 * u8 + 2 * k;
+                    const float p0 = ex2_t(s[j] - m_use), p1 = ex2_t(s[j + 1] - m_use);
+                    ls += p0 + p1;
+                    const float2 vc = *reinterpret_cast<const float2*>(vscale + j);
+                    const __half2 hh = __floats2half2_rn(p0 * vc.x, p1 * vc.y);
+                    w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(ptile + sw128(r, u8)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l_run += ls;
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p_full + 8 * st);
+        }
+        // ---- epilogue: the row's partial (acc, m in natural-log units, l) ----
+        if (!fail) {
+            float* out = nullptr;
+            if (rg < rows_total) {
+                const long long seq = static_cast<long long>(b) * p.nq + rg / G;
+                out = p.partials + ((seq * p.splits + split) * p.hq + h * G + rg % G) * TQ_PARTIAL_STRIDE;
+            }
+            if (n_tiles > 0) {
+                if (!warp_wait(bar_pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) fail = 6;
+                tc_fence_after();
+            }
+            if (!fail) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    float o[32];
+                    if (n_tiles > 0) {
+                        tmem_ld32(tmem_o + lane_base + c0, o);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o[j] = 0.0f;
+                    }
+                    if (out) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2)  // records are 520 bytes apart: 8-byte aligned only
+                            *reinterpret_cast<float2*>(out + c0 + j) = make_float2(o[j], o[j + 1]);
+                    }
+                }
+                if (out) {
+                    out[128] = m_use * kLn2T;
+                    out[129] = l_run;
+                }
+            }
+        }
+    }
+    if (fail) atomicMax(&g_prefill_tc_status, fail);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+}
+
+}  // namespace
+
+int prefill_tc_status() {
+    int v = 0;
+    check_cuda(cudaMemcpyFromSymbol(&v, g_prefill_tc_status, sizeof v), "cudaMemcpyFromSymbol(prefill status)");
+    return v;
+}
+
+void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* block_tables,
+                       int table_stride, const int32_t* seq_lens, const void* chunk_key,
+                       const void* chunk_value, void* output, const PageGeom& geo, int head_dim,
+                       int batch, int nq, int hq, int max_prefix_tokens, cudaStream_t stream) {
+    const int H = geo.num_kv_heads;
+    if (batch <= 0 || nq <= 0) return;
+    if (hq % H != 0) throw std::runtime_error("prefill: num_q_heads must be a multiple of num_kv_heads");
+    if (geo.block_size != 16) throw std::runtime_error("prefill: block_size must be 16");
+    if ((reinterpret_cast<uintptr_t>(pool) & 15) || (geo.page_size & 15) || (geo.k_codes & 15) ||
+        (geo.v_codes & 15))
+        throw std::runtime_error("prefill: page pool must be 16-byte aligned");
+    const int G = hq / H;
+    const long long q_rows = static_cast<long long>(batch) * nq * hq;
+    const long long kv_rows = chunk_key ? static_cast<long long>(batch) * nq * H : 0;
+    const int rows_total = nq * G;
+    const int mtiles = (rows_total + kRowsCta - 1) / kRowsCta;
+    const int prefix_tiles = (max_prefix_tokens + kTileTok - 1) / kTileTok;
+    // one CTA per SM: pick the split count (up to 8) that fills whole waves best
+    const int base = mtiles * H * batch, sms = sm_count();
+    int splits = 1;
+    double best = 0.0;
+    for (int sp = 1; sp <= 8 && sp <= (prefix_tiles + 7) / 8; ++sp) {
+        const double waves = static_cast<double>(base) * sp / sms;
+        const double eff = waves / static_cast<double>(static_cast<long long>(waves + 0.999999));
+        if (eff > best + 0.02) {
+            best = eff;
+            splits = sp;
+        }
+    }
+    const size_t q_bytes = static_cast<size_t>(q_rows) * kHeadDim * 2;
+    const size_t kv_bytes = static_cast<size_t>(kv_rows) * kHeadDim * 2;
+    const size_t part_bytes = static_cast<size_t>(q_rows) * splits * TQ_PARTIAL_STRIDE * sizeof(float);
+    auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+    uint8_t* ws = nullptr;
+    check_cuda(cudaMallocAsync(reinterpret_cast<void**>(&ws), up(q_bytes) + 2 * up(kv_bytes) + part_bytes, stream),
+               "cudaMallocAsync(prefill workspace)");
+    __half* q_rot = reinterpret_cast<__half*>(ws);
+    __half* ck_rot = reinterpret_cast<__half*>(ws + up(q_bytes));
+    __half* cv_rot = reinterpret_cast<__half*>(ws + up(q_bytes) + up(kv_bytes));
+    float* partials = reinterpret_cast<float*>(ws + up(q_bytes) + 2 * up(kv_bytes));
+
+    const uint32_t alpha_bits = 0x404c9252u;
+    float alpha;
+    std::memcpy(&alpha, &alpha_bits, sizeof alpha);
+    // q' = R(q) / sqrt(D) * log2(e) / alpha: the rotation's own 1/sqrt(D) is applied in the kernel
+    rotate_rows_tc_kernel<<<static_cast<unsigned>((q_rows + 3) / 4), 128, 0, stream>>>(
+        static_cast<const __half*>(query), q_rot, q_rows, hq, G, kLog2eT / alpha * 0.08838834764831845f, head_dim);
+    check_launch("prefill rotate q");
+    if (chunk_key) {
+        rotate_rows_tc_kernel<<<static_cast<unsigned>((kv_rows + 3) / 4), 128, 0, stream>>>(
+            static_cast<const __half*>(chunk_key), ck_rot, kv_rows, H, 1, alpha, head_dim);
+        rotate_rows_tc_kernel<<<static_cast<unsigned>((kv_rows + 3) / 4), 128, 0, stream>>>(
+            static_cast<const __half*>(chunk_value), cv_rot, kv_rows, H, 1, alpha, head_dim);
+        check_launch("prefill rotate chunk");
+    }
+    PrefillTcParams p{};
+    p.q_rot = q_rot;
+    p.ck_rot = chunk_key ? ck_rot : nullptr;
+    p.cv_rot = chunk_key ? cv_rot : nullptr;
+    p.pool = pool;
+    p.block_tables = block_tables;
+    p.seq_lens = seq_lens;
+    p.partials = partials;
+    p.geo = geo;
+    p.table_stride = table_stride;
+    p.nq = nq;
+    p.hq = hq;
+    p.groups = G;
+    p.splits = splits;
+    static bool attr[64] = {};
+    int dev = 0;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev >= 0 && dev < 64 && !attr[dev]) {
+        check_cuda(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc),
+                   "prefill smem attr");
+        attr[dev] = true;
+    }
+    prefill_tc_kernel<<<dim3(mtiles, H * splits, batch), kThreadsTc, kSmemTc, stream>>>(p);
+    check_launch("turbo_mse prefill (tcgen05)");
+    launch_merge_splits(partials, splits, output, static_cast<int>(q_rows), hq, H, head_dim, stream);
+    check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(prefill workspace)");
+}
+
+}  // namespace tq

@@ -75,6 +75,7 @@ SIGNATURES = {
     "tq_dequant_kv_hnd": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _CFG, C.c_int, _P]),
     "tq_mse_prefill_paged": (C.c_int, [_P, _P, _P, C.c_int, _P, _P, _P, _P, _MSE, _CFG, C.c_int,
                                        C.c_int, C.c_int, _P]),
+    "tq_mse_prefill_status": (C.c_int, []),
     "tq_block_table_create": (_P, [C.c_int, C.c_int]),
     "tq_block_table_destroy": (None, [_P]),
     "tq_block_table_free_pages": (C.c_int, [_P]),
@@ -320,6 +321,10 @@ class TurboQuantWrapper:
                    _ptr(seq_lens), _ptr(chunk_key), _ptr(chunk_value), _ptr(output),
                    C.byref(layout), C.byref(cfg), b, nq, hq, C.c_void_p(stream))
         return output
+
+    def mse_prefill_status(self) -> int:
+        """0 when every bounded wait inside the prefill kernel was satisfied (synchronises)."""
+        return int(self._lib.tq_mse_prefill_status())
 
 
 class BlockTable:
