@@ -43,13 +43,18 @@ constexpr int kWaitLimit = 1 << 20;
 constexpr float kRescaleLag = 8.0f;  // log2 units a row maximum may run ahead of the one in use
 
 // shared-memory map (bytes); every operand tile starts on a 1024-byte boundary
-constexpr int kOffLut = 0;                      // 256 rows of 256 B: 32 replicas x half2 in the first 128 B
-constexpr int kOffQ = 65536;                    // [2 dim chunks][128 rows][128 B]
-constexpr int kOffKV = 98304;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
-constexpr int kOffP = 163840;                   // 2 x [128 rows][128 B]
-constexpr int kOffScale = 196608;               // kscale[2][64], vscale[2][64] (fp32)
-constexpr int kOffBar = kOffScale + 1024;       // mbarriers, TMEM base
-constexpr int kSmemTc = kOffBar + 128;
+constexpr int kOffLut = 0;                      // 256 rows x 32 replicas x half2 (128 B per row)
+constexpr int kOffQ = 32768;                    // [2 dim chunks][128 rows][128 B]
+constexpr int kKvStages = 3;
+constexpr int kOffKV = 65536;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
+constexpr int kOffP = kOffKV + kKvStages * 32768;  // 2 x [128 rows][128 B]
+constexpr int kOffScale = kOffP + 32768;        // per K/V stage: kscale[64], vscale[64] (fp32)
+constexpr int kOffBar = kOffScale + 2048;       // mbarriers, TMEM base
+constexpr int kRawStages = 3;
+constexpr int kRawStage = 8704;                 // K codes 4 KB, V codes 4 KB, 64 x (K scale word, V scale word)
+constexpr int kOffRaw = kOffBar + 128;
+constexpr int kSmemTc = kOffRaw + kRawStages * kRawStage;
+static_assert(kSmemTc <= 232448, "shared memory of one SM");
 
 // fp16(alpha4 * |level|) of the 4-bit codebook as byte pools (entries 0-3 | 4-7), and alpha4
 #define TQ_ALPHA4T TQF(0x404c9252)
@@ -120,10 +125,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+// Non-blocking test of the same condition.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // The same for a whole warp: every lane gets the same answer, so warp-collective instructions
 // that follow are executed by all lanes or by none.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
+__device__ __forceinline__ void cp_async16_t(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4_t(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -157,6 +176,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+
+#ifdef TQ_TC_TRACE
+__device__ long long g_tc_trace[3][128][4];
+#define TC_TRACE(role, it, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 128 && (tid & 127) == 0) g_tc_trace[role][it][slot] = clock64(); } while (0)
+#define TC_TRACE_MMA(it, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 128) g_tc_trace[1][it][slot] = clock64(); } while (0)
+#else
+#define TC_TRACE(role, it, slot)
+#define TC_TRACE_MMA(it, slot)
+#endif
 
 // Status word of the last prefill launches on this device: 0 = every wait was satisfied.
 __device__ int g_prefill_tc_status = 0;
@@ -213,11 +241,12 @@ prefill_tc_kernel(PrefillTcParams p) {
     const int b = blockIdx.z;
     const int rows_total = p.nq * G;
 
-    // barriers: kv_full[2] (128 arrivals), s_full[2] (1), p_full[2] (128), pv_done[2] (1): the
-    // barrier with index j % 2 serves tile j, its phase number is j / 2
+    // barriers: kv_full[3] (128 arrivals) / kv_empty[3] (1): barrier j % 3 serves tile j, phase j / 3;
+    // s_full[2] (1), p_full[2] (128), pv_done[2] (1): barrier j % 2 serves tile j, phase j / 2
     const uint32_t bar0 = sbase + kOffBar;
-    const uint32_t bar_kv_full = bar0, bar_s_full = bar0 + 16, bar_p_full = bar0 + 32, bar_pv_done = bar0 + 48;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 96);
+    const uint32_t bar_kv_full = bar0, bar_kv_empty = bar0 + 24, bar_s_full = bar0 + 48, bar_p_full = bar0 + 64,
+                   bar_pv_done = bar0 + 80;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 112);
 
     // ---- tile schedule of this CTA (identical in every role) ----
     const int n_prefix = __ldg(p.seq_lens + b);
@@ -233,7 +262,7 @@ prefill_tc_kernel(PrefillTcParams p) {
     for (int i = tid; i < 256 * 8; i += kThreadsTc) {
         const uint32_t row = i >> 3, n0 = row & 15u, n1 = row >> 4;
         const uint32_t e = level4_half_bits(n0) | (level4_half_bits(n1) << 16);
-        *reinterpret_cast<uint4*>(smem + kOffLut + row * 256 + (i & 7) * 16) = make_uint4(e, e, e, e);
+        *reinterpret_cast<uint4*>(smem + kOffLut + row * 128 + (i & 7) * 16) = make_uint4(e, e, e, e);
     }
     for (int i = tid; i < kRowsCta * 16; i += kThreadsTc) {
         const int r = i >> 4, u = i & 15;
@@ -244,8 +273,10 @@ prefill_tc_kernel(PrefillTcParams p) {
     }
     fence_async_smem();
     if (tid == 0) {
-        mbar_init(bar_kv_full, 128);
-        mbar_init(bar_kv_full + 8, 128);
+        for (int k = 0; k < kKvStages; ++k) {
+            mbar_init(bar_kv_full + 8 * k, 128);
+            mbar_init(bar_kv_empty + 8 * k, 1);
+        }
         mbar_init(bar_s_full, 1);
         mbar_init(bar_s_full + 8, 1);
         mbar_init(bar_p_full, 128);
@@ -270,64 +301,95 @@ prefill_tc_kernel(PrefillTcParams p) {
         // =========================== unpack warps ===========================
         const int u = tid - 128;
         const int ut = u & 63, uh = u >> 6;   // token of the tile, 32-byte half of its 64 code bytes
-        const uint32_t lane_v = static_cast<uint32_t>(lane) * 4u;
+        const uint32_t lane_v = static_cast<uint32_t>(lane) * 8u;  // table address = (byte << 8 | lane * 8) >> 1
         const int32_t* table = p.block_tables + static_cast<long long>(b) * p.table_stride;
-        struct Raw {
-            uint4 k0, k1, v0, v1;
-            float ks, vs;
-        } raw;
-        raw.k0 = raw.k1 = raw.v0 = raw.v1 = make_uint4(0u, 0u, 0u, 0u);
-        raw.ks = raw.vs = 0.0f;
-        auto fetch = [&](int it) {
-            if (it >= n_pref) return;
+        // Page bytes travel global -> shared with cp.async, two tiles ahead, into a ring of
+        // three raw stages (an HBM round trip is longer than a tile takes, and loads parked in
+        // registers would share scoreboards with younger loads).  A thread copies exactly the bytes
+        // it will read itself (32 code bytes of K and of V, and the two words holding its scales),
+        // so cp.async.wait_group is the only synchronisation the raw ring needs.
+        const uint32_t raw_base = sbase + kOffRaw;
+        // 16-byte piece c (0..3) of token ut sits at an XOR-ed position, so the 16-byte reads of
+        // eight neighbouring tokens cover all banks
+        const uint32_t code_off0 = static_cast<uint32_t>(ut * 64 + (((2 * uh) ^ ((ut >> 1) & 3)) << 4));
+        const uint32_t code_off1 = static_cast<uint32_t>(ut * 64 + (((2 * uh + 1) ^ ((ut >> 1) & 3)) << 4));
+        auto load_page = [&](int it) {
+            if (it >= n_pref) return 0;
             const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
-            const int page = __ldg(table + (t >> 4));
-            const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
-            const unsigned th = static_cast<unsigned>((t & 15) * H + h);
-            const uint4* kc = reinterpret_cast<const uint4*>(pg + p.geo.k_codes + th * 64 + 32 * uh);
-            const uint4* vc = reinterpret_cast<const uint4*>(pg + p.geo.v_codes + th * 64 + 32 * uh);
-            raw.k0 = __ldg(kc);
-            raw.k1 = __ldg(kc + 1);
-            raw.v0 = __ldg(vc);
-            raw.v1 = __ldg(vc + 1);
-            if (uh == 0) {
-                raw.ks = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.k_scales + th * 2))));
-                raw.vs = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(pg + p.geo.v_scales + th * 2))));
+            return __ldg(table + (t >> 4));
+        };
+        auto prefetch = [&](int it, int page) {
+            if (it < n_pref) {
+                const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
+                const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
+                const unsigned th = static_cast<unsigned>((t & 15) * H + h);
+                const uint32_t dst = raw_base + (it % kRawStages) * kRawStage;
+                const uint8_t* kc = pg + p.geo.k_codes + th * 64 + 32 * uh;
+                const uint8_t* vc = pg + p.geo.v_codes + th * 64 + 32 * uh;
+                cp_async16_t(dst + code_off0, kc);
+                cp_async16_t(dst + code_off1, kc + 16);
+                cp_async16_t(dst + 4096 + code_off0, vc);
+                cp_async16_t(dst + 4096 + code_off1, vc + 16);
+                if (uh == 0) {  // the aligned 4-byte words that hold this token-head's two fp16 scales
+                    cp_async4_t(dst + 8192 + ut * 8, pg + p.geo.k_scales + ((th * 2) & ~3u));
+                    cp_async4_t(dst + 8192 + ut * 8 + 4, pg + p.geo.v_scales + ((th * 2) & ~3u));
+                }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, empty or not
         };
-        // one code word (8 codes) -> 8 fp16 operands = one 16-byte unit
-        auto unpack_word = [&](uint32_t w) {
-            uint4 o;
-            o.x = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5504u));
-            o.y = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5514u));
-            o.z = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5524u));
-            o.w = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w, lane_v, 0x5534u));
-            return o;
+        // eight code words (64 codes) -> eight 16-byte units of fp16 operands.  All table loads are
+        // issued before the first store: shared-memory stores and loads through unrelated pointers
+        // keep their program order, so alternating them would serialise on the load latency.
+        auto unpack_row = [&](const uint32_t (&w)[8], uint8_t* dst_chunk) {
+            uint32_t o[32];
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi) {
+                o[4 * wi + 0] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5504u) >> 1));
+                o[4 * wi + 1] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5514u) >> 1));
+                o[4 * wi + 2] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5524u) >> 1));
+                o[4 * wi + 3] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5534u) >> 1));
+            }
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi)
+                *reinterpret_cast<uint4*>(dst_chunk + sw128(ut, wi)) =
+                    make_uint4(o[4 * wi], o[4 * wi + 1], o[4 * wi + 2], o[4 * wi + 3]);
         };
-        fetch(0);
-        for (int it = 0; it < n_tiles; ++it) {
-            const int st = it & 1;
-            if (it >= 2 && !warp_wait(bar_pv_done + 8 * st, ((it >> 1) - 1) & 1)) { fail = 1; break; }
+        // one tile: its raw bytes have landed -> start the copies of tile it + 2 -> wait for the
+        // operand stage -> unpack (or copy a chunk tile)
+        auto do_tile = [&](int it, int& page) {
+            const int st = it % kKvStages;
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // every byte a thread reads it copied itself
+            prefetch(it + 2, page);
+            page = load_page(it + 3);
+            if (it >= kKvStages && !warp_wait(bar_kv_empty + 8 * st, (it / kKvStages - 1) & 1)) { fail = 1; return; }
+            TC_TRACE(0, it, 0);
             uint8_t* ktile = smem + kOffKV + st * 32768;
             uint8_t* vtile = ktile + 16384;
-            float* kscale = reinterpret_cast<float*>(smem + kOffScale) + st * 64;
-            float* vscale = kscale + 128;
+            float* kscale = reinterpret_cast<float*>(smem + kOffScale) + st * 128;
+            float* vscale = kscale + 64;
             if (it < n_pref) {
-                const uint32_t kw[8] = {raw.k0.x, raw.k0.y, raw.k0.z, raw.k0.w, raw.k1.x, raw.k1.y, raw.k1.z, raw.k1.w};
-                const uint32_t vw[8] = {raw.v0.x, raw.v0.y, raw.v0.z, raw.v0.w, raw.v1.x, raw.v1.y, raw.v1.z, raw.v1.w};
-                const float ks = raw.ks, vs = raw.vs;
+                const uint8_t* rawst = smem + kOffRaw + (it % kRawStages) * kRawStage;
+                const uint4 k0 = *reinterpret_cast<const uint4*>(rawst + code_off0);
+                const uint4 k1 = *reinterpret_cast<const uint4*>(rawst + code_off1);
+                const uint4 v0 = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off0);
+                const uint4 v1 = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off1);
+                const uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+                const uint32_t vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                 const int t0 = (tile_lo + it) * kTileTok;
-                fetch(it + 1);  // next tile's bytes travel while this one is unpacked
-#pragma unroll
-                for (int wi = 0; wi < 8; ++wi) {
-                    // unit 8 uh + wi of the 16 of a row: dim chunk uh, unit wi inside the chunk
-                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = unpack_word(kw[wi]);
-                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = unpack_word(vw[wi]);
-                }
+                const int tcl = min(t0 + ut, n_prefix - 1);
+                const uint32_t sc_rd = 8192u + ut * 8u + ((((tcl & 15) * H + h) * 2u) & 2u);
+                const unsigned short ks_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd);
+                const unsigned short vs_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd + 4);
+                // this thread's 64 dims are dim chunk uh of the tile, units 0..7 inside it
+                TC_TRACE(0, it, 1);
+                unpack_row(kw, ktile + uh * 8192);
+                TC_TRACE(0, it, 2);
+                unpack_row(vw, vtile + uh * 8192);
+                TC_TRACE(0, it, 3);
                 if (uh == 0) {
                     const bool ok = t0 + ut < n_prefix;
-                    kscale[ut] = ok ? ks : 0.0f;
-                    vscale[ut] = ok ? vs * (1.0f / TQ_ALPHA4T) : 0.0f;
+                    kscale[ut] = ok ? __half2float(__ushort_as_half(ks_bits)) : 0.0f;
+                    vscale[ut] = ok ? __half2float(__ushort_as_half(vs_bits)) * (1.0f / TQ_ALPHA4T) : 0.0f;
                 }
             } else {
                 const int t0 = (it - n_pref) * kTileTok;
@@ -335,10 +397,16 @@ prefill_tc_kernel(PrefillTcParams p) {
                 const long long rowi = (static_cast<long long>(b) * p.nq + t) * H + h;
                 const uint4* ks = reinterpret_cast<const uint4*>(p.ck_rot + rowi * kHeadDim) + 8 * uh;
                 const uint4* vs = reinterpret_cast<const uint4*>(p.cv_rot + rowi * kHeadDim) + 8 * uh;
+                uint4 kq[8], vq[8];
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
-                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = __ldg(ks + wi);
-                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = __ldg(vs + wi);
+                    kq[wi] = __ldg(ks + wi);
+                    vq[wi] = __ldg(vs + wi);
+                }
+#pragma unroll
+                for (int wi = 0; wi < 8; ++wi) {
+                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = kq[wi];
+                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = vq[wi];
                 }
                 if (uh == 0) {
                     const bool ok = t0 + ut < p.nq;
@@ -348,36 +416,58 @@ prefill_tc_kernel(PrefillTcParams p) {
             }
             fence_async_smem();
             mbar_arrive(bar_kv_full + 8 * st);
-        }
+        };
+        int page = load_page(0);
+        prefetch(0, page);
+        page = load_page(1);
+        prefetch(1, page);
+        page = load_page(2);
+        for (int it = 0; it < n_tiles && !fail; ++it) do_tile(it, page);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp == 8) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
+            // Two counters: S tiles issued, P V tiles issued.  Whichever operand set is ready first
+            // is issued first; S may run at most two tiles ahead of P V (two S buffers).
             const uint32_t q_addr = sbase + kOffQ;
-            auto issue_s = [&](int it) {
-                const int st = it & 1;
-                if (!mbar_wait(bar_kv_full + 8 * st, (it >> 1) & 1)) return false;
-                tc_fence_after();
-                const uint32_t k_addr = sbase + kOffKV + st * 32768;
+            int next_s = 0, next_pv = 0, idle = 0;
+            while (next_pv < n_tiles) {
+                bool progress = false;
+                if (next_s < n_tiles && next_s <= next_pv + 1 &&
+                    mbar_test(bar_kv_full + 8 * (next_s % kKvStages), (next_s / kKvStages) & 1)) {
+                    tc_fence_after();
+                    const uint32_t k_addr = sbase + kOffKV + (next_s % kKvStages) * 32768;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_f16_ss(tmem + 64 * (it & 1),
-                               make_desc(q_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                               make_desc(k_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS, ks > 0);
-                mma_commit(bar_s_full + 8 * (it & 1));
-                return true;
-            };
-            if (n_tiles > 0 && !issue_s(0)) fail = 2;
-            for (int it = 0; it < n_tiles && !fail; ++it) {
-                if (it + 1 < n_tiles && !issue_s(it + 1)) { fail = 2; break; }
-                if (!mbar_wait(bar_p_full + 8 * (it & 1), (it >> 1) & 1)) { fail = 3; break; }
-                tc_fence_after();
-                const uint32_t p_addr = sbase + kOffP + (it & 1) * 16384;
-                const uint32_t v_addr = sbase + kOffKV + (it & 1) * 32768 + 16384;
+                    for (int ks = 0; ks < 8; ++ks)
+                        mma_f16_ss(tmem + 64 * (next_s & 1),
+                                   make_desc(q_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                                   make_desc(k_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS, ks > 0);
+                    mma_commit(bar_s_full + 8 * (next_s & 1));
+                    TC_TRACE_MMA(next_s, 0);
+                    ++next_s;
+                    progress = true;
+                }
+                if (next_pv < next_s && mbar_test(bar_p_full + 8 * (next_pv & 1), (next_pv >> 1) & 1)) {
+                    tc_fence_after();
+                    const uint32_t p_addr = sbase + kOffP + (next_pv & 1) * 16384;
+                    const uint32_t v_addr = sbase + kOffKV + (next_pv % kKvStages) * 32768 + 16384;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_f16_ss(tmem_o, make_desc(p_addr + ks * 32, 16, 1024),
-                               make_desc(v_addr + ks * 2048, 8192, 1024), kIdescPV, (it > 0 || ks > 0) ? 1u : 0u);
-                mma_commit(bar_pv_done + 8 * (it & 1));
+                    for (int ks = 0; ks < 4; ++ks)
+                        mma_f16_ss(tmem_o, make_desc(p_addr + ks * 32, 16, 1024),
+                                   make_desc(v_addr + ks * 2048, 8192, 1024), kIdescPV,
+                                   (next_pv > 0 || ks > 0) ? 1u : 0u);
+                    mma_commit(bar_pv_done + 8 * (next_pv & 1));
+                    mma_commit(bar_kv_empty + 8 * (next_pv % kKvStages));
+                    TC_TRACE_MMA(next_pv, 1);
+                    ++next_pv;
+                    progress = true;
+                }
+                if (progress) {
+                    idle = 0;
+                } else if (++idle > kWaitLimit) {
+                    fail = 2;
+                    break;
+                }
             }
         }
     } else {
@@ -394,8 +484,8 @@ prefill_tc_kernel(PrefillTcParams p) {
             const int n_valid = is_chunk ? p.nq : n_prefix;
             if (!warp_wait(bar_s_full + 8 * st, (it >> 1) & 1)) { fail = 4; break; }
             tc_fence_after();
-            const float* kscale = reinterpret_cast<const float*>(smem + kOffScale) + st * 64;
-            const float* vscale = kscale + 128;
+            const float* kscale = reinterpret_cast<const float*>(smem + kOffScale) + (it % kKvStages) * 128;
+            const float* vscale = kscale + 64;
             float s[64];
             {
                 float part[32];
@@ -406,6 +496,7 @@ prefill_tc_kernel(PrefillTcParams p) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
             }
+            TC_TRACE(2, it, 0);
             const bool need_mask = is_chunk || t0 + kTileTok > n_valid;
             float mx = -INFINITY;
 #pragma unroll
@@ -426,6 +517,7 @@ prefill_tc_kernel(PrefillTcParams p) {
             }
 #pragma unroll
             for (int j = 0; j < 64; ++j) mx = fmaxf(mx, s[j]);
+            TC_TRACE(2, it, 1);
             // keep the maximum in use until the true one runs ahead by more than kRescaleLag
             const float m_true = fmaxf(m_use, mx);
             const bool grow = m_true > m_use + kRescaleLag || (it == 0);
@@ -447,8 +539,19 @@ prefill_tc_kernel(PrefillTcParams p) {
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             m_use = m_new;
+            TC_TRACE(2, it, 2);
             float ls = 0.0f;
             uint8_t* ptile = smem + kOffP + st * 16384;
+            // every V scale is loaded before the first P store (stores and later loads keep order)
+            float vsc[64];
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+                const float4 vc = *reinterpret_cast<const float4*>(vscale + j);
+                vsc[j] = vc.x;
+                vsc[j + 1] = vc.y;
+                vsc[j + 2] = vc.z;
+                vsc[j + 3] = vc.w;
+            }
 #pragma unroll
             for (int u8 = 0; u8 < 8; ++u8) {
                 uint32_t w[4];
@@ -457,13 +560,13 @@ prefill_tc_kernel(PrefillTcParams p) {
                     const int j = 8 * u8 + 2 * k;
                     const float p0 = ex2_t(s[j] - m_use), p1 = ex2_t(s[j + 1] - m_use);
                     ls += p0 + p1;
-                    const float2 vc = *reinterpret_cast<const float2*>(vscale + j);
-                    const __half2 hh = __floats2half2_rn(p0 * vc.x, p1 * vc.y);
+                    const __half2 hh = __floats2half2_rn(p0 * vsc[j], p1 * vsc[j + 1]);
                     w[k] = *reinterpret_cast<const uint32_t*>(&hh);
                 }
                 *reinterpret_cast<uint4*>(ptile + sw128(r, u8)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
             l_run += ls;
+            TC_TRACE(2, it, 3);
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar_p_full + 8 * st);
@@ -511,6 +614,12 @@ prefill_tc_kernel(PrefillTcParams p) {
 
 }  // namespace
 
+#ifdef TQ_TC_TRACE
+extern "C" int tq_tc_trace(long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * 3 * 128 * 4));
+}
+#endif
+
 int prefill_tc_status() {
     int v = 0;
     check_cuda(cudaMemcpyFromSymbol(&v, g_prefill_tc_status, sizeof v), "cudaMemcpyFromSymbol(prefill status)");
@@ -526,7 +635,7 @@ void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* bl
     if (hq % H != 0) throw std::runtime_error("prefill: num_q_heads must be a multiple of num_kv_heads");
     if (geo.block_size != 16) throw std::runtime_error("prefill: block_size must be 16");
     if ((reinterpret_cast<uintptr_t>(pool) & 15) || (geo.page_size & 15) || (geo.k_codes & 15) ||
-        (geo.v_codes & 15))
+        (geo.v_codes & 15) || (geo.k_scales & 3) || (geo.v_scales & 3))
         throw std::runtime_error("prefill: page pool must be 16-byte aligned");
     const int G = hq / H;
     const long long q_rows = static_cast<long long>(batch) * nq * hq;
