@@ -7,24 +7,31 @@
 // follows the reference's rotated-domain formulation (q' = R(q), logits <q', k'>/sqrt(D), V
 // accumulated in the rotated domain, inverse rotation in the merge kernel).
 //
-// One CTA = 128 query rows of one (sequence, kv head, prefix split), 9 warps in three roles:
-//   warps 0-3  softmax: thread i owns row i, which is TMEM lane i.  Per 64-token tile it reads its
-//              S row from TMEM (tcgen05.ld), applies the per-token K scale, the causal / length
-//              mask and the online softmax, and writes P * (V scale) as fp16 into a shared tile
-//              laid out as the A operand of the second product.  When a row maximum grows by more
-//              than 2^8 the O accumulator (TMEM) is rescaled in place (tcgen05.ld / st).
-//   warps 4-7  unpack: fetch the page bytes of the next tile (one tile ahead, in registers), turn
-//              every code byte into two fp16 operands with one shared-memory table lookup, and store
-//              K and V tiles in the 128-byte-swizzled canonical operand layout; chunk tiles (fp16,
-//              rotated by a pre-pass) are copied instead.
-//   warp 8     one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128: 8 instructions, A and
+// One CTA = 128 query rows of one (sequence, kv head, prefix split), 17 warps in three roles:
+//   warps 0-3, 8-11  softmax: two threads per row (tokens 0-31 / 32-63 of a 64-token tile); a row
+//              is TMEM lane i, which warps w and w + 8 may both touch.  Per tile a thread reads
+//              its 32 scores from TMEM (tcgen05.ld), applies the per-token K scale and the causal /
+//              length mask, agrees with its partner on the row maximum (shared memory + a 64-thread
+//              named barrier), and writes P * (V scale) as fp16 into a shared tile laid out as the A
+//              operand of the second product.  The maximum in use only follows the true one when
+//              that runs ahead by more than 2^8; then the O accumulator (TMEM) is rescaled in place
+//              (tcgen05.ld / st).  Elementwise work uses packed fp32 pairs.
+//   warps 4-7, 13-16  unpack: page bytes travel global -> shared with cp.async two tiles ahead (a
+//              thread copies exactly the bytes it reads back, so wait_group is the only
+//              synchronisation); every code byte becomes two fp16 operands with one shared-memory
+//              table lookup; K and V tiles are stored in the 128-byte-swizzled canonical operand
+//              layout (three stages); chunk tiles (fp16, rotated by a pre-pass) are copied instead.
+//   warp 12    one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128: 8 instructions, A and
 //              B K-major) into one of two TMEM buffers, and O += P V (M 128, N 128, K 64: 4
 //              instructions, V as MN-major B operand) into TMEM; tcgen05.commit arrives on
-//              mbarriers.  S of tile j+1 is issued before P V of tile j, so the tensor pipe works
-//              on the next scores while the softmax warps work on the current ones.
-// Synchronisation is all mbarriers (two K/V stages, two S buffers, two P buffers); every wait is
-// bounded: after kWaitLimit polls a thread records a status code, stops working and goes to
-// the common exit, where the TMEM allocation is released.
+//              mbarriers.  It issues whichever product has its operands ready, S up to two tiles
+//              ahead, so the tensor pipe works on the next scores during the current softmax.
+// Synchronisation is all mbarriers (K/V stages full / empty, S full, P full, P V done); every wait
+// is bounded: after kWaitLimit polls a warp records a status code, stops waiting (it keeps
+// walking its loop so that no partner blocks) and the kernel ends through the common exit, where
+// the TMEM allocation is released.  tq_mse_prefill_status() reports the code.
+// Measured bound: shared-memory bandwidth (operand tiles are written once by the unpack warps
+// and read by the tensor core, P makes a round trip, plus table lookups and the raw ring).
 #include <climits>
 #include <cstring>
 
@@ -38,7 +45,7 @@ constexpr float kLog2eT = 1.4426950408889634f;
 constexpr float kLn2T = 0.6931471805599453f;
 constexpr int kTileTok = 64;
 constexpr int kRowsCta = 128;
-constexpr int kThreadsTc = 288;
+constexpr int kThreadsTc = 544;  // warps: softmax 0-3, unpack 4-7, softmax 8-11, MMA issue 12, unpack 13-16
 constexpr int kWaitLimit = 1 << 20;
 constexpr float kRescaleLag = 8.0f;  // log2 units a row maximum may run ahead of the one in use
 
@@ -52,7 +59,8 @@ constexpr int kOffScale = kOffP + 32768;        // per K/V stage: kscale[64], vs
 constexpr int kOffBar = kOffScale + 2048;       // mbarriers, TMEM base
 constexpr int kRawStages = 3;
 constexpr int kRawStage = 8704;                 // K codes 4 KB, V codes 4 KB, 64 x (K scale word, V scale word)
-constexpr int kOffRaw = kOffBar + 128;
+constexpr int kOffXch = kOffBar + 128;          // row maxima exchanged by the two threads of a row
+constexpr int kOffRaw = kOffXch + 2048;
 constexpr int kSmemTc = kOffRaw + kRawStages * kRawStage;
 static_assert(kSmemTc <= 232448, "shared memory of one SM");
 
@@ -177,15 +185,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         : "memory");
 }
 
-#ifdef TQ_TC_TRACE
-__device__ long long g_tc_trace[3][128][4];
-#define TC_TRACE(role, it, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 128 && (tid & 127) == 0) g_tc_trace[role][it][slot] = clock64(); } while (0)
-#define TC_TRACE_MMA(it, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 128) g_tc_trace[1][it][slot] = clock64(); } while (0)
-#else
-#define TC_TRACE(role, it, slot)
-#define TC_TRACE_MMA(it, slot)
-#endif
-
 // Status word of the last prefill launches on this device: 0 = every wait was satisfied.
 __device__ int g_prefill_tc_status = 0;
 
@@ -274,13 +273,13 @@ prefill_tc_kernel(PrefillTcParams p) {
     fence_async_smem();
     if (tid == 0) {
         for (int k = 0; k < kKvStages; ++k) {
-            mbar_init(bar_kv_full + 8 * k, 128);
+            mbar_init(bar_kv_full + 8 * k, 256);
             mbar_init(bar_kv_empty + 8 * k, 1);
         }
         mbar_init(bar_s_full, 1);
         mbar_init(bar_s_full + 8, 1);
-        mbar_init(bar_p_full, 128);
-        mbar_init(bar_p_full + 8, 128);
+        mbar_init(bar_p_full, 256);
+        mbar_init(bar_p_full + 8, 256);
         mbar_init(bar_pv_done, 1);
         mbar_init(bar_pv_done + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -297,96 +296,103 @@ prefill_tc_kernel(PrefillTcParams p) {
     const uint32_t tmem_o = tmem + 128;
     int fail = 0;
 
-    if (warp >= 4 && warp < 8) {
+    if ((warp >= 4 && warp < 8) || warp >= 13) {
         // =========================== unpack warps ===========================
-        const int u = tid - 128;
-        const int ut = u & 63, uh = u >> 6;   // token of the tile, 32-byte half of its 64 code bytes
+        const int u = warp < 8 ? tid - 128 : tid - 288;   // 0..255
+        const int ut = u & 63, uq = u >> 6;   // token of the tile, 16-byte quarter of its 64 code bytes
+        const int uh = uq >> 1;               // dim chunk (64 dims) the quarter belongs to
         const uint32_t lane_v = static_cast<uint32_t>(lane) * 8u;  // table address = (byte << 8 | lane * 8) >> 1
         const int32_t* table = p.block_tables + static_cast<long long>(b) * p.table_stride;
         // Page bytes travel global -> shared with cp.async, two tiles ahead, into a ring of
         // three raw stages (an HBM round trip is longer than a tile takes, and loads parked in
         // registers would share scoreboards with younger loads).  A thread copies exactly the bytes
-        // it will read itself (32 code bytes of K and of V, and the two words holding its scales),
+        // it will read itself (16 code bytes of K and of V, and the two words holding its scales),
         // so cp.async.wait_group is the only synchronisation the raw ring needs.
         const uint32_t raw_base = sbase + kOffRaw;
-        // 16-byte piece c (0..3) of token ut sits at an XOR-ed position, so the 16-byte reads of
-        // eight neighbouring tokens cover all banks
-        const uint32_t code_off0 = static_cast<uint32_t>(ut * 64 + (((2 * uh) ^ ((ut >> 1) & 3)) << 4));
-        const uint32_t code_off1 = static_cast<uint32_t>(ut * 64 + (((2 * uh + 1) ^ ((ut >> 1) & 3)) << 4));
-        auto load_page = [&](int it) {
-            if (it >= n_pref) return 0;
-            const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
+        // 16-byte piece uq of token ut sits at an XOR-ed position, so the 16-byte reads of eight
+        // neighbouring tokens cover all banks
+        const uint32_t code_off = static_cast<uint32_t>(ut * 64 + ((uq ^ ((ut >> 1) & 3)) << 4));
+        // Block-table entries: lane l of a warp holds the entry of prefix tile ids_base + l / 2, page
+        // 2 (warp % 2) + l % 2 of that tile (a warp's 32 tokens lie in two pages), i.e. 16 tiles per
+        // load; the next 16 are loaded half a block early and handed out by shuffles.
+        const int page_sel = 2 * ((u >> 5) & 1);
+        auto load_ids = [&](int base_tile) {
+            const int tile = base_tile + (lane >> 1);
+            if (tile >= n_pref) return 0;
+            const int t = min((tile_lo + tile) * kTileTok + 16 * (page_sel + (lane & 1)), n_prefix - 1);
             return __ldg(table + (t >> 4));
         };
-        auto prefetch = [&](int it, int page) {
+        int ids_base = 0, ids_cur = load_ids(0), ids_next = 0;
+        auto page_of = [&](int it) {   // warp-uniform control flow
+            if (it - ids_base >= 16) {
+                ids_cur = ids_next;
+                ids_base += 16;
+            }
+            if (it - ids_base == 8) ids_next = load_ids(ids_base + 16);
+            int page = __shfl_sync(0xffffffffu, ids_cur, 2 * (it - ids_base) + ((ut >> 4) & 1));
+            // tokens past the end of the prefix read the last valid token's page
+            const int t = (tile_lo + it) * kTileTok + ut;
+            if (t >= n_prefix) page = __ldg(table + ((n_prefix - 1) >> 4));
+            return page;
+        };
+        auto prefetch = [&](int it) {
             if (it < n_pref) {
+                const int page = page_of(it);
                 const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
                 const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
                 const unsigned th = static_cast<unsigned>((t & 15) * H + h);
                 const uint32_t dst = raw_base + (it % kRawStages) * kRawStage;
-                const uint8_t* kc = pg + p.geo.k_codes + th * 64 + 32 * uh;
-                const uint8_t* vc = pg + p.geo.v_codes + th * 64 + 32 * uh;
-                cp_async16_t(dst + code_off0, kc);
-                cp_async16_t(dst + code_off1, kc + 16);
-                cp_async16_t(dst + 4096 + code_off0, vc);
-                cp_async16_t(dst + 4096 + code_off1, vc + 16);
-                if (uh == 0) {  // the aligned 4-byte words that hold this token-head's two fp16 scales
+                cp_async16_t(dst + code_off, pg + p.geo.k_codes + th * 64 + 16 * uq);
+                cp_async16_t(dst + 4096 + code_off, pg + p.geo.v_codes + th * 64 + 16 * uq);
+                if (uq == 0) {  // the aligned 4-byte words that hold this token-head's two fp16 scales
                     cp_async4_t(dst + 8192 + ut * 8, pg + p.geo.k_scales + ((th * 2) & ~3u));
                     cp_async4_t(dst + 8192 + ut * 8 + 4, pg + p.geo.v_scales + ((th * 2) & ~3u));
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, empty or not
         };
-        // eight code words (64 codes) -> eight 16-byte units of fp16 operands.  All table loads are
+        // four code words (32 codes) -> four 16-byte units of fp16 operands.  All table loads are
         // issued before the first store: shared-memory stores and loads through unrelated pointers
         // keep their program order, so alternating them would serialise on the load latency.
-        auto unpack_row = [&](const uint32_t (&w)[8], uint8_t* dst_chunk) {
-            uint32_t o[32];
+        auto unpack_row = [&](const uint4& c, uint8_t* dst_chunk) {
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            uint32_t o[16];
 #pragma unroll
-            for (int wi = 0; wi < 8; ++wi) {
+            for (int wi = 0; wi < 4; ++wi) {
                 o[4 * wi + 0] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5504u) >> 1));
                 o[4 * wi + 1] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5514u) >> 1));
                 o[4 * wi + 2] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5524u) >> 1));
                 o[4 * wi + 3] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5534u) >> 1));
             }
 #pragma unroll
-            for (int wi = 0; wi < 8; ++wi)
-                *reinterpret_cast<uint4*>(dst_chunk + sw128(ut, wi)) =
+            for (int wi = 0; wi < 4; ++wi)
+                *reinterpret_cast<uint4*>(dst_chunk + sw128(ut, 4 * (uq & 1) + wi)) =
                     make_uint4(o[4 * wi], o[4 * wi + 1], o[4 * wi + 2], o[4 * wi + 3]);
         };
         // one tile: its raw bytes have landed -> start the copies of tile it + 2 -> wait for the
         // operand stage -> unpack (or copy a chunk tile)
-        auto do_tile = [&](int it, int& page) {
+        auto do_tile = [&](int it) {
             const int st = it % kKvStages;
             asm volatile("cp.async.wait_group 1;" ::: "memory");  // every byte a thread reads it copied itself
-            prefetch(it + 2, page);
-            page = load_page(it + 3);
+            prefetch(it + 2);
             if (it >= kKvStages && !warp_wait(bar_kv_empty + 8 * st, (it / kKvStages - 1) & 1)) { fail = 1; return; }
-            TC_TRACE(0, it, 0);
             uint8_t* ktile = smem + kOffKV + st * 32768;
             uint8_t* vtile = ktile + 16384;
             float* kscale = reinterpret_cast<float*>(smem + kOffScale) + st * 128;
             float* vscale = kscale + 64;
             if (it < n_pref) {
                 const uint8_t* rawst = smem + kOffRaw + (it % kRawStages) * kRawStage;
-                const uint4 k0 = *reinterpret_cast<const uint4*>(rawst + code_off0);
-                const uint4 k1 = *reinterpret_cast<const uint4*>(rawst + code_off1);
-                const uint4 v0 = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off0);
-                const uint4 v1 = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off1);
-                const uint32_t kw[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-                const uint32_t vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                const uint4 kc = *reinterpret_cast<const uint4*>(rawst + code_off);
+                const uint4 vc = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off);
                 const int t0 = (tile_lo + it) * kTileTok;
                 const int tcl = min(t0 + ut, n_prefix - 1);
                 const uint32_t sc_rd = 8192u + ut * 8u + ((((tcl & 15) * H + h) * 2u) & 2u);
                 const unsigned short ks_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd);
                 const unsigned short vs_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd + 4);
-                // this thread's 64 dims are dim chunk uh of the tile, units 0..7 inside it
-                TC_TRACE(0, it, 1);
-                unpack_row(kw, ktile + uh * 8192);
-                TC_TRACE(0, it, 2);
-                unpack_row(vw, vtile + uh * 8192);
-                TC_TRACE(0, it, 3);
-                if (uh == 0) {
+                // this thread's 32 dims: dim chunk uh of the tile, units 4 (uq % 2) .. + 3 inside it
+                unpack_row(kc, ktile + uh * 8192);
+                unpack_row(vc, vtile + uh * 8192);
+                if (uq == 0) {
                     const bool ok = t0 + ut < n_prefix;
                     kscale[ut] = ok ? __half2float(__ushort_as_half(ks_bits)) : 0.0f;
                     vscale[ut] = ok ? __half2float(__ushort_as_half(vs_bits)) * (1.0f / TQ_ALPHA4T) : 0.0f;
@@ -395,20 +401,20 @@ prefill_tc_kernel(PrefillTcParams p) {
                 const int t0 = (it - n_pref) * kTileTok;
                 const int t = min(t0 + ut, p.nq - 1);
                 const long long rowi = (static_cast<long long>(b) * p.nq + t) * H + h;
-                const uint4* ks = reinterpret_cast<const uint4*>(p.ck_rot + rowi * kHeadDim) + 8 * uh;
-                const uint4* vs = reinterpret_cast<const uint4*>(p.cv_rot + rowi * kHeadDim) + 8 * uh;
-                uint4 kq[8], vq[8];
+                const uint4* ks = reinterpret_cast<const uint4*>(p.ck_rot + rowi * kHeadDim) + 4 * uq;
+                const uint4* vs = reinterpret_cast<const uint4*>(p.cv_rot + rowi * kHeadDim) + 4 * uq;
+                uint4 kq[4], vq[4];
 #pragma unroll
-                for (int wi = 0; wi < 8; ++wi) {
+                for (int wi = 0; wi < 4; ++wi) {
                     kq[wi] = __ldg(ks + wi);
                     vq[wi] = __ldg(vs + wi);
                 }
 #pragma unroll
-                for (int wi = 0; wi < 8; ++wi) {
-                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, wi)) = kq[wi];
-                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, wi)) = vq[wi];
+                for (int wi = 0; wi < 4; ++wi) {
+                    *reinterpret_cast<uint4*>(ktile + uh * 8192 + sw128(ut, 4 * (uq & 1) + wi)) = kq[wi];
+                    *reinterpret_cast<uint4*>(vtile + uh * 8192 + sw128(ut, 4 * (uq & 1) + wi)) = vq[wi];
                 }
-                if (uh == 0) {
+                if (uq == 0) {
                     const bool ok = t0 + ut < p.nq;
                     kscale[ut] = ok ? 1.0f : 0.0f;
                     vscale[ut] = ok ? 1.0f / TQ_ALPHA4T : 0.0f;
@@ -417,14 +423,11 @@ prefill_tc_kernel(PrefillTcParams p) {
             fence_async_smem();
             mbar_arrive(bar_kv_full + 8 * st);
         };
-        int page = load_page(0);
-        prefetch(0, page);
-        page = load_page(1);
-        prefetch(1, page);
-        page = load_page(2);
-        for (int it = 0; it < n_tiles && !fail; ++it) do_tile(it, page);
+        prefetch(0);
+        prefetch(1);
+        for (int it = 0; it < n_tiles && !fail; ++it) do_tile(it);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else if (warp == 8) {
+    } else if (warp == 12) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
             // Two counters: S tiles issued, P V tiles issued.  Whichever operand set is ready first
@@ -443,7 +446,6 @@ prefill_tc_kernel(PrefillTcParams p) {
                                    make_desc(q_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
                                    make_desc(k_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS, ks > 0);
                     mma_commit(bar_s_full + 8 * (next_s & 1));
-                    TC_TRACE_MMA(next_s, 0);
                     ++next_s;
                     progress = true;
                 }
@@ -458,78 +460,84 @@ prefill_tc_kernel(PrefillTcParams p) {
                                    (next_pv > 0 || ks > 0) ? 1u : 0u);
                     mma_commit(bar_pv_done + 8 * (next_pv & 1));
                     mma_commit(bar_kv_empty + 8 * (next_pv % kKvStages));
-                    TC_TRACE_MMA(next_pv, 1);
                     ++next_pv;
                     progress = true;
                 }
                 if (progress) {
                     idle = 0;
-                } else if (++idle > kWaitLimit) {
-                    fail = 2;
-                    break;
+                } else {
+                    // a tight polling loop would take issue slots from the warps of this scheduler
+                    __nanosleep(100);
+                    if (++idle > kWaitLimit) {
+                        fail = 2;
+                        break;
+                    }
                 }
             }
         }
     } else {
         // =========================== softmax warps ===========================
-        const int r = tid;                               // row of the tile = TMEM lane
-        const int rg = mt * kRowsCta + r;                // row of this (sequence, kv head)
-        const int tok = min(rg, rows_total - 1) / G;     // chunk position of the row's token
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        // Two threads per row: warps 0-3 take the tile's tokens 0-31, warps 8-11 tokens 32-63 (both
+        // sets may touch TMEM lanes 32 (warp % 4) ..).  The two threads of a row agree on the
+        // row maximum through shared memory and a 64-thread named barrier per warp pair.  After a
+        // failed wait a warp keeps walking the loop (without waiting) so its partner never blocks.
+        const int half = warp >> 3;                       // 0: tokens 0-31 of a tile, 1: tokens 32-63
+        const int r = (warp & 3) * 32 + lane;             // row of the tile = TMEM lane
+        const int rg = mt * kRowsCta + r;                 // row of this (sequence, kv head)
+        const int tok = min(rg, rows_total - 1) / G;      // chunk position of the row's token
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const int pair_bar = 1 + (warp & 3);
+        float* xch = reinterpret_cast<float*>(smem + kOffXch);  // [2 buffers][2 halves][128 rows]
         float m_use = kInitMaxLogit, l_run = 0.0f;
         for (int it = 0; it < n_tiles; ++it) {
             const int st = it & 1;
             const bool is_chunk = it >= n_pref;
-            const int t0 = is_chunk ? (it - n_pref) * kTileTok : (tile_lo + it) * kTileTok;
+            const int t0 = (is_chunk ? (it - n_pref) * kTileTok : (tile_lo + it) * kTileTok) + 32 * half;
             const int n_valid = is_chunk ? p.nq : n_prefix;
-            if (!warp_wait(bar_s_full + 8 * st, (it >> 1) & 1)) { fail = 4; break; }
+            if (!fail && !warp_wait(bar_s_full + 8 * st, (it >> 1) & 1)) fail = 4;
             tc_fence_after();
-            const float* kscale = reinterpret_cast<const float*>(smem + kOffScale) + (it % kKvStages) * 128;
+            const float* kscale = reinterpret_cast<const float*>(smem + kOffScale) + (it % kKvStages) * 128 + 32 * half;
             const float* vscale = kscale + 64;
-            float s[64];
+            // the row's 32 scores as 16 packed pairs: scale, mask, maximum (packed fp32 arithmetic)
+            float2 s2[16];
             {
-                float part[32];
-                tmem_ld32(tmem + lane_base + 64 * st, part);
+                float s[32];
+                tmem_ld32(tmem + lane_base + 64 * st + 32 * half, s);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) s[j] = part[j];
-                tmem_ld32(tmem + lane_base + 64 * st + 32, part);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
-            }
-            TC_TRACE(2, it, 0);
-            const bool need_mask = is_chunk || t0 + kTileTok > n_valid;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 64; j += 4) {
-                const float4 kc = *reinterpret_cast<const float4*>(kscale + j);
-                s[j] *= kc.x;
-                s[j + 1] *= kc.y;
-                s[j + 2] *= kc.z;
-                s[j + 3] *= kc.w;
-            }
-            if (need_mask) {
-#pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    const int t = t0 + j;
-                    const bool ok = t < n_valid && (!is_chunk || t <= tok);
-                    if (!ok) s[j] = -INFINITY;
+                for (int j = 0; j < 16; j += 2) {
+                    const float4 kc = *reinterpret_cast<const float4*>(kscale + 2 * j);
+                    s2[j] = mul2(make_float2(s[2 * j], s[2 * j + 1]), make_float2(kc.x, kc.y));
+                    s2[j + 1] = mul2(make_float2(s[2 * j + 2], s[2 * j + 3]), make_float2(kc.z, kc.w));
                 }
             }
+            const bool need_mask = is_chunk || t0 + 32 > n_valid;
+            if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) mx = fmaxf(mx, s[j]);
-            TC_TRACE(2, it, 1);
+                for (int j = 0; j < 16; ++j) {
+                    const int t = t0 + 2 * j;
+                    if (!(t < n_valid && (!is_chunk || t <= tok))) s2[j].x = -INFINITY;
+                    if (!(t + 1 < n_valid && (!is_chunk || t + 1 <= tok))) s2[j].y = -INFINITY;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mx = fmaxf(mx, fmaxf(s2[j].x, s2[j].y));
+            // exchange the half-row maxima
+            xch[(st * 2 + half) * 128 + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, xch[(st * 2 + (half ^ 1)) * 128 + r]);
             // keep the maximum in use until the true one runs ahead by more than kRescaleLag
             const float m_true = fmaxf(m_use, mx);
             const bool grow = m_true > m_use + kRescaleLag || (it == 0);
             const float m_new = grow ? m_true : m_use;
             if (it > 0 && __any_sync(0xffffffffu, grow)) {
-                // O *= 2^(m_use - m_new): the previous P V must have landed first
-                if (!warp_wait(bar_pv_done + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1)) { fail = 5; break; }
+                // O *= 2^(m_use - m_new) on this thread's 64 columns: the previous P V must have landed
+                if (!fail && !warp_wait(bar_pv_done + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1)) fail = 5;
                 tc_fence_after();
                 const float al = ex2_t(m_use - m_new);
                 l_run *= al;
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
+                for (int c0 = 64 * half; c0 < 64 * half + 64; c0 += 32) {
                     float o[32];
                     tmem_ld32(tmem_o + lane_base + c0, o);
 #pragma unroll
@@ -539,69 +547,70 @@ prefill_tc_kernel(PrefillTcParams p) {
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             m_use = m_new;
-            TC_TRACE(2, it, 2);
-            float ls = 0.0f;
             uint8_t* ptile = smem + kOffP + st * 16384;
             // every V scale is loaded before the first P store (stores and later loads keep order)
-            float vsc[64];
+            float2 vs2[16];
 #pragma unroll
-            for (int j = 0; j < 64; j += 4) {
-                const float4 vc = *reinterpret_cast<const float4*>(vscale + j);
-                vsc[j] = vc.x;
-                vsc[j + 1] = vc.y;
-                vsc[j + 2] = vc.z;
-                vsc[j + 3] = vc.w;
+            for (int j = 0; j < 16; j += 2) {
+                const float4 vc = *reinterpret_cast<const float4*>(vscale + 2 * j);
+                vs2[j] = make_float2(vc.x, vc.y);
+                vs2[j + 1] = make_float2(vc.z, vc.w);
             }
+            const float2 neg_m = make_float2(-m_use, -m_use);
+            float2 ls2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int u8 = 0; u8 < 8; ++u8) {
+            for (int u8 = 0; u8 < 4; ++u8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const int j = 8 * u8 + 2 * k;
-                    const float p0 = ex2_t(s[j] - m_use), p1 = ex2_t(s[j + 1] - m_use);
-                    ls += p0 + p1;
-                    const __half2 hh = __floats2half2_rn(p0 * vsc[j], p1 * vsc[j + 1]);
+                    const int j = 4 * u8 + k;
+                    const float2 a = add2(s2[j], neg_m);
+                    const float2 pp = make_float2(ex2_t(a.x), ex2_t(a.y));
+                    ls2 = add2(ls2, pp);
+                    const float2 pv = mul2(pp, vs2[j]);
+                    const __half2 hh = __floats2half2_rn(pv.x, pv.y);
                     w[k] = *reinterpret_cast<const uint32_t*>(&hh);
                 }
-                *reinterpret_cast<uint4*>(ptile + sw128(r, u8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(ptile + sw128(r, 4 * half + u8)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            const float ls = ls2.x + ls2.y;
             l_run += ls;
-            TC_TRACE(2, it, 3);
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar_p_full + 8 * st);
         }
-        // ---- epilogue: the row's partial (acc, m in natural-log units, l) ----
-        if (!fail) {
+        // ---- epilogue: the row's partial (acc, m in natural-log units, l); each thread 64 dims ----
+        {
             float* out = nullptr;
             if (rg < rows_total) {
                 const long long seq = static_cast<long long>(b) * p.nq + rg / G;
                 out = p.partials + ((seq * p.splits + split) * p.hq + h * G + rg % G) * TQ_PARTIAL_STRIDE;
             }
             if (n_tiles > 0) {
-                if (!warp_wait(bar_pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) fail = 6;
+                if (!fail && !warp_wait(bar_pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1)) fail = 6;
                 tc_fence_after();
             }
-            if (!fail) {
+            if (half == 1) xch[r] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (half == 0) l_run += xch[r];
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
-                    float o[32];
-                    if (n_tiles > 0) {
-                        tmem_ld32(tmem_o + lane_base + c0, o);
-                    } else {
+            for (int c0 = 64 * half; c0 < 64 * half + 64; c0 += 32) {
+                float o[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(tmem_o + lane_base + c0, o);
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) o[j] = 0.0f;
-                    }
-                    if (out) {
+                    for (int j = 0; j < 32; ++j) o[j] = 0.0f;
+                }
+                if (out && !fail) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2)  // records are 520 bytes apart: 8-byte aligned only
-                            *reinterpret_cast<float2*>(out + c0 + j) = make_float2(o[j], o[j + 1]);
-                    }
+                    for (int j = 0; j < 32; j += 2)  // records are 520 bytes apart: 8-byte aligned only
+                        *reinterpret_cast<float2*>(out + c0 + j) = make_float2(o[j], o[j + 1]);
                 }
-                if (out) {
-                    out[128] = m_use * kLn2T;
-                    out[129] = l_run;
-                }
+            }
+            if (out && !fail && half == 0) {
+                out[128] = m_use * kLn2T;
+                out[129] = l_run;
             }
         }
     }
@@ -613,12 +622,6 @@ prefill_tc_kernel(PrefillTcParams p) {
 }
 
 }  // namespace
-
-#ifdef TQ_TC_TRACE
-extern "C" int tq_tc_trace(long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * 3 * 128 * 4));
-}
-#endif
 
 int prefill_tc_status() {
     int v = 0;
