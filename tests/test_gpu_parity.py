@@ -117,6 +117,21 @@ def test_pack_full_store_unit(tq, oracle, dev, scheme, tag):
     assert r["code_mismatches"] == 0
 
 
+@pytest.mark.parametrize("scheme,tag", SCHEMES)
+def test_pack_large_outlier_rows_identical_pool(tq, oracle, dev, scheme, tag):
+    """32768 tokens x 2 kv heads with two outlier channels: every byte of the pool, the fp16 scales
+    included, equals the oracle's.  Sums of squares that are off in their last fp32 bit (a fused
+    multiply-add where the reference multiplies and adds) show up here as a handful of scale
+    bytes, which smaller cases miss."""
+    rng = np.random.default_rng(32768)
+    key, value = make_kv(rng, 32768, 2)
+    key[:, :, [5, 77]] *= 6
+    slots = make_slots(rng, 32768, True)
+    mine = gpu_pack(tq, scheme, key, value, slots, cfg_for(tq, 2), dev)
+    ref = oracle.pack(scheme, key, value, slots, oracle.make_config(2))
+    assert int((mine != ref).sum()) == 0
+
+
 def test_pack_block_size_other_than_16(tq, oracle, dev):
     rng = np.random.default_rng(77)
     key, value = make_kv(rng, 40, 2)

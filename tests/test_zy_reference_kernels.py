@@ -1,0 +1,108 @@
+"""Side by side with the reference's own CUDA kernels on the same GPU.
+
+``oracle/_ref/libturboquant_ref.so`` is the reference's unmodified kernel sources compiled for
+this GPU (``make -C oracle ref``).  Both libraries export the same ``tq_launch_*`` symbols, so
+the same ctypes calls drive them.  The test checks, at sizes the golden fixtures do not reach
+(one 32768-token sequence), that packed pools and dequantised tensors are bit-identical and
+that attention agrees within the path's tolerance, and it prints the two timings.
+"""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "oracle" / "_ref" / "libturboquant_ref.so"
+OURS = ROOT / "turborag_b200" / "lib" / "libturboquant.so"
+
+pytestmark = pytest.mark.gpu
+
+
+from turborag_b200.wrapper import TQConfig, TQTurboProdPageLayout, TQTurbomsePageLayout  # noqa: E402
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _time(fn, iters=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3  # us
+
+
+@pytest.mark.parametrize("scheme", ["prod", "mse"])
+@pytest.mark.parametrize("n,nq", [(1143, 8), (32768, 8)])
+def test_against_reference_kernels(n, nq, scheme):
+    if not REF.exists():
+        pytest.skip("reference kernels were not built on this machine (make -C oracle ref)")
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    dev = torch.device("cuda:0")
+    h = 2
+    libs = {"reference": C.CDLL(str(REF)), "ours": C.CDLL(str(OURS))}
+    g = torch.Generator(device=dev)
+    g.manual_seed(n)
+    key = torch.randn(n, h, 128, device=dev, generator=g).half()
+    value = torch.randn(n, h, 128, device=dev, generator=g).half()
+    key[:, :, [5, 77]] *= 6  # outlier channels, as in real K caches
+    query = torch.randn(nq, h, 128, device=dev, generator=g).half()
+    pages = (n + 15) // 16
+    perm = torch.randperm(pages, device=dev, generator=g)
+    t = torch.arange(n, device=dev)
+    slots = (perm[t // 16] * 16 + t % 16).to(torch.int32)
+
+    res, times = {}, {}
+    for name, lib in libs.items():
+        lib.tq_last_error.restype = C.c_char_p
+        cfg = TQConfig()
+        lib.tq_make_default_config(C.byref(cfg))
+        cfg.num_kv_heads, cfg.head_dim = h, 128
+        lay_s = TQTurboProdPageLayout() if scheme == "prod" else TQTurbomsePageLayout()
+        getattr(lib, f"tq_make_turbo_{scheme}_layout")(C.byref(cfg), C.byref(lay_s))
+        lay = C.byref(lay_s)
+        page_bytes = lay_s.page_size_bytes
+        assert page_bytes == (4288 if scheme == "prod" else 4608)
+        pool = torch.zeros(pages * page_bytes, dtype=torch.uint8, device=dev)
+        ok = torch.zeros(n, h, 128, dtype=torch.float16, device=dev)
+        ov = torch.zeros_like(ok)
+        oa = torch.zeros(nq, h, 128, dtype=torch.float16, device=dev)
+
+        def pack():
+            assert getattr(lib, f"tq_launch_turbo_{scheme}_pack_kv")(_p(key), _p(value), _p(slots), _p(pool), lay,
+                                                    C.byref(cfg), n, None) == 0, lib.tq_last_error()
+
+        def dequant():
+            assert getattr(lib, f"tq_launch_turbo_{scheme}_dequant_kv")(_p(pool), _p(slots), _p(ok), _p(ov), lay,
+                                                       C.byref(cfg), n, None) == 0, lib.tq_last_error()
+
+        def attend():
+            assert getattr(lib, f"tq_launch_turbo_{scheme}_fused_attention_output")(
+                _p(query), _p(pool), _p(slots), _p(oa), lay, C.byref(cfg), nq, n, None) == 0, lib.tq_last_error()
+
+        times[name] = (_time(pack), _time(dequant), _time(attend))
+        res[name] = (pool.cpu().numpy(), ok.cpu().numpy().view(np.uint16), ov.cpu().numpy().view(np.uint16),
+                     oa.float().cpu().numpy())
+
+    r, o = res["reference"], res["ours"]
+    assert np.array_equal(r[0], o[0]), "packed pools differ from the reference kernels"
+    assert np.array_equal(r[1], o[1]) and np.array_equal(r[2], o[2]), "dequant differs from the reference kernels"
+    err = np.abs(r[3] - o[3]).max(axis=-1) / np.maximum(np.abs(r[3]).max(axis=-1), 1e-6)
+    assert err.max() < 2e-3, f"attention differs from the reference kernels: {err.max():.3e}"
+    tr, to = times["reference"], times["ours"]
+    print(f"\nturbo_{scheme} n={n} nq={nq} H={h}  (us: pack, dequant, fused attention)\n"
+          f"  reference kernels: {tr[0]:9.1f} {tr[1]:9.1f} {tr[2]:9.1f}\n"
+          f"  this library:      {to[0]:9.1f} {to[1]:9.1f} {to[2]:9.1f}\n"
+          f"  ratio:             {tr[0] / to[0]:9.1f} {tr[1] / to[1]:9.1f} {tr[2] / to[2]:9.1f}   "
+          f"attention max rel err {err.max():.2e}")
+    assert to[2] < tr[2], "fused attention slower than the reference's serial kernel"

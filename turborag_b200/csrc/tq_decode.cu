@@ -10,13 +10,13 @@
 //   * a warp owns one kv-head of a block: the 16x128 code tile is the A operand
 //     of mma.sync m16n8k16 (rows = tokens), the up-to-8 query heads that share the
 //     kv-head are the 8 columns, so GQA costs no extra code traffic or unpack work;
-//   * 4-bit codes go nibble -> fp16 in registers with byte-permute lookups
-//     (8-entry signed table for the 3-bit K code, 8-entry magnitude table plus a
-//     sign XOR for the 4-bit codes); the 1-bit residual sign is a second MMA with
-//     +-1 operands, scaled per token column (ks*re) afterwards;
-//   * V^T is the A operand of the second product; its k index runs over tokens, so the
-//     lookup selectors are assembled from the same word of two adjacent tokens and the
-//     table values come out already paired along tokens (no shared-memory transpose).
+//   * a code byte (two 4-bit fields) becomes two fp16 operands either by one lookup in a
+//     byte-indexed, lane-replicated shared-memory table (paged fast path) or by byte-permute
+//     lookups in registers (general kernel: 8-entry signed table for the 3-bit K code, 8-entry
+//     magnitude table plus a sign XOR for the 4-bit codes); the 1-bit residual sign is a second
+//     MMA with +-1 operands, scaled per token column (ks*re) afterwards;
+//   * V^T is the A operand of the second product; its k index runs over tokens, so operand
+//     halves of two adjacent tokens are paired in registers (no shared-memory transpose).
 // Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
 // and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
 #include <climits>

@@ -109,6 +109,14 @@ __device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK, 
     return (__float_as_uint(t.w) + (above ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
 }
 
+// Squares that feed the reference's summation tree.  They are scalar multiplies on purpose: the
+// assembler contracts a packed mul.rn.f32x2 into the packed add that consumes it (observed: the
+// first tree level came out as fma(x, x, y*y)), which changes the sum in its last bit for about
+// half of the rows; the scalar mul.rn.f32 is never contracted.
+__device__ __forceinline__ float2 square2(const float2& v) {
+    return make_float2(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y));
+}
+
 // Move a row's 64 code bytes from "lane l' holds byte l'+8j" to "lane l holds
 // bytes 8l..8l+7" through a per-warp byte buffer, then store them.
 __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t* code_buf,
@@ -186,7 +194,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         if (PROD) {
             float2 sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = mul2(y[j], y[j]);
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
             const float krms = rms_from_sum(tree128(sq));
             const float kr = __frcp_rn(krms);
             float2 e2[8];
@@ -197,8 +205,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 const uint32_t n0 = quant_k3_lut(kn.x, lutK, rep_k, e0);
                 const uint32_t n1 = quant_k3_lut(kn.y, lutK, rep_k, e1);
                 kbytes[j] = n0 | (n1 << 4);
-                const float2 e = make_float2(e0, e1);
-                e2[j] = mul2(e, e);
+                e2[j] = square2(make_float2(e0, e1));
             }
             const float rms_e = rms_from_sum(tree128(e2));
             if (valid && l == 0) {
@@ -233,7 +240,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         if (PROD) {
             float2 sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = mul2(y[j], y[j]);
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
             vrms = rms_from_sum(tree128(sq));
         } else {
             float pr[8];
