@@ -54,8 +54,7 @@ constexpr int kOffLut = 0;                      // 256 rows x 32 replicas x half
 constexpr int kOffQ = 32768;                    // [2 dim chunks][128 rows][128 B]
 constexpr int kKvStages = 3;
 constexpr int kOffKV = 65536;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
-constexpr int kOffP = kOffKV + kKvStages * 32768;  // 2 x [128 rows][128 B]
-constexpr int kOffScale = kOffP + 32768;        // per K/V stage: kscale[64], vscale[64] (fp32)
+constexpr int kOffScale = kOffKV + kKvStages * 32768;  // per K/V stage: kscale[64], vscale[64] (fp32)
 constexpr int kOffBar = kOffScale + 2048;       // mbarriers, TMEM base
 constexpr int kRawStages = 3;
 constexpr int kRawStage = 8704;                 // K codes 4 KB, V codes 4 KB, 64 x (K scale word, V scale word)
@@ -111,6 +110,14 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a, uint64_t
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
         ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// A operand in tensor memory (lane = row, packed 16-bit pairs along K), B through a descriptor.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -182,6 +189,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 
@@ -286,7 +301,7 @@ prefill_tc_kernel(PrefillTcParams p) {
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(256u) : "memory");
+                     "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -294,6 +309,7 @@ prefill_tc_kernel(PrefillTcParams p) {
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;          // columns 0-63 / 64-127: S buffers, 128-255: O
     const uint32_t tmem_o = tmem + 128;
+    const uint32_t tmem_p = tmem + 256;        // columns 256-287 / 288-319: P buffers (fp16 pairs)
     int fail = 0;
 
     if ((warp >= 4 && warp < 8) || warp >= 13) {
@@ -451,11 +467,10 @@ prefill_tc_kernel(PrefillTcParams p) {
                 }
                 if (next_pv < next_s && mbar_test(bar_p_full + 8 * (next_pv & 1), (next_pv >> 1) & 1)) {
                     tc_fence_after();
-                    const uint32_t p_addr = sbase + kOffP + (next_pv & 1) * 16384;
                     const uint32_t v_addr = sbase + kOffKV + (next_pv % kKvStages) * 32768 + 16384;
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        mma_f16_ss(tmem_o, make_desc(p_addr + ks * 32, 16, 1024),
+                    for (int ks = 0; ks < 4; ++ks)  // 16 tokens = 8 TMEM columns of P per instruction
+                        mma_f16_ts(tmem_o, tmem_p + 32 * (next_pv & 1) + 8 * ks,
                                    make_desc(v_addr + ks * 2048, 8192, 1024), kIdescPV,
                                    (next_pv > 0 || ks > 0) ? 1u : 0u);
                     mma_commit(bar_pv_done + 8 * (next_pv & 1));
@@ -547,8 +562,6 @@ prefill_tc_kernel(PrefillTcParams p) {
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             m_use = m_new;
-            uint8_t* ptile = smem + kOffP + st * 16384;
-            // every V scale is loaded before the first P store (stores and later loads keep order)
             float2 vs2[16];
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
@@ -558,24 +571,21 @@ prefill_tc_kernel(PrefillTcParams p) {
             }
             const float2 neg_m = make_float2(-m_use, -m_use);
             float2 ls2 = make_float2(0.0f, 0.0f);
+            uint32_t pw[16];  // P * (V scale) of this thread's 32 tokens as 16 fp16 pairs
 #pragma unroll
-            for (int u8 = 0; u8 < 4; ++u8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int j = 4 * u8 + k;
-                    const float2 a = add2(s2[j], neg_m);
-                    const float2 pp = make_float2(ex2_t(a.x), ex2_t(a.y));
-                    ls2 = add2(ls2, pp);
-                    const float2 pv = mul2(pp, vs2[j]);
-                    const __half2 hh = __floats2half2_rn(pv.x, pv.y);
-                    w[k] = *reinterpret_cast<const uint32_t*>(&hh);
-                }
-                *reinterpret_cast<uint4*>(ptile + sw128(r, 4 * half + u8)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int j = 0; j < 16; ++j) {
+                const float2 a = add2(s2[j], neg_m);
+                const float2 pp = make_float2(ex2_t(a.x), ex2_t(a.y));
+                ls2 = add2(ls2, pp);
+                const float2 pv = mul2(pp, vs2[j]);
+                const __half2 hh = __floats2half2_rn(pv.x, pv.y);
+                pw[j] = *reinterpret_cast<const uint32_t*>(&hh);
             }
-            const float ls = ls2.x + ls2.y;
-            l_run += ls;
-            fence_async_smem();
+            l_run += ls2.x + ls2.y;
+            // P goes to TMEM as the A operand of the second product: lane = row, 32-bit column c of
+            // the buffer holds tokens 2c, 2c+1 of the tile (this thread: columns 16 half .. + 15)
+            tmem_st16(tmem_p + lane_base + 32 * st + 16 * half, pw);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar_p_full + 8 * st);
         }
@@ -618,7 +628,7 @@ prefill_tc_kernel(PrefillTcParams p) {
     tc_fence_before();
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
 }  // namespace
