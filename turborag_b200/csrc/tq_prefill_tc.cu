@@ -12,8 +12,8 @@
 //              is TMEM lane i, which warps w and w + 8 may both touch.  Per tile a thread reads
 //              its 32 scores from TMEM (tcgen05.ld), applies the per-token K scale and the causal /
 //              length mask, agrees with its partner on the row maximum (shared memory + a 64-thread
-//              named barrier), and writes P * (V scale) as fp16 into a shared tile laid out as the A
-//              operand of the second product.  The maximum in use only follows the true one when
+//              named barrier), and writes P * (V scale) as fp16 pairs into TMEM (tcgen05.st), where
+//              it is the A operand of the second product.  The maximum in use only follows the true one when
 //              that runs ahead by more than 2^8; then the O accumulator (TMEM) is rescaled in place
 //              (tcgen05.ld / st).  Elementwise work uses packed fp32 pairs.
 //   warps 4-7, 13-16  unpack: page bytes travel global -> shared with cp.async two tiles ahead (a
@@ -23,15 +23,15 @@
 //              layout (three stages); chunk tiles (fp16, rotated by a pre-pass) are copied instead.
 //   warp 12    one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128: 8 instructions, A and
 //              B K-major) into one of two TMEM buffers, and O += P V (M 128, N 128, K 64: 4
-//              instructions, V as MN-major B operand) into TMEM; tcgen05.commit arrives on
+//              instructions, A = P from TMEM, V as MN-major B operand) into TMEM; tcgen05.commit arrives on
 //              mbarriers.  It issues whichever product has its operands ready, S up to two tiles
 //              ahead, so the tensor pipe works on the next scores during the current softmax.
 // Synchronisation is all mbarriers (K/V stages full / empty, S full, P full, P V done); every wait
 // is bounded: after kWaitLimit polls a warp records a status code, stops waiting (it keeps
 // walking its loop so that no partner blocks) and the kernel ends through the common exit, where
 // the TMEM allocation is released.  tq_mse_prefill_status() reports the code.
-// Measured bound: shared-memory bandwidth (operand tiles are written once by the unpack warps
-// and read by the tensor core, P makes a round trip, plus table lookups and the raw ring).
+// Measured bound: the shared-memory port (operand tiles are written once by the unpack warps and
+// read by the tensor core, plus table lookups and the raw ring) and the softmax chain's latency.
 #include <climits>
 #include <cstring>
 
