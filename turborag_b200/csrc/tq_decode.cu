@@ -116,27 +116,12 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t fp16_bits(float v) {
-    return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(v)));
-}
 
 // Byte pools for the permute lookups: entry e of an 8-entry fp16 table is split
 // into its high byte (pool hi.x/hi.y) and low byte (pool lo.x/lo.y).
 struct BytePools {
     uint32_t hi_a, hi_b, lo_a, lo_b;
 };
-__device__ __forceinline__ BytePools make_pools(const float (&t)[8]) {
-    BytePools p = {0u, 0u, 0u, 0u};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const uint32_t a = fp16_bits(t[e]), b = fp16_bits(t[e + 4]);
-        p.hi_a |= (a >> 8) << (8 * e);
-        p.lo_a |= (a & 0xFFu) << (8 * e);
-        p.hi_b |= (b >> 8) << (8 * e);
-        p.lo_b |= (b & 0xFFu) << (8 * e);
-    }
-    return p;
-}
 
 // Eight 3-bit selectors (one per nibble, bit 3 of every nibble clear) -> four
 // half2 registers holding the table values of nibble pairs (0,4) (1,5) (2,6) (3,7).
@@ -335,17 +320,11 @@ __device__ __forceinline__ void build_operand_lut(uint8_t* lut) {
         const uint32_t n0 = row & 15u, n1 = row >> 4;
         const uint32_t lv3 = level3_bits(n0) | (level3_bits(n1) << 16);
         const uint32_t lv4 = level4_bits(n0) | (level4_bits(n1) << 16);
-        const uint32_t sgn = ((n0 & 8u) ? 0x3C00u : 0xBC00u) | ((n1 & 8u) ? 0x3C000000u : 0xBC000000u);
-        (void)sgn;
         uint4* dk = reinterpret_cast<uint4*>(lut + row * 256 + part * 64);
         uint4* dv = reinterpret_cast<uint4*>(lut + row * 256 + 128 + part * 64);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-#ifdef TQ_SIGN_LUT
-            dk[k] = make_uint4(lv3, sgn, lv3, sgn);
-#else
             dk[k] = make_uint4(lv3, lv3, lv3, lv3);
-#endif
             dv[k] = make_uint4(lv4, lv4, lv4, lv4);
         }
     }
@@ -376,22 +355,15 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
                                               WarpState& st) {
     const int g = c.g, tig = c.tig, h = c.h, H = c.H;
     const int nq = c.nq, gq0 = c.gq0;
-#ifdef TQ_RUNTIME_POOLS
-    const BytePools& pool3 = c.pool3;
-    const BytePools& mag4 = c.mag4;
-#else
     const BytePools pool3 = {TQ_POOL3_HI_A, TQ_POOL3_HI_B, TQ_POOL3_LO_A, TQ_POOL3_LO_B};
     const BytePools mag4 = {TQ_MAG4_HI_A, TQ_MAG4_HI_B, TQ_MAG4_LO_A, TQ_MAG4_LO_B};
-#endif
     const float inv_alpha_v = c.inv_alpha_v;
     float (&o)[8][4] = st.o;
     float (&m_run)[2] = st.m_run;
     float (&l_run)[2] = st.l_run;
     const uint32_t (&qf)[8][2] = c.qf;
     // ---- S = K_hat Q'^T (rows = tokens g, g+8; cols = queries 2tig, 2tig+1) ----
-    // two independent accumulators per product: halves the dependent HMMA chains
     float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
-    float s1b[4] = {0.f, 0.f, 0.f, 0.f}, s2b[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t kw0[4] = {cur.k0.x, cur.k0.y, cur.k0.z, cur.k0.w};
     const uint32_t kw1[4] = {cur.k1.x, cur.k1.y, cur.k1.z, cur.k1.w};
     if constexpr (LUT) {
@@ -401,17 +373,6 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         for (int n = 0; n < 8; ++n) {
             const int wi = n >> 1;
             const uint32_t sa = (n & 1) ? 0x5524u : 0x5504u, sb = (n & 1) ? 0x5534u : 0x5514u;
-#ifdef TQ_SIGN_LUT
-            if (PROD) {
-                const uint32_t lk = (c.lane_k & 0x3Cu) << 1;  // (lane % 16) * 8
-                const uint2 e00 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw0[wi], lk, sa));
-                const uint2 e10 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw1[wi], lk, sa));
-                const uint2 e01 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw0[wi], lk, sb));
-                const uint2 e11 = *reinterpret_cast<const uint2*>(c.lut + prmt(kw1[wi], lk, sb));
-                mma16816(s1, e00.x, e10.x, e01.x, e11.x, qf[n][0], qf[n][1]);
-                mma16816(s2, e00.y, e10.y, e01.y, e11.y, qf[n][0], qf[n][1]);
-            } else
-#endif
             if (PROD) {
                 const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_k, sa);
                 const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_k, sa);
@@ -444,27 +405,14 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             unpack_c4(kw1[wi], mag4, bq);
         }
         mma16816(s1, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-#ifdef TQ_SPLIT_ACC
-        mma16816(s1b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-#else
         mma16816(s1, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-#endif
         if (PROD) {
             unpack_sign(kw0[wi], a);
             unpack_sign(kw1[wi], bq);
             mma16816(s2, a[0], bq[0], a[1], bq[1], qf[2 * wi][0], qf[2 * wi][1]);
-#ifdef TQ_SPLIT_ACC
-            mma16816(s2b, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-#else
             mma16816(s2, a[2], bq[2], a[3], bq[3], qf[2 * wi + 1][0], qf[2 * wi + 1][1]);
-#endif
         }
     }
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        s1[e] += s1b[e];
-        s2[e] += s2b[e];
     }
     const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
     float lg[4];
@@ -639,21 +587,10 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
             }
         }
     }
-#ifdef TQ_RUNTIME_POOLS
-    const float t3[8] = {-TQ_C3_3 * TQ_ALPHA3, -TQ_C3_2 * TQ_ALPHA3, -TQ_C3_1 * TQ_ALPHA3,
-                         -TQ_C3_0 * TQ_ALPHA3, TQ_C3_0 * TQ_ALPHA3,  TQ_C3_1 * TQ_ALPHA3,
-                         TQ_C3_2 * TQ_ALPHA3,  TQ_C3_3 * TQ_ALPHA3};
-    const float t4[8] = {TQ_C4_0 * TQ_ALPHA4, TQ_C4_1 * TQ_ALPHA4, TQ_C4_2 * TQ_ALPHA4,
-                         TQ_C4_3 * TQ_ALPHA4, TQ_C4_4 * TQ_ALPHA4, TQ_C4_5 * TQ_ALPHA4,
-                         TQ_C4_6 * TQ_ALPHA4, TQ_C4_7 * TQ_ALPHA4};
-    ctx.pool3 = make_pools(t3);
-    ctx.mag4 = make_pools(t4);
-#else
     // fp16(alpha * level) split into high-byte and low-byte pools, entries 0-3 | 4-7
-    // (what make_pools() computes; tests/test_abi.py recomputes them from the level tables)
+    // (tests/test_abi.py recomputes them from the level tables)
     ctx.pool3 = BytePools{TQ_POOL3_HI_A, TQ_POOL3_HI_B, TQ_POOL3_LO_A, TQ_POOL3_LO_B};
     ctx.mag4 = BytePools{TQ_MAG4_HI_A, TQ_MAG4_HI_B, TQ_MAG4_LO_A, TQ_MAG4_LO_B};
-#endif
     ctx.inv_alpha_v = 1.0f / TQ_ALPHA4;
     ctx.warp_smem = warp_smem;
     ctx.warp_smem_addr = static_cast<uint32_t>(__cvta_generic_to_shared(warp_smem));
@@ -794,7 +731,7 @@ decode_kernel(DecodeParams p) {
 // scales travel global -> shared with cp.async (no registers held while in flight) into a
 // per-warp ring of kStages stages; cp.async.wait_group paces the consumer.
 constexpr int kStages = 3;
-constexpr int kStageCodeBytes = 2 * 32 * 16 + 4 * 32 * 8;  // K: 2 x 16 B, V: 4 x 8 B per lane
+constexpr int kStageCodeBytes = 2 * 32 * 16 + 2 * 32 * 16;  // K and V: two 16-byte pieces per lane each
 constexpr int kStageScaleBytes = 3 * 256;                   // three regions of 16*H fp16, H <= 8
 constexpr int kStageBytes = kStageCodeBytes + kStageScaleBytes;
 constexpr int kFastWarpBytes = kStages * kStageBytes;       // 8448 >= kWarpSmemBytes (merge record)
@@ -802,9 +739,6 @@ static_assert(kFastWarpBytes >= kWarpSmemBytes, "the merge record reuses the rin
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst_smem, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
