@@ -228,8 +228,21 @@ def longctx(args):
     ws = torch.empty(max(tq.decode_workspace_bytes(B, HQ, N, cfg), 16), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
 
+    # partials travel by peer stores over NVLink (PeerExchange) unless --exchange nccl asks for the
+    # all-gather path
+    xchg = None
+    if world > 1 and args.exchange == "peer":
+        from turborag_b200.parallel import PeerExchange
+        xchg = PeerExchange(tq, B * HQ, dev)
+
     def step():
         for l in range(L):
+            if xchg is not None:
+                tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
+                                partials_out=xchg.local.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo,
+                                kv_end=hi, workspace=ws, stream=stream)
+                xchg.publish_and_merge(B * HQ, out[l].view(B * HQ, 128), HQ, H, stream)
+                continue
             tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
                             partials_out=part.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo, kv_end=hi,
                             workspace=ws, stream=stream)
@@ -268,12 +281,14 @@ def longctx(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": workload_name(args), "global_batch": B, "kv_tokens": N, "layers": L,
-                       "parallelism": f"kv sequence split over {world} rank(s), one all-gather of "
-                                      f"{B * HQ * 130 * 4} B per rank per layer, local LSE merge",
+                       "parallelism": (f"kv sequence split over {world} rank(s), {B * HQ * 130 * 4} B of partials per "
+                                       f"rank per layer exchanged by " +
+                                       (f"peer stores over NVLink ({xchg.how})" if xchg is not None
+                                        else "one NCCL all-gather") + ", local LSE merge"),
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": per_rank, "peak": peak, "unit": "GB/s",
                          "frac": per_rank / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "decode_kernel<turbo_prod> + all-gather + merge, per rank"},
+                         "kernel": "decode_paged16_kernel<turbo_prod> + partial exchange + merge, per rank"},
             "gpu_launches": args.steps * L * 3, "clocks": clocks,
         }))
     if world > 1:
@@ -610,6 +625,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--q-heads", type=int, default=None)
     ap.add_argument("--kv-heads", type=int, default=None)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="longctx on several GPUs: how the split-KV partials travel")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-secondary", action="store_true")
     args = ap.parse_args()

@@ -215,6 +215,25 @@ int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_pool,
  * launch are then undefined); negative on a CUDA error.  No reference counterpart. */
 int tq_mse_prefill_status(void);
 
+/* Exchange of split-KV partials between the GPUs of one NVLink domain by plain peer stores (no
+ * collective library call).  No reference counterpart (the reference is single-GPU).
+ * Every rank owns one buffer of tq_peer_buffer_bytes(world, rows_cap) bytes, zero-initialised
+ * once, mapped into every peer (CUDA IPC or symmetric memory; the host side does that).
+ * Per exchange (numbered 1, 2, 3, ... identically on all ranks):
+ *   tq_peer_publish: stores this rank's records local_partials[rows][130] into slot `rank` of
+ *     every buffer in peer_buffers[world] (device pointers valid on this GPU, own buffer
+ *     included) and raises this rank's flag there;
+ *   tq_peer_merge: waits (at most 2 s) until every rank's flag in my_buffer shows `exchange`, then
+ *     merges the world records per row (log-sum-exp), normalises, applies the inverse rotation and
+ *     writes fp16 output[rows][128]; rows = sequences * num_q_heads, rows ordered (sequence, q head).
+ * tq_peer_status(): 0, or 1 if a wait ever ran out on the current device (synchronises). */
+size_t tq_peer_buffer_bytes(int world, int rows_cap);
+int tq_peer_publish(const float* local_partials, void* const* peer_buffers, int rank, int world,
+                    int rows, int rows_cap, unsigned int exchange, tq_stream_t stream);
+int tq_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange,
+                  tq_half* output, int num_q_heads, int num_kv_heads, int head_dim, tq_stream_t stream);
+int tq_peer_status(void);
+
 /* Host-side page allocator and block table (LIFO free list and the slot
  * formula of src/tq_allocator.cpp:5-31, src/tq_block_table.cpp:7-39; the pool
  * memory itself stays with the caller). */

@@ -304,7 +304,8 @@ def build_paged(oracle, scheme, rng, lens, h, extra=3):
 
 @pytest.mark.parametrize("scheme,tag", SCHEMES)
 @pytest.mark.parametrize("hq,h,lens", [(16, 2, [1143, 16, 700, 1]), (28, 4, [333, 64]), (8, 8, [100, 5]),
-                                       (4, 2, [0, 40]), (32, 2, [257]), (2, 2, [4096, 4095, 31])])
+                                       (4, 2, [0, 40]), (32, 2, [257]), (2, 2, [4096, 4095, 31]),
+                                       (8, 1, [77, 300, 2049])])
 def test_decode_paged_vs_oracle(tq, oracle, dev, scheme, tag, hq, h, lens):
     rng = np.random.default_rng(sum(lens) + hq)
     pool, tables = build_paged(oracle, scheme, rng, lens, h)

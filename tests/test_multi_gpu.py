@@ -1,6 +1,8 @@
 """KV-sequence split across GPUs: every rank decodes its page-aligned token range of every
 sequence, ONE NCCL all-gather brings the (acc, m, l) partials into local memory and the local
-merge kernel finishes (turborag_b200.parallel.decode_kv_split).  Needs >= 2 GPUs; skipped on a
+merge kernel finishes (turborag_b200.parallel.decode_kv_split); then the same with the partials
+exchanged by plain peer stores (PeerExchange / decode_kv_split_peer), which must give the
+identical output.  Needs >= 2 GPUs; skipped on a
 single-GPU box (the host-side logic is covered on CPU ranks by test_kv_split_gloo.py)."""
 import numpy as np
 import pytest
@@ -20,7 +22,7 @@ def _worker(rank, world, port, q):
     import turborag_b200
     from oracle import oracle as O
     from tests.golden.cases import make_kv
-    from turborag_b200.parallel import decode_kv_split
+    from turborag_b200.parallel import PeerExchange, decode_kv_split, decode_kv_split_peer
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -32,6 +34,8 @@ def _worker(rank, world, port, q):
         rng = np.random.default_rng(77)  # identical data on every rank
         lens, hq, h = [3000, 1234], 28, 4
         res = {}
+        xchg = PeerExchange(tq, len(lens) * hq, dev)
+        res["mapping"] = xchg.how
         for scheme in ("turbo_prod", "turbo_mse"):
             ocfg = O.make_config(h)
             lay_o = O.layout_for(scheme, ocfg)
@@ -56,6 +60,17 @@ def _worker(rank, world, port, q):
             ref = O.decode_paged(scheme, query, pool, tables, lens, ocfg).astype(np.float32)
             got = out.cpu().numpy().astype(np.float32)
             res[scheme] = float((np.abs(got - ref).max(-1) / np.abs(ref).max(-1)).max())
+            # the same with the partials exchanged by peer stores; three calls in a row exercise both
+            # buffer parities and the self-resetting ticket
+            for rep in range(3):
+                out2 = torch.full_like(out, 7.0)
+                decode_kv_split_peer(xchg, scheme, torch.from_numpy(query.view(np.int16)).to(dev).view(torch.float16),
+                                     torch.from_numpy(pool).to(dev), torch.from_numpy(tables).to(dev),
+                                     torch.tensor(lens, dtype=torch.int32, device=dev), lay, cfg,
+                                     max_kv_tokens=max(lens), output=out2)
+                torch.cuda.synchronize()
+                assert torch.equal(out2, out), f"peer exchange differs from the all-gather path (call {rep})"
+        res["peer_status"] = tq.peer_status()
         gathered = [None] * world
         dist.all_gather_object(gathered, res)
         if rank == 0:
@@ -78,5 +93,7 @@ def test_kv_split_across_gpus():
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    print(res)
     for r in res:
         assert r["turbo_prod"] < 2e-3 and r["turbo_mse"] < 2e-3, res
+        assert r["peer_status"] == 0, res

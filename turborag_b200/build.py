@@ -19,7 +19,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libturboquant.so"
 SOURCES = ["tq_capi.cpp", "tq_pack.cu", "tq_dequant.cu", "tq_decode.cu", "tq_prefill.cu",
-           "tq_prefill_tc.cu", "tq_noalloc.cu"]
+           "tq_prefill_tc.cu", "tq_peer.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -76,6 +76,10 @@ SIGNATURES = {
     "tq_mse_prefill_paged": (C.c_int, [_P, _P, _P, C.c_int, _P, _P, _P, _P, _MSE, _CFG, C.c_int,
                                        C.c_int, C.c_int, _P]),
     "tq_mse_prefill_status": (C.c_int, []),
+    "tq_peer_buffer_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "tq_peer_publish": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, _P]),
+    "tq_peer_merge": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_uint, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "tq_peer_status": (C.c_int, []),
     "tq_block_table_create": (_P, [C.c_int, C.c_int]),
     "tq_block_table_destroy": (None, [_P]),
     "tq_block_table_free_pages": (C.c_int, [_P]),
@@ -321,6 +325,26 @@ class TurboQuantWrapper:
                    _ptr(seq_lens), _ptr(chunk_key), _ptr(chunk_value), _ptr(output),
                    C.byref(layout), C.byref(cfg), b, nq, hq, C.c_void_p(stream))
         return output
+
+    # -- peer exchange of split-KV partials (see turborag_b200/parallel.py: PeerExchange) --------
+    def peer_buffer_bytes(self, world: int, rows_cap: int) -> int:
+        return int(self._lib.tq_peer_buffer_bytes(world, rows_cap))
+
+    def peer_publish(self, local_partials, peer_ptrs, rank: int, world: int, rows: int, rows_cap: int,
+                     exchange: int, stream: int = 0) -> None:
+        """``peer_ptrs``: ctypes array of ``world`` device pointers (own buffer included)."""
+        _cuda(local_partials)
+        self._call("kv split", "peer_publish", self._lib.tq_peer_publish, _ptr(local_partials),
+                   C.cast(peer_ptrs, C.c_void_p), rank, world, rows, rows_cap, exchange, C.c_void_p(stream))
+
+    def peer_merge(self, my_buffer, world: int, rows: int, rows_cap: int, exchange: int, output,
+                   num_q_heads: int, num_kv_heads: int, stream: int = 0) -> None:
+        _cuda(my_buffer, output)
+        self._call("kv split", "peer_merge", self._lib.tq_peer_merge, _ptr(my_buffer), world, rows,
+                   rows_cap, exchange, _ptr(output), num_q_heads, num_kv_heads, 128, C.c_void_p(stream))
+
+    def peer_status(self) -> int:
+        return int(self._lib.tq_peer_status())
 
     def mse_prefill_status(self) -> int:
         """0 when every bounded wait inside the prefill kernel was satisfied (synchronises)."""
