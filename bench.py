@@ -238,10 +238,12 @@ def longctx(args):
     def step():
         for l in range(L):
             if xchg is not None:
-                tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
-                                partials_out=xchg.local.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo,
-                                kv_end=hi, workspace=ws, stream=stream)
-                xchg.publish_and_merge(B * HQ, out[l].view(B * HQ, 128), HQ, H, stream)
+                xchg.exchange += 1
+                tq.decode_paged_publish("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg, xchg.ptr_array,
+                                        rank, world, xchg.rows_cap, xchg.exchange, N, lo, hi, workspace=ws,
+                                        stream=stream)
+                tq.peer_merge(xchg.buf, world, B * HQ, xchg.rows_cap, xchg.exchange, out[l].view(B * HQ, 128),
+                              HQ, H, stream)
                 continue
             tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
                             partials_out=part.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo, kv_end=hi,

@@ -226,8 +226,16 @@ int tq_mse_prefill_status(void);
  *   tq_peer_merge: waits (at most 2 s) until every rank's flag in my_buffer shows `exchange`, then
  *     merges the world records per row (log-sum-exp), normalises, applies the inverse rotation and
  *     writes fp16 output[rows][128]; rows = sequences * num_q_heads, rows ordered (sequence, q head).
- * tq_peer_status(): 0, or 1 if a wait ever ran out on the current device (synchronises). */
+ * tq_peer_status(): 0, or 1 if a wait ever ran out on the current device (synchronises).
+ * tq_decode_paged_publish = tq_decode_paged restricted to [kv_begin, kv_end) whose split merge
+ * writes the records straight into the peers' buffers (decode + publish in two launches). */
 size_t tq_peer_buffer_bytes(int world, int rows_cap);
+int tq_decode_paged_publish(int scheme, const tq_half* query, const uint8_t* page_pool,
+                            const int32_t* block_tables, int table_stride, const int32_t* seq_lens,
+                            const void* layout, const TQConfig* cfg, int batch, int num_q_heads,
+                            int max_kv_tokens, int kv_begin, int kv_end, void* workspace,
+                            size_t workspace_bytes, void* const* peer_buffers, int rank, int world,
+                            int rows_cap, unsigned int exchange, tq_stream_t stream);
 int tq_peer_publish(const float* local_partials, void* const* peer_buffers, int rank, int world,
                     int rows, int rows_cap, unsigned int exchange, tq_stream_t stream);
 int tq_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange,

@@ -366,6 +366,56 @@ extern "C" int tq_decode_paged(int scheme, const tq_half* query, const uint8_t* 
     });
 }
 
+extern "C" int tq_decode_paged_publish(int scheme, const tq_half* query, const uint8_t* page_pool,
+                                       const int32_t* block_tables, int table_stride,
+                                       const int32_t* seq_lens, const void* layout, const TQConfig* cfg,
+                                       int batch, int num_q_heads, int max_kv_tokens, int kv_begin,
+                                       int kv_end, void* workspace, size_t workspace_bytes,
+                                       void* const* peer_buffers, int rank, int world, int rows_cap,
+                                       unsigned int exchange, tq_stream_t stream) {
+    if (!query || !page_pool || !block_tables || !seq_lens || !layout || !cfg || !peer_buffers) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "decode_paged_publish");
+        check_align(query, 8, "query");
+        if (batch < 0 || num_q_heads < 1 || max_kv_tokens < 0 || table_stride < 0)
+            throw std::runtime_error("decode_paged_publish: negative size");
+        if (static_cast<long long>(table_stride) * cfg->block_size < max_kv_tokens)
+            throw std::runtime_error("decode_paged_publish: block table narrower than max_kv_tokens");
+        const long long rows = static_cast<long long>(batch) * num_q_heads;
+        if (world < 1 || world > 8 || rank < 0 || rank >= world || rows > rows_cap)
+            throw std::runtime_error("decode_paged_publish: bad rank / world / rows_cap");
+        tq::DecodeArgs a{};
+        a.scheme = scheme;
+        a.query = query;
+        a.pool = page_pool;
+        a.block_tables = block_tables;
+        a.table_stride = table_stride;
+        a.seq_lens = seq_lens;
+        a.geo = geom_for(scheme, layout, *cfg);
+        a.head_dim = cfg->head_dim;
+        a.batch = batch;
+        a.num_q_heads = num_q_heads;
+        a.ref_query_layout = 0;
+        a.max_kv_tokens = max_kv_tokens;
+        a.kv_begin = kv_begin;
+        a.kv_end = kv_end;
+        a.workspace = workspace;
+        a.workspace_bytes = workspace_bytes;
+        const size_t rec = (size_t(2) * world * rows_cap * TQ_PARTIAL_STRIDE * sizeof(float) + 255) / 256 * 256;
+        for (int q = 0; q < world; ++q) {
+            if (!peer_buffers[q]) throw std::runtime_error("decode_paged_publish: null peer buffer");
+            a.peer.records[q] = static_cast<float*>(peer_buffers[q]);
+            a.peer.flags[q] = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(peer_buffers[q]) + rec);
+        }
+        a.peer.ticket = a.peer.flags[rank] + 2 * world;
+        a.peer.world = world;
+        a.peer.rank = rank;
+        a.peer.rows_cap = rows_cap;
+        a.peer.exchange = exchange;
+        tq::launch_decode(a, static_cast<cudaStream_t>(stream));
+    });
+}
+
 extern "C" int tq_merge_partials(const float* partials, int num_parts, tq_half* output, int rows,
                                  int num_q_heads, int num_kv_heads, tq_stream_t stream) {
     if (!partials || !output) return -1;

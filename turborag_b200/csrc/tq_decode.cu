@@ -886,16 +886,12 @@ decode_paged16_kernel(DecodeParams p) {
     decode_epilogue(p, kFastWarpBytes, ctx, r, st);
 }
 
-// ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
-// One warp per (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
-__global__ void __launch_bounds__(128)
-merge_kernel(const float* __restrict__ partials, int num_parts, long long part_stride,
-             long long seq_stride, int rows_per_seq, __half* __restrict__ output,
-             float* __restrict__ partials_out, int rows, int num_q_heads, int num_kv_heads,
-             int ref_layout, int head_dim) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
+// One warp merges the parts of one (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
+__device__ __forceinline__ void merge_row(const float* __restrict__ partials, int num_parts,
+                                          long long part_stride, long long seq_stride, int rows_per_seq,
+                                          __half* __restrict__ output, float* __restrict__ partials_out,
+                                          int row, int num_q_heads, int num_kv_heads, int ref_layout,
+                                          int head_dim, int lane, const PeerOut* peer) {
     const int seq = row / rows_per_seq, r = row - seq * rows_per_seq;
     const float* base = partials + seq * seq_stride + static_cast<long long>(r) * TQ_PARTIAL_STRIDE;
     float mmax = kInitMaxLogit;
@@ -919,6 +915,16 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
         if (lane == 0) {
             po[128] = mmax;
             po[129] = l;
+        }
+    }
+    if (peer) {
+        const long long at = ((static_cast<long long>(peer->exchange & 1u) * peer->world + peer->rank) *
+                                  peer->rows_cap + row) * TQ_PARTIAL_STRIDE;
+        for (int q = 0; q < peer->world; ++q) {
+            float* po = peer->records[q] + at;
+            *reinterpret_cast<float2*>(po + 4 * lane) = make_float2(acc[0], acc[1]);
+            *reinterpret_cast<float2*>(po + 4 * lane + 2) = make_float2(acc[2], acc[3]);
+            if (lane == 0) *reinterpret_cast<float2*>(po + 128) = make_float2(mmax, l);
         }
     }
     if (!output) return;
@@ -946,6 +952,39 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
     __half2* dst = reinterpret_cast<__half2*>(output + orow * kHeadDim + 4 * lane);
     dst[0] = __floats2half2_rn(x[0] * s0, x[1] * -s0);
     dst[1] = __floats2half2_rn(x[2] * s0, x[3] * -s0);
+}
+
+// ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
+// One warp per (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
+__global__ void __launch_bounds__(128)
+merge_kernel(const float* __restrict__ partials, int num_parts, long long part_stride,
+             long long seq_stride, int rows_per_seq, __half* __restrict__ output,
+             float* __restrict__ partials_out, int rows, int num_q_heads, int num_kv_heads,
+             int ref_layout, int head_dim, PeerOut peer) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (peer.world > 0) {
+        // Publishing variant: the row's merged record goes straight into slot `rank` of every
+        // peer's buffer; the last CTA to finish raises this rank's flag on every peer.
+        if (row < rows) merge_row(partials, num_parts, part_stride, seq_stride, rows_per_seq, nullptr, nullptr,
+                                  row, num_q_heads, num_kv_heads, ref_layout, head_dim, lane, &peer);
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int done = atomicAdd(peer.ticket, 1u);
+            if (done == gridDim.x - 1) {
+                *peer.ticket = 0u;
+                __threadfence_system();
+                for (int q = 0; q < peer.world; ++q)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer.flags[q] + (peer.exchange & 1u) * peer.world + peer.rank),
+                                 "r"(peer.exchange) : "memory");
+            }
+        }
+        return;
+    }
+    if (row >= rows) return;
+    merge_row(partials, num_parts, part_stride, seq_stride, rows_per_seq, output, partials_out, row,
+              num_q_heads, num_kv_heads, ref_layout, head_dim, lane, nullptr);
 }
 
 // Dynamic shared memory above 48 KB has to be opted into once per device.
@@ -1000,7 +1039,7 @@ void launch_merge(const float* partials, int num_parts, void* output, float* par
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
         partials, num_parts, part_stride, static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE,
         num_q_heads, static_cast<__half*>(output), partials_out, rows, num_q_heads, num_kv_heads,
-        ref_query_layout, head_dim);
+        ref_query_layout, head_dim, PeerOut{});
     check_launch("merge_partials");
 }
 
@@ -1010,7 +1049,7 @@ void launch_merge_splits(const float* partials, int splits, void* output, int ro
     const long long part_stride = static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE;
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(partials, splits, part_stride, part_stride * splits,
                                                    num_q_heads, static_cast<__half*>(output), nullptr,
-                                                   rows, num_q_heads, num_kv_heads, 0, head_dim);
+                                                   rows, num_q_heads, num_kv_heads, 0, head_dim, PeerOut{});
     check_launch("merge splits");
 }
 
@@ -1114,7 +1153,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
         ws, splits, part_stride, part_stride * splits, a.num_q_heads,
         static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
-        a.ref_query_layout, a.head_dim);
+        a.ref_query_layout, a.head_dim, a.peer);
     check_launch("decode merge");
     if (owned) check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(decode workspace)");
 }

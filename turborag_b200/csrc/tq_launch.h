@@ -33,6 +33,16 @@ void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* 
                     void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,
                     cudaStream_t stream);
 
+// Where the merged (acc, m, l) record of every row goes when the partials are published to the
+// GPUs of an NVLink domain (see tq_peer.cu for the buffer layout); world == 0 turns it off.
+struct PeerOut {
+    float* records[8];
+    unsigned int* flags[8];
+    unsigned int* ticket;
+    int world, rank, rows_cap;
+    unsigned int exchange;
+};
+
 struct DecodeArgs {
     int scheme;                   // TQ_SCHEME_*
     const void* query;            // fp16
@@ -53,6 +63,7 @@ struct DecodeArgs {
     int kv_begin, kv_end;
     void* workspace;
     size_t workspace_bytes;
+    PeerOut peer;                 // optional: publish the merged records to every peer
 };
 void launch_decode(const DecodeArgs& a, cudaStream_t stream);
 int decode_num_splits(int batch, int max_kv_tokens, int num_kv_heads, int block_size);

@@ -124,14 +124,17 @@ class PeerExchange:
 def decode_kv_split_peer(xchg: PeerExchange, scheme, query, page_pool, block_tables, seq_lens, layout,
                          cfg, max_kv_tokens: int, output: torch.Tensor, workspace=None,
                          stream: int = 0) -> torch.Tensor:
-    """``decode_kv_split`` with the partials exchanged by peer stores instead of an all-gather."""
+    """``decode_kv_split`` with the partials exchanged by peer stores instead of an all-gather:
+    decode kernel, split merge that stores the records into every peer's buffer, merge of the
+    records that arrived here -- three launches, no collective."""
     tq = xchg.tq
     b, hq, _ = query.shape
     rows = b * hq
     begin, end = kv_token_range(max_kv_tokens, xchg.rank, xchg.world, cfg.block_size)
-    tq.decode_paged(scheme, query, page_pool, block_tables, seq_lens, layout, cfg,
-                    partials_out=xchg.local[:rows].view(b, hq, PARTIAL_STRIDE),
-                    max_kv_tokens=max_kv_tokens, kv_begin=begin, kv_end=end, workspace=workspace,
-                    stream=stream)
-    xchg.publish_and_merge(rows, output.view(rows, -1), hq, cfg.num_kv_heads, stream)
+    xchg.exchange += 1
+    tq.decode_paged_publish(scheme, query, page_pool, block_tables, seq_lens, layout, cfg, xchg.ptr_array,
+                            xchg.rank, xchg.world, xchg.rows_cap, xchg.exchange, max_kv_tokens, begin, end,
+                            workspace=workspace, stream=stream)
+    tq.peer_merge(xchg.buf, xchg.world, rows, xchg.rows_cap, xchg.exchange, output.view(rows, -1), hq,
+                  cfg.num_kv_heads, stream)
     return output

@@ -77,6 +77,9 @@ SIGNATURES = {
                                        C.c_int, C.c_int, _P]),
     "tq_mse_prefill_status": (C.c_int, []),
     "tq_peer_buffer_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "tq_decode_paged_publish": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _CFG, C.c_int, C.c_int,
+                                          C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, C.c_int, C.c_int,
+                                          C.c_int, C.c_uint, _P]),
     "tq_peer_publish": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, _P]),
     "tq_peer_merge": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_uint, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tq_peer_status": (C.c_int, []),
@@ -336,6 +339,18 @@ class TurboQuantWrapper:
         _cuda(local_partials)
         self._call("kv split", "peer_publish", self._lib.tq_peer_publish, _ptr(local_partials),
                    C.cast(peer_ptrs, C.c_void_p), rank, world, rows, rows_cap, exchange, C.c_void_p(stream))
+
+    def decode_paged_publish(self, scheme, query, page_pool, block_tables, seq_lens, layout, cfg, peer_ptrs,
+                             rank: int, world: int, rows_cap: int, exchange: int, max_kv_tokens: int,
+                             kv_begin: int, kv_end: int, workspace=None, stream: int = 0) -> None:
+        """Decode this rank's token range and store the merged records into every peer's buffer."""
+        _cuda(query, page_pool, block_tables, seq_lens, workspace)
+        b, hq, _ = query.shape
+        self._call(scheme, "decode_paged_publish", self._lib.tq_decode_paged_publish, SCHEME_ID[scheme],
+                   _ptr(query), _ptr(page_pool), _ptr(block_tables), block_tables.shape[1], _ptr(seq_lens),
+                   C.cast(C.byref(layout), C.c_void_p), C.byref(cfg), b, hq, max_kv_tokens, kv_begin, kv_end,
+                   _ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(),
+                   C.cast(peer_ptrs, C.c_void_p), rank, world, rows_cap, exchange, C.c_void_p(stream))
 
     def peer_merge(self, my_buffer, world: int, rows: int, rows_cap: int, exchange: int, output,
                    num_q_heads: int, num_kv_heads: int, stream: int = 0) -> None:
