@@ -478,17 +478,28 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
 
     // ---- O^T += V^T P^T: A = V^T (rows = this lane's dims 16g + 2j + {0,1}, k = tokens) ----
     if constexpr (LUT) {
-        // tile j = byte j of the lane's 8 V bytes: a looked-up half2 holds dims 2j, 2j+1 of one
-        // token; two permutes re-pair the same dim of two adjacent tokens
+        // The A fragment pairs the same dim of two adjacent tokens.  The table row of byte
+        // (nibble_lo | nibble_hi << 4) holds half2(level(lo), level(hi)), so an index byte made of
+        // the two TOKENS' nibbles of one dim returns the fragment register itself: per code word of
+        // a token pair, two logic ops build the index bytes of its even dims (lo) and odd dims (hi).
+        constexpr uint32_t kLoNib = 0x0F0F0F0Fu;
+        uint32_t ilo[2][2], ihi[2][2];  // [token pair][word]
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int pr = 0; pr < 2; ++pr) {
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+                const uint32_t wa = w ? cur.v[2 * pr].y : cur.v[2 * pr].x;          // token 2tig (+8)
+                const uint32_t wb = w ? cur.v[2 * pr + 1].y : cur.v[2 * pr + 1].x;  // token 2tig+1 (+8)
+                ilo[pr][w] = (wa & kLoNib) | (shl_mul<4>(wb) & ~kLoNib);
+                ihi[pr][w] = (shr_mul<4>(wa) & kLoNib) | (wb & ~kLoNib);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {  // tile j = byte j of the lane's 8 V bytes: dims 2j (row g), 2j+1 (row g+8)
             const uint32_t sel = 0x5504u | (static_cast<uint32_t>(j & 3) << 4);
-            const uint32_t e0 = lut_v(c.lut, j < 4 ? cur.v[0].x : cur.v[0].y, c.lane_v, sel);
-            const uint32_t e1 = lut_v(c.lut, j < 4 ? cur.v[1].x : cur.v[1].y, c.lane_v, sel);
-            const uint32_t e2 = lut_v(c.lut, j < 4 ? cur.v[2].x : cur.v[2].y, c.lane_v, sel);
-            const uint32_t e3 = lut_v(c.lut, j < 4 ? cur.v[3].x : cur.v[3].y, c.lane_v, sel);
-            mma16816(o[j], prmt(e0, e1, 0x5410u), prmt(e0, e1, 0x7632u), prmt(e2, e3, 0x5410u),
-                     prmt(e2, e3, 0x7632u), pb0, pb1);
+            const int w = j >> 2;
+            mma16816(o[j], lut_v(c.lut, ilo[0][w], c.lane_v, sel), lut_v(c.lut, ihi[0][w], c.lane_v, sel),
+                     lut_v(c.lut, ilo[1][w], c.lane_v, sel), lut_v(c.lut, ihi[1][w], c.lane_v, sel), pb0, pb1);
         }
     } else {
 #pragma unroll
