@@ -15,8 +15,10 @@
 //     lookups in registers (general kernel: 8-entry signed table for the 3-bit K code, 8-entry
 //     magnitude table plus a sign XOR for the 4-bit codes); the 1-bit residual sign is a second
 //     MMA with +-1 operands, scaled per token column (ks*re) afterwards;
-//   * V^T is the A operand of the second product; its k index runs over tokens, so operand
-//     halves of two adjacent tokens are paired in registers (no shared-memory transpose).
+//   * V^T is the A operand of the second product; its k index runs over tokens, so a fragment
+//     register pairs the same dim of two adjacent tokens: built in registers, by looking up an
+//     index byte made of the two tokens' nibbles (fast path) or by paired permutes (general
+//     kernel); no shared-memory transpose.
 // Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
 // and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
 #include <climits>
