@@ -1,0 +1,140 @@
+"""Disk store (turborag_b200/store.py): file names and manifest as the reference writes them
+(tq_backend/cag_store.py:24-157), and the GPU load path."""
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+ROOT = Path(__file__).resolve().parent.parent
+REFERENCE = Path("/root/reference")
+
+
+def test_names_and_manifest(tmp_path, lib_path):
+    from turborag_b200.store import CAGStore
+    st = CAGStore(tmp_path, lib_path)
+    import hashlib
+    h = hashlib.sha256(b"doc one").hexdigest()
+    assert st._key("doc one", 3, "turbo_prod") == f"{h[:16]}_L03_turbo_prod"
+    assert st._pool_path("doc one", 3, "turbo_mse").name == f"{h[:16]}_L03_turbo_mse.bin"
+    assert st._meta_path("doc one", 12, "fp16").name == f"{h[:16]}_L12_fp16.meta"
+    assert not st.exists("doc one", 3, "turbo_prod")
+    st._update_manifest("doc one", 3, "turbo_prod", 77)
+    st._update_manifest("doc one", 4, "turbo_prod", 77)
+    m = json.loads((tmp_path / "manifest.json").read_text())
+    assert m["v"] == 1 and m["entries"]["doc one"]["sha256"] == h
+    assert m["entries"]["doc one"]["layers"]["3::turbo_prod"]["key"] == f"{h[:16]}_L03_turbo_prod"
+    assert m["entries"]["doc one"]["layers"]["4::turbo_prod"]["num_tokens"] == 77
+    st._verify_manifest("doc one", 3, "turbo_prod")      # consistent
+    st._verify_manifest("never stored", 0, "turbo_prod")  # no entry: accepted
+    m["entries"]["doc one"]["sha256"] = "0" * 64
+    (tmp_path / "manifest.json").write_text(json.dumps(m))
+    with pytest.raises(RuntimeError, match="integrity"):
+        st._verify_manifest("doc one", 3, "turbo_prod")
+    m["entries"]["doc one"]["sha256"] = h
+    m["entries"]["doc one"]["layers"]["3::turbo_prod"]["key"] = "something_else"
+    (tmp_path / "manifest.json").write_text(json.dumps(m))
+    with pytest.raises(RuntimeError, match="key mismatch"):
+        st._verify_manifest("doc one", 3, "turbo_prod")
+    (tmp_path / "manifest.json").write_text("{ not json")
+    st._verify_manifest("doc one", 3, "turbo_prod")       # unreadable manifest = no manifest
+    with pytest.raises(FileNotFoundError):
+        st.load_document("doc one", 3, "turbo_prod", (2, 128))
+    assert st.vram_bytes("turbo_prod", 1143, (2, 128)) == 72 * 4288
+    assert st.vram_bytes("turbo_mse", 1143, (2, 128)) == 72 * 4608
+    assert st.vram_bytes("fp16", 1143, (2, 128)) == 1143 * 2 * 128 * 2 * 2
+
+
+@pytest.mark.skipif(not (REFERENCE / "tq_backend" / "cag_store.py").exists(),
+                    reason="the reference checkout is not on this machine")
+def test_reference_store_and_wrapper_accept_this_library(tmp_path, lib_path):
+    """The reference's own Python classes, unmodified, bound to this library: same file names, same
+    manifest, same layouts and byte counts (everything they do without a GPU)."""
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        from tq_backend.cag_store import CAGStore as RefStore
+    finally:
+        sys.path.remove(str(REFERENCE))
+    from turborag_b200.store import CAGStore
+    ref, mine = RefStore(tmp_path / "ref", lib_path), CAGStore(tmp_path / "mine", lib_path)
+    for doc, layer, scheme in [("a", 0, "turbo_prod"), ("long document id / with : chars", 35, "turbo_mse"),
+                               ("z", 7, "fp16")]:
+        assert ref._key(doc, layer, scheme) == mine._key(doc, layer, scheme)
+        assert ref._pool_path(doc, layer, scheme).name == mine._pool_path(doc, layer, scheme).name
+        assert ref._meta_path(doc, layer, scheme).name == mine._meta_path(doc, layer, scheme).name
+        ref._update_manifest(doc, layer, scheme, 123)
+        mine._update_manifest(doc, layer, scheme, 123)
+    a = json.loads((tmp_path / "ref" / "manifest.json").read_text())
+    b = json.loads((tmp_path / "mine" / "manifest.json").read_text())
+    for m in (a, b):
+        for e in m["entries"].values():
+            for l in e["layers"].values():
+                l.pop("stored_at")
+    assert a == b
+    for hs in [(2, 128), (4, 128), (8, 128)]:
+        for scheme in ("turbo_prod", "turbo_mse", "fp16"):
+            assert ref.vram_bytes(scheme, 1143, hs) == mine.vram_bytes(scheme, 1143, hs)
+        rc, mc = ref._make_cfg_from_shape(hs), mine._make_cfg_from_shape(hs)
+        rl, ml = ref.tq.make_layout_for(rc), mine.tq.make_layout_for(mc)
+        assert bytes(rl) == bytes(ml)
+        assert bytes(ref.tq.make_mse_layout_for(rc)) == bytes(mine.tq.make_mse_layout_for(mc))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse", "fp16"])
+def test_store_round_trip_on_gpu(tmp_path, lib_path, scheme):
+    from turborag_b200.store import CAGStore
+    dev = torch.device("cuda:0")
+    st = CAGStore(tmp_path, lib_path)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    n, h, d, layers = 1143, 2, 128, 3
+    kv = [(torch.randn(n, h, d, device=dev, generator=g).half(), torch.randn(n, h, d, device=dev, generator=g).half())
+          for _ in range(layers)]
+    for l, (k, v) in enumerate(kv):
+        size = st.pack_document("doc", l, k, v, scheme)
+        assert size == st._pool_path("doc", l, scheme).stat().st_size
+        assert st.pack_document("doc", l, k, v, scheme) == size  # second call: already there
+    if scheme != "fp16":
+        assert st._pool_path("doc", 0, scheme).stat().st_size == st.vram_bytes(scheme, n, (h, d))
+    # layer by layer, [N, H, D]
+    direct = []
+    for l, (k, v) in enumerate(kv):
+        dk, dv = st.load_as_kv_fp16("doc", l, scheme, (h, d))
+        assert dk.shape == (n, h, d) and dk.dtype == torch.float16
+        if scheme == "fp16":
+            assert torch.equal(dk, k) and torch.equal(dv, v)
+        else:
+            rel = ((dk.float() - k.float()).pow(2).mean() / k.float().pow(2).mean()).item()
+            assert rel < 0.35  # the reference's own round-trip bound (tests/test_cag.py:240-246)
+        direct.append((dk, dv))
+    # all layers, [1, H, N, D], reads overlapped with dequant: same bits as the layer-by-layer path
+    got, doc_len = st.load_layers_hnd("doc", layers + 2, scheme, (h, d))
+    assert doc_len == n and [l for l, _, _ in got] == list(range(layers))
+    for (l, k4, v4), (dk, dv) in zip(got, direct):
+        assert k4.shape == (1, h, n, d)
+        assert torch.equal(k4[0], dk.permute(1, 0, 2)) and torch.equal(v4[0], dv.permute(1, 0, 2))
+    cache, doc_len2 = st.build_dynamic_cache("doc", layers, scheme, (h, d))
+    assert doc_len2 == n
+    # attention over the stored pages: single query row per kv head (the reference call) and GQA
+    pool, slots, n2 = st.load_document("doc", 1, scheme, (h, d))
+    assert n2 == n
+    q = torch.randn(8, h, d, device=dev, generator=g).half()
+    out = st.fused_attention(q, pool, slots, n, scheme, (h, d))
+    dk, dv = direct[1]
+    ref = torch.softmax(torch.einsum("qhd,nhd->hqn", q.float(), dk.float()) * d ** -0.5, dim=-1)
+    ref = torch.einsum("hqn,nhd->qhd", ref, dv.float())
+    err = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
+    assert err < 5e-3, err  # against attention over the dequantised fp16 tensors
+    if scheme != "fp16":
+        pools = [st.load_document("doc", l, scheme, (h, d))[0] for l in range(layers)]
+        qb = torch.randn(layers, 16, d, device=dev, generator=g).half()
+        ob = st.decode_documents(qb, pools, [n] * layers, scheme, (h, d))
+        for l in range(layers):
+            # query head j belongs to kv head j // 8: rows [g, h] of the reference layout
+            ql = qb[l].view(h, 8, d).permute(1, 0, 2).contiguous()
+            want = st.fused_attention(ql, pools[l], slots, n, scheme, (h, d)).permute(1, 0, 2).reshape(16, d)
+            assert torch.allclose(ob[l].float(), want.float(), atol=2e-3, rtol=2e-3)

@@ -1,0 +1,314 @@
+"""Per-layer compressed-KV disk store, file-compatible with the reference's
+``tq_backend/cag_store.py`` (same method names, arguments and on-disk format), with the load
+path rebuilt for a B200 host.
+
+On-disk format (``tq_backend/cag_store.py:97-157``), kept bit-for-bit so stores written by either
+implementation can be read by the other:
+  * ``<sha256(doc_id)[:16]>_L<layer:02d>_<scheme>.bin``  -- the raw page pool
+    (``ceil(N / 16) * page_size_bytes`` bytes), or for scheme ``fp16`` a ``torch.save`` of
+    ``{"num_tokens", "kv", "shape"}``;
+  * ``...meta``  -- ``torch.save({"num_tokens": N, "slots": arange(N, int32)})``;
+  * ``manifest.json``  -- ``{"v": 1, "entries": {doc_id: {"sha256", "layers": {"<layer>::<scheme>":
+    {"key", "num_tokens", "stored_at"}}}}}``, written through a temporary file and a rename.
+
+What differs from the reference on the way back to the GPU (``cag_store.py:161-255``):
+  * the pool file is read straight into a reusable pinned host buffer (``readinto``: no
+    ``bytes -> bytearray -> frombuffer -> clone`` copies) and copied to the device on a side
+    stream, so the read of layer l+1 overlaps the dequant of layer l;
+  * ``build_dynamic_cache`` dequantises directly into the ``[1, H, N, D]`` layout a Hugging Face
+    cache wants (``tq_dequant_kv_hnd``), instead of ``[N, H, D]`` followed by
+    ``permute().contiguous()``;
+  * ``fused_attention`` accepts any number of query rows per kv head (GQA) and
+    ``decode_documents`` serves a batch of stored documents with one paged call.
+There is no CPU fallback: every tensor operation needs the CUDA library.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import time
+from pathlib import Path
+from typing import Literal
+
+import torch
+
+from .wrapper import TQConfig, TurboQuantWrapper
+
+Scheme = Literal["fp16", "turbo_prod", "turbo_mse"]
+_MANIFEST = "manifest.json"
+
+
+class CAGStore:
+    def __init__(self, store_dir: str | Path, lib_path: str | Path | None = None) -> None:
+        self.store_dir = Path(store_dir)
+        self.store_dir.mkdir(parents=True, exist_ok=True)
+        self.tq = TurboQuantWrapper(lib_path)
+        self._manifest_path = self.store_dir / _MANIFEST
+        self._pinned: list[torch.Tensor | None] = [None, None]  # two staging buffers, used in turn
+        self._copy_stream: torch.cuda.Stream | None = None
+
+    # ---- names and manifest -------------------------------------------------------------------
+    @staticmethod
+    def _doc_hash(doc_id: str) -> str:
+        return hashlib.sha256(doc_id.encode()).hexdigest()
+
+    def _key(self, doc_id: str, layer: int, scheme: Scheme) -> str:
+        return f"{self._doc_hash(doc_id)[:16]}_L{layer:02d}_{scheme}"
+
+    def _pool_path(self, doc_id: str, layer: int, scheme: Scheme) -> Path:
+        return self.store_dir / (self._key(doc_id, layer, scheme) + ".bin")
+
+    def _meta_path(self, doc_id: str, layer: int, scheme: Scheme) -> Path:
+        return self.store_dir / (self._key(doc_id, layer, scheme) + ".meta")
+
+    def exists(self, doc_id: str, layer: int, scheme: Scheme) -> bool:
+        return self._pool_path(doc_id, layer, scheme).exists()
+
+    def _load_manifest(self) -> dict:
+        try:
+            return json.loads(self._manifest_path.read_text())
+        except (FileNotFoundError, json.JSONDecodeError, OSError):
+            return {"v": 1, "entries": {}}
+
+    def _save_manifest(self, manifest: dict) -> None:
+        tmp = self._manifest_path.with_suffix(".tmp")
+        tmp.write_text(json.dumps(manifest, indent=2))
+        tmp.replace(self._manifest_path)  # a torn write never replaces a good manifest
+
+    def _update_manifest(self, doc_id: str, layer: int, scheme: Scheme, num_tokens: int) -> None:
+        manifest = self._load_manifest()
+        entry = manifest.setdefault("entries", {}).setdefault(doc_id, {"sha256": "", "layers": {}})
+        entry["sha256"] = self._doc_hash(doc_id)
+        entry.setdefault("layers", {})[f"{layer}::{scheme}"] = {
+            "key": self._key(doc_id, layer, scheme), "num_tokens": num_tokens, "stored_at": time.time()}
+        self._save_manifest(manifest)
+
+    def _verify_manifest(self, doc_id: str, layer: int, scheme: Scheme) -> None:
+        """RuntimeError when the manifest contradicts the file about to be read; a store without
+        a manifest entry for the document is accepted (older stores have none)."""
+        entry = self._load_manifest().get("entries", {}).get(doc_id)
+        if entry is None:
+            return
+        stored, computed = entry.get("sha256", ""), self._doc_hash(doc_id)
+        if stored and stored != computed:
+            raise RuntimeError(f"Manifest integrity error for doc_id={doc_id!r}: stored SHA-256 "
+                               f"{stored[:8]}... != computed {computed[:8]}...")
+        layer_entry = entry.get("layers", {}).get(f"{layer}::{scheme}")
+        if layer_entry and layer_entry.get("key") != self._key(doc_id, layer, scheme):
+            raise RuntimeError(f"Manifest key mismatch for doc_id={doc_id!r} layer={layer} scheme={scheme}: "
+                               f"stored {layer_entry.get('key')!r} != computed "
+                               f"{self._key(doc_id, layer, scheme)!r}")
+
+    # ---- configuration ------------------------------------------------------------------------
+    def _make_cfg_from_shape(self, head_shape: tuple[int, int]) -> TQConfig:
+        cfg = self.tq.default_config()
+        cfg.num_kv_heads, cfg.head_dim = head_shape
+        return cfg
+
+    def _make_cfg(self, key: torch.Tensor) -> TQConfig:
+        return self._make_cfg_from_shape((key.shape[1], key.shape[2]))
+
+    def _layout(self, scheme: Scheme, cfg: TQConfig):
+        if scheme == "turbo_prod":
+            return self.tq.make_layout_for(cfg)
+        if scheme == "turbo_mse":
+            return self.tq.make_mse_layout_for(cfg)
+        raise ValueError(f"Unknown scheme: {scheme}")
+
+    def _pool_bytes(self, scheme: Scheme, num_tokens: int, cfg: TQConfig) -> int:
+        pages = -(-num_tokens // cfg.block_size)
+        return pages * self._layout(scheme, cfg).page_size_bytes
+
+    def vram_bytes(self, scheme: Scheme, num_tokens: int, head_shape: tuple[int, int]) -> int:
+        cfg = self._make_cfg_from_shape(head_shape)
+        if scheme == "fp16":
+            return 2 * num_tokens * cfg.num_kv_heads * cfg.head_dim * 2
+        return self._pool_bytes(scheme, num_tokens, cfg)
+
+    # ---- offline: pack ------------------------------------------------------------------------
+    def pack_document(self, doc_id: str, layer: int, key: torch.Tensor, value: torch.Tensor,
+                      scheme: Scheme = "turbo_prod", overwrite: bool = False) -> int:
+        """Compress and save one layer's KV ([N, H, D] fp16 CUDA tensors); returns the bytes on disk."""
+        pool_p, meta_p = self._pool_path(doc_id, layer, scheme), self._meta_path(doc_id, layer, scheme)
+        if pool_p.exists() and not overwrite:
+            return pool_p.stat().st_size
+        n = key.shape[0]
+        slots = torch.arange(n, dtype=torch.int32, device=key.device)
+        if scheme == "fp16":
+            kv = torch.cat([key.reshape(-1), value.reshape(-1)]).cpu()
+            torch.save({"num_tokens": n, "kv": kv, "shape": list(key.shape)}, pool_p)
+        else:
+            cfg = self._make_cfg(key)
+            layout = self._layout(scheme, cfg)
+            pool = torch.zeros(self._pool_bytes(scheme, n, cfg), dtype=torch.uint8, device=key.device)
+            (self.tq.pack if scheme == "turbo_prod" else self.tq.mse_pack)(
+                key.contiguous(), value.contiguous(), slots, pool, layout, cfg)
+            host = torch.empty(pool.numel(), dtype=torch.uint8, pin_memory=True)
+            host.copy_(pool, non_blocking=True)
+            torch.cuda.current_stream(key.device).synchronize()
+            with pool_p.open("wb") as f:
+                f.write(memoryview(host.numpy()))
+        torch.save({"num_tokens": n, "slots": slots.cpu()}, meta_p)
+        self._update_manifest(doc_id, layer, scheme, n)
+        return pool_p.stat().st_size
+
+    # ---- online: load -------------------------------------------------------------------------
+    def _staging(self, which: int, nbytes: int) -> torch.Tensor:
+        buf = self._pinned[which]
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, pin_memory=True)
+            self._pinned[which] = buf
+        return buf
+
+    def _read_pool(self, doc_id: str, layer: int, scheme: Scheme, cfg: TQConfig, num_tokens: int,
+                   which: int, device: torch.device) -> tuple[torch.Tensor, torch.cuda.Event]:
+        """File -> pinned buffer -> device on the copy stream; returns the device pool and the
+        event that marks the end of the copy."""
+        nbytes = self._pool_bytes(scheme, num_tokens, cfg)
+        host = self._staging(which, nbytes)
+        with self._pool_path(doc_id, layer, scheme).open("rb", buffering=0) as f:
+            got = f.readinto(memoryview(host.numpy())[:nbytes])
+        if got != nbytes:
+            raise RuntimeError(f"{self._pool_path(doc_id, layer, scheme)}: {got} bytes, expected {nbytes} "
+                               f"(wrong head_shape, or a stale store)")
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device)
+        pool = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        done = torch.cuda.Event()
+        with torch.cuda.stream(self._copy_stream):
+            pool.copy_(host[:nbytes], non_blocking=True)
+            done.record()
+        return pool, done
+
+    def load_document(self, doc_id: str, layer: int, scheme: Scheme = "turbo_prod",
+                      head_shape: tuple[int, int] = (2, 64)) -> tuple[torch.Tensor, torch.Tensor, int]:
+        """Load compressed KV to CUDA.  Returns (pool or (key, value), slots, num_tokens)."""
+        pool_p = self._pool_path(doc_id, layer, scheme)
+        if not pool_p.exists():
+            raise FileNotFoundError(f"No pre-computed KV: doc={doc_id} layer={layer} scheme={scheme}")
+        self._verify_manifest(doc_id, layer, scheme)
+        meta = torch.load(self._meta_path(doc_id, layer, scheme), weights_only=False)
+        n, slots = int(meta["num_tokens"]), meta["slots"]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        if scheme == "fp16":
+            kv = torch.load(pool_p, weights_only=False)["kv"].to(dev, non_blocking=True)
+            h, d = head_shape
+            return (kv[:n * h * d].reshape(n, h, d).contiguous(),
+                    kv[n * h * d:].reshape(n, h, d).contiguous()), slots.to(dev), n
+        cfg = self._make_cfg_from_shape(head_shape)
+        pool, done = self._read_pool(doc_id, layer, scheme, cfg, n, 0, dev)
+        torch.cuda.current_stream(dev).wait_event(done)
+        # the staging buffer is reused by the next call: the copy out of it must have finished
+        done.synchronize()
+        return pool, slots.to(dev), n
+
+    def load_as_kv_fp16(self, doc_id: str, layer: int, scheme: Scheme,
+                        head_shape: tuple[int, int] = (2, 64)) -> tuple[torch.Tensor, torch.Tensor]:
+        """Load and dequantise one layer -> (key, value), each [N, H, D] fp16 CUDA."""
+        pool, slots, n = self.load_document(doc_id, layer, scheme, head_shape)
+        if scheme == "fp16":
+            return pool
+        cfg = self._make_cfg_from_shape(head_shape)
+        h, d = head_shape
+        out_k = torch.empty(n, h, d, device=slots.device, dtype=torch.float16)
+        out_v = torch.empty_like(out_k)
+        (self.tq.dequant if scheme == "turbo_prod" else self.tq.mse_dequant)(
+            pool, slots, out_k, out_v, self._layout(scheme, cfg), cfg)
+        return out_k, out_v
+
+    def load_layers_hnd(self, doc_id: str, num_layers: int, scheme: Scheme,
+                        head_shape: tuple[int, int] = (2, 64)) -> tuple[list, int]:
+        """[(layer, key, value)] with key/value [1, H, N, D] fp16 CUDA for every stored layer, and
+        the document length.  The file read and host-to-device copy of the next layer run while
+        the current one is dequantised."""
+        dev = torch.device("cuda", torch.cuda.current_device())
+        layers = [l for l in range(num_layers) if self.exists(doc_id, l, scheme)]
+        out, doc_len = [], 0
+        if scheme == "fp16":
+            for l in layers:
+                k, v = self.load_as_kv_fp16(doc_id, l, scheme, head_shape)
+                out.append((l, k.permute(1, 0, 2).unsqueeze(0).contiguous(),
+                            v.permute(1, 0, 2).unsqueeze(0).contiguous()))
+                doc_len = doc_len or k.shape[0]
+            return out, doc_len
+        cfg = self._make_cfg_from_shape(head_shape)
+        layout = self._layout(scheme, cfg)
+        h, d = head_shape
+        metas = {}
+        for l in layers:
+            self._verify_manifest(doc_id, l, scheme)
+            meta = torch.load(self._meta_path(doc_id, l, scheme), weights_only=False)
+            metas[l] = (int(meta["num_tokens"]), meta["slots"])
+        pending = None
+        copies_in_flight: list[torch.cuda.Event | None] = [None, None]
+        for i, l in enumerate(layers):
+            if pending is None:
+                pending = self._read_pool(doc_id, l, scheme, cfg, metas[l][0], i & 1, dev)
+                copies_in_flight[i & 1] = pending[1]
+            pool, done = pending
+            pending = None
+            if i + 1 < len(layers):  # start the next layer's read + copy before this layer's dequant
+                nxt = layers[i + 1]
+                if copies_in_flight[(i + 1) & 1] is not None:
+                    copies_in_flight[(i + 1) & 1].synchronize()  # its staging buffer is free again
+                pending = self._read_pool(doc_id, nxt, scheme, cfg, metas[nxt][0], (i + 1) & 1, dev)
+                copies_in_flight[(i + 1) & 1] = pending[1]
+            n, slots = metas[l]
+            torch.cuda.current_stream(dev).wait_event(done)
+            k = torch.empty(1, h, n, d, device=dev, dtype=torch.float16)
+            v = torch.empty_like(k)
+            self.tq.dequant_hnd(scheme, pool, slots.to(dev), k, v, layout, cfg)
+            out.append((l, k, v))
+            doc_len = doc_len or n
+        for ev in copies_in_flight:
+            if ev is not None:
+                ev.synchronize()
+        return out, doc_len
+
+    def build_dynamic_cache(self, doc_id: str, num_layers: int, scheme: Scheme,
+                            head_shape: tuple[int, int] = (2, 64)):
+        """Hugging Face ``DynamicCache`` from the stored layers; returns (cache, doc_num_tokens)."""
+        from transformers import DynamicCache
+        cache = DynamicCache()
+        layers, doc_len = self.load_layers_hnd(doc_id, num_layers, scheme, head_shape)
+        for l, k, v in layers:
+            cache.update(k, v, l)
+        return cache, doc_len
+
+    # ---- attention over stored pages ------------------------------------------------------------
+    def fused_attention(self, query: torch.Tensor, pool, slots: torch.Tensor, N: int, scheme: Scheme,
+                        head_shape: tuple[int, int] = (2, 64)) -> torch.Tensor:
+        """Compressed-KV attention; ``query`` [Q, H, D] fp16 (Q rows per kv head), returns [Q, H, D]."""
+        if scheme == "fp16":
+            key, value = pool
+            q, k, v = query.permute(1, 0, 2).float(), key.permute(1, 0, 2).float(), value.permute(1, 0, 2).float()
+            attn = torch.softmax(torch.bmm(q, k.transpose(1, 2)) * head_shape[1] ** -0.5, dim=-1)
+            return torch.bmm(attn, v).permute(1, 0, 2).to(query.dtype)
+        cfg = self._make_cfg_from_shape(head_shape)
+        output = torch.empty_like(query)
+        fn = self.tq.fused_attn_output if scheme == "turbo_prod" else self.tq.mse_fused_attn_output
+        fn(query.contiguous(), pool, slots, output, self._layout(scheme, cfg), cfg, query.shape[0], N)
+        return output
+
+    def decode_documents(self, query: torch.Tensor, pools: list[torch.Tensor], lengths: list[int],
+                         scheme: Scheme, head_shape: tuple[int, int] = (2, 64)) -> torch.Tensor:
+        """One paged GQA decode over a batch of stored documents: ``query`` [B, Hq, D] fp16 (query
+        head j belongs to kv head j // (Hq / H)), ``pools[b]`` the loaded pool of document b with
+        identity slots (what ``pack_document`` writes), ``lengths[b]`` its token count."""
+        if scheme == "fp16":
+            raise ValueError("decode_documents serves the compressed schemes")
+        cfg = self._make_cfg_from_shape(head_shape)
+        layout = self._layout(scheme, cfg)
+        page = layout.page_size_bytes
+        pages = [p.numel() // page for p in pools]
+        pool = torch.cat(pools)
+        width = max(max(pages), 1)
+        tables = torch.zeros(len(pools), width, dtype=torch.int32)
+        first = 0
+        for b, n in enumerate(pages):
+            tables[b, :n] = torch.arange(first, first + n, dtype=torch.int32)
+            first += n
+        dev = query.device
+        return self.tq.decode_paged(scheme, query.contiguous(), pool, tables.to(dev),
+                                    torch.tensor(lengths, dtype=torch.int32, device=dev), layout, cfg,
+                                    max_kv_tokens=max(lengths))
