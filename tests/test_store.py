@@ -39,6 +39,14 @@ def test_names_and_manifest(tmp_path, lib_path):
     (tmp_path / "manifest.json").write_text(json.dumps(m))
     with pytest.raises(RuntimeError, match="key mismatch"):
         st._verify_manifest("doc one", 3, "turbo_prod")
+    # a record that says what the bytes mean refuses a load with another head shape
+    m["entries"]["doc one"]["layers"]["3::turbo_prod"]["key"] = f"{h[:16]}_L03_turbo_prod"
+    (tmp_path / "manifest.json").write_text(json.dumps(m))
+    st._update_manifest("doc one", 5, "turbo_prod", 77, (2, 128))
+    st._verify_manifest("doc one", 5, "turbo_prod", (2, 128))
+    st._verify_manifest("doc one", 5, "turbo_prod")  # no shape given: nothing to compare
+    with pytest.raises(RuntimeError, match="head shape"):
+        st._verify_manifest("doc one", 5, "turbo_prod", (4, 128))
     (tmp_path / "manifest.json").write_text("{ not json")
     st._verify_manifest("doc one", 3, "turbo_prod")       # unreadable manifest = no manifest
     with pytest.raises(FileNotFoundError):

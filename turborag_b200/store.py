@@ -9,7 +9,10 @@ implementation can be read by the other:
     ``{"num_tokens", "kv", "shape"}``;
   * ``...meta``  -- ``torch.save({"num_tokens": N, "slots": arange(N, int32)})``;
   * ``manifest.json``  -- ``{"v": 1, "entries": {doc_id: {"sha256", "layers": {"<layer>::<scheme>":
-    {"key", "num_tokens", "stored_at"}}}}}``, written through a temporary file and a rename.
+    {"key", "num_tokens", "stored_at"}}}}}``, written through a temporary file and a rename.  This
+    implementation adds ``head_shape`` and ``page_size_bytes`` to a layer record (the reference
+    ignores fields it does not know) and refuses a load that contradicts them: the format itself
+    is unversioned and stale pages would otherwise decode to garbage silently.
 
 What differs from the reference on the way back to the GPU (``cag_store.py:161-255``):
   * the pool file is read straight into a reusable pinned host buffer (``readinto``: no
@@ -75,18 +78,26 @@ class CAGStore:
         tmp.write_text(json.dumps(manifest, indent=2))
         tmp.replace(self._manifest_path)  # a torn write never replaces a good manifest
 
-    def _update_manifest(self, doc_id: str, layer: int, scheme: Scheme, num_tokens: int) -> None:
+    def _update_manifest(self, doc_id: str, layer: int, scheme: Scheme, num_tokens: int,
+                         head_shape: tuple[int, int] | None = None) -> None:
         manifest = self._load_manifest()
         entry = manifest.setdefault("entries", {}).setdefault(doc_id, {"sha256": "", "layers": {}})
         entry["sha256"] = self._doc_hash(doc_id)
-        entry.setdefault("layers", {})[f"{layer}::{scheme}"] = {
-            "key": self._key(doc_id, layer, scheme), "num_tokens": num_tokens, "stored_at": time.time()}
+        rec = {"key": self._key(doc_id, layer, scheme), "num_tokens": num_tokens, "stored_at": time.time()}
+        if head_shape is not None:
+            # Not in the reference's manifest (it ignores unknown fields): what the bytes mean, so that
+            # a load with another head shape or page geometry fails instead of decoding garbage.
+            rec["head_shape"] = [int(head_shape[0]), int(head_shape[1])]
+            if scheme != "fp16":
+                rec["page_size_bytes"] = int(self._layout(scheme, self._make_cfg_from_shape(head_shape)).page_size_bytes)
+        entry.setdefault("layers", {})[f"{layer}::{scheme}"] = rec
         self._save_manifest(manifest)
 
-    def _verify_manifest(self, doc_id: str, layer: int, scheme: Scheme) -> None:
+    def _verify_manifest(self, doc_id: str, layer: int, scheme: Scheme,
+                         head_shape: tuple[int, int] | None = None, manifest: dict | None = None) -> None:
         """RuntimeError when the manifest contradicts the file about to be read; a store without
         a manifest entry for the document is accepted (older stores have none)."""
-        entry = self._load_manifest().get("entries", {}).get(doc_id)
+        entry = (manifest if manifest is not None else self._load_manifest()).get("entries", {}).get(doc_id)
         if entry is None:
             return
         stored, computed = entry.get("sha256", ""), self._doc_hash(doc_id)
@@ -98,6 +109,15 @@ class CAGStore:
             raise RuntimeError(f"Manifest key mismatch for doc_id={doc_id!r} layer={layer} scheme={scheme}: "
                                f"stored {layer_entry.get('key')!r} != computed "
                                f"{self._key(doc_id, layer, scheme)!r}")
+        if layer_entry and head_shape is not None and "head_shape" in layer_entry:
+            if list(layer_entry["head_shape"]) != [int(head_shape[0]), int(head_shape[1])]:
+                raise RuntimeError(f"doc_id={doc_id!r} layer={layer} scheme={scheme} was stored with head shape "
+                                   f"{tuple(layer_entry['head_shape'])}, asked for {tuple(head_shape)}")
+            if scheme != "fp16" and "page_size_bytes" in layer_entry:
+                page = int(self._layout(scheme, self._make_cfg_from_shape(head_shape)).page_size_bytes)
+                if int(layer_entry["page_size_bytes"]) != page:
+                    raise RuntimeError(f"doc_id={doc_id!r} layer={layer} scheme={scheme}: stored pages are "
+                                       f"{layer_entry['page_size_bytes']} bytes, this build uses {page}")
 
     # ---- configuration ------------------------------------------------------------------------
     def _make_cfg_from_shape(self, head_shape: tuple[int, int]) -> TQConfig:
@@ -149,7 +169,7 @@ class CAGStore:
             with pool_p.open("wb") as f:
                 f.write(memoryview(host.numpy()))
         torch.save({"num_tokens": n, "slots": slots.cpu()}, meta_p)
-        self._update_manifest(doc_id, layer, scheme, n)
+        self._update_manifest(doc_id, layer, scheme, n, (key.shape[1], key.shape[2]))
         return pool_p.stat().st_size
 
     # ---- online: load -------------------------------------------------------------------------
@@ -186,7 +206,7 @@ class CAGStore:
         pool_p = self._pool_path(doc_id, layer, scheme)
         if not pool_p.exists():
             raise FileNotFoundError(f"No pre-computed KV: doc={doc_id} layer={layer} scheme={scheme}")
-        self._verify_manifest(doc_id, layer, scheme)
+        self._verify_manifest(doc_id, layer, scheme, head_shape)
         meta = torch.load(self._meta_path(doc_id, layer, scheme), weights_only=False)
         n, slots = int(meta["num_tokens"]), meta["slots"]
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -234,11 +254,23 @@ class CAGStore:
         cfg = self._make_cfg_from_shape(head_shape)
         layout = self._layout(scheme, cfg)
         h, d = head_shape
-        metas = {}
+        # one manifest read for the whole document; the token count comes from the manifest record
+        # when there is one (pack_document always writes slots = arange(N), which is rebuilt on the
+        # device), else from the .meta file as in the reference
+        manifest = self._load_manifest()
+        records = manifest.get("entries", {}).get(doc_id, {}).get("layers", {})
+        metas, identity = {}, {}
         for l in layers:
-            self._verify_manifest(doc_id, l, scheme)
-            meta = torch.load(self._meta_path(doc_id, l, scheme), weights_only=False)
-            metas[l] = (int(meta["num_tokens"]), meta["slots"])
+            self._verify_manifest(doc_id, l, scheme, head_shape, manifest)
+            rec = records.get(f"{l}::{scheme}")
+            if rec and "num_tokens" in rec:
+                n = int(rec["num_tokens"])
+                if n not in identity:
+                    identity[n] = torch.arange(n, dtype=torch.int32, device=dev)
+                metas[l] = (n, identity[n])
+            else:
+                meta = torch.load(self._meta_path(doc_id, l, scheme), weights_only=False)
+                metas[l] = (int(meta["num_tokens"]), meta["slots"].to(dev))
         pending = None
         copies_in_flight: list[torch.cuda.Event | None] = [None, None]
         for i, l in enumerate(layers):
@@ -257,7 +289,7 @@ class CAGStore:
             torch.cuda.current_stream(dev).wait_event(done)
             k = torch.empty(1, h, n, d, device=dev, dtype=torch.float16)
             v = torch.empty_like(k)
-            self.tq.dequant_hnd(scheme, pool, slots.to(dev), k, v, layout, cfg)
+            self.tq.dequant_hnd(scheme, pool, slots, k, v, layout, cfg)
             out.append((l, k, v))
             doc_len = doc_len or n
         for ev in copies_in_flight:
