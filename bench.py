@@ -594,10 +594,18 @@ def load_numbers(torch, dev, gen, tokens, layers):
             torch.cuda.synchronize()
             return out
 
-        a, b = ours(), reference_style()
-        same = all(torch.equal(x[1], y[1]) and torch.equal(x[2], y[2]) for x, y in zip(a, b))
+        st.export_container("doc", layers, "turbo_prod", (H, D))
+
+        def container():
+            out, n = st.load_container_hnd("doc", "turbo_prod", (H, D))
+            torch.cuda.synchronize()
+            return out
+
+        a, b, c = ours(), reference_style(), container()
+        same = all(torch.equal(x[1], y[1]) and torch.equal(x[2], y[2]) and torch.equal(x[1], z[1]) and
+                   torch.equal(x[2], z[2]) for x, y, z in zip(a, b, c))
         times = {}
-        for name, fn in (("ours_ms", ours), ("reference_style_ms", reference_style)):
+        for name, fn in (("ours_ms", ours), ("container_ms", container), ("reference_style_ms", reference_style)):
             best = 1e9
             for _ in range(5):
                 t0 = time.perf_counter()

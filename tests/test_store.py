@@ -146,3 +146,82 @@ def test_store_round_trip_on_gpu(tmp_path, lib_path, scheme):
             ql = qb[l].view(h, 8, d).permute(1, 0, 2).contiguous()
             want = st.fused_attention(ql, pools[l], slots, n, scheme, (h, d)).permute(1, 0, 2).reshape(16, d)
             assert torch.allclose(ob[l].float(), want.float(), atol=2e-3, rtol=2e-3)
+
+
+def _fake_layers(st, doc, scheme, n, layers, head_shape=(2, 128)):
+    """Per-layer files with random bytes of the right size (no GPU needed to test the container)."""
+    rng = np.random.default_rng(3)
+    cfg = st._make_cfg_from_shape(head_shape)
+    blobs = []
+    for l in layers:
+        blob = rng.integers(0, 256, st._pool_bytes(scheme, n, cfg), dtype=np.uint8).tobytes()
+        st._pool_path(doc, l, scheme).write_bytes(blob)
+        torch.save({"num_tokens": n, "slots": torch.arange(n, dtype=torch.int32)}, st._meta_path(doc, l, scheme))
+        st._update_manifest(doc, l, scheme, n, head_shape)
+        blobs.append(blob)
+    return blobs
+
+
+def test_container_header_and_damage_detection(tmp_path, lib_path):
+    import struct
+    import zlib
+    from turborag_b200.store import CAGStore
+    st = CAGStore(tmp_path, lib_path)
+    blobs = _fake_layers(st, "doc", "turbo_mse", 77, [0, 1, 3])
+    path = st.export_container("doc", 6, "turbo_mse", (2, 128))
+    assert path.name.endswith("_turbo_mse.tqdoc")
+    with path.open("rb") as f:
+        hd = st.read_container_header(f)
+        assert hd["scheme"] == "turbo_mse" and hd["num_tokens"] == 77 and hd["head_shape"] == (2, 128)
+        assert hd["layers"] == [0, 1, 3] and hd["block_size"] == 16 and hd["page_size_bytes"] == 4608
+        assert hd["layer_bytes"] == 5 * 4608 and hd["layer_stride"] % 4096 == 0 and hd["header_bytes"] % 4096 == 0
+        for i, blob in enumerate(blobs):
+            f.seek(hd["header_bytes"] + i * hd["layer_stride"])
+            assert f.read(hd["layer_bytes"]) == blob and zlib.crc32(blob) == hd["crc32"][i]
+    raw = bytearray(path.read_bytes())
+    for offset, what in [(0, "magic"), (8, "version"), (24, "checksum"), (70, "checksum")]:
+        bad = bytearray(raw)
+        bad[offset] ^= 0x01
+        p2 = tmp_path / "bad.tqdoc"
+        p2.write_bytes(bad)
+        with p2.open("rb") as f, pytest.raises(RuntimeError, match=what):
+            st.read_container_header(f)
+    with pytest.raises(RuntimeError, match="head shape"):
+        st.export_container("doc", 6, "turbo_mse", (4, 128))  # the manifest knows the stored shape
+    with pytest.raises(FileNotFoundError):
+        st.export_container("other", 6, "turbo_mse", (2, 128))
+    assert struct.calcsize("<8sIIIIQIIIIQQ") == 64
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse"])
+def test_container_load_matches_per_layer_files(tmp_path, lib_path, scheme):
+    from turborag_b200.store import CAGStore
+    dev = torch.device("cuda:0")
+    st = CAGStore(tmp_path, lib_path)
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    n, h, d, layers = 1143, 2, 128, 4
+    for l in range(layers):
+        st.pack_document("doc", l, torch.randn(n, h, d, device=dev, generator=g).half(),
+                         torch.randn(n, h, d, device=dev, generator=g).half(), scheme)
+    want, n0 = st.load_layers_hnd("doc", layers, scheme, (h, d))
+    path = st.export_container("doc", layers, scheme, (h, d))
+    for verify in (False, True):
+        got, n1 = st.load_container_hnd("doc", scheme, (h, d), verify=verify)
+        assert n1 == n0 == n and [x[0] for x in got] == list(range(layers))
+        for (_, k, v), (_, k0, v0) in zip(got, want):
+            assert torch.equal(k, k0) and torch.equal(v, v0)
+    pools, _ = st.load_container_pools("doc", scheme)
+    for l, pool in pools:
+        assert torch.equal(pool, st.load_document("doc", l, scheme, (h, d))[0])
+    with pytest.raises(RuntimeError, match="head shape"):
+        st.load_container_hnd("doc", scheme, (4, 128))
+    # one flipped byte in the third layer: found when asked to verify
+    with path.open("rb") as f:
+        hd = st.read_container_header(f)
+    raw = bytearray(path.read_bytes())
+    raw[hd["header_bytes"] + 2 * hd["layer_stride"] + 100] ^= 0x40
+    path.write_bytes(raw)
+    with pytest.raises(RuntimeError, match="checksum mismatch in layer 2"):
+        st.load_container_hnd("doc", scheme, (h, d), verify=True)

@@ -12,7 +12,10 @@ implementation can be read by the other:
     {"key", "num_tokens", "stored_at"}}}}}``, written through a temporary file and a rename.  This
     implementation adds ``head_shape`` and ``page_size_bytes`` to a layer record (the reference
     ignores fields it does not know) and refuses a load that contradicts them: the format itself
-    is unversioned and stale pages would otherwise decode to garbage silently.
+    is unversioned and stale pages would otherwise decode to garbage silently;
+  * ``<sha256(doc_id)[:16]>_<scheme>.tqdoc`` (this implementation only, ``export_container``) -- all
+    layers of a document in one file behind a versioned, checksummed header that states scheme,
+    head shape, page geometry and token count; read front to back by ``load_container_hnd``.
 
 What differs from the reference on the way back to the GPU (``cag_store.py:161-255``):
   * the pool file is read straight into a reusable pinned host buffer (``readinto``: no
@@ -29,7 +32,9 @@ from __future__ import annotations
 
 import hashlib
 import json
+import struct
 import time
+import zlib
 from pathlib import Path
 from typing import Literal
 
@@ -39,6 +44,24 @@ from .wrapper import TQConfig, TurboQuantWrapper
 
 Scheme = Literal["fp16", "turbo_prod", "turbo_mse"]
 _MANIFEST = "manifest.json"
+
+# One-file-per-document container (not in the reference, whose per-layer files carry no header):
+#   fixed part  "<8sIIIIQIIIIQQ": magic, version, header_bytes, scheme (0 turbo_prod, 1 turbo_mse),
+#               num_layers, num_tokens, num_kv_heads, head_dim, block_size, page_size_bytes,
+#               layer_bytes, layer_stride
+#   then        num_layers x "<II": layer index, CRC-32 of that layer's pool
+#   then        "<I": CRC-32 of every header byte before it
+#   padding to header_bytes (a multiple of 4096); layer i's pool at header_bytes + i * layer_stride
+#   (layer_stride = layer_bytes rounded up to 4096, so every pool starts on a page of the file).
+_DOC_MAGIC = b"TQCAGDOC"
+_DOC_VERSION = 1
+_DOC_FIXED = struct.Struct("<8sIIIIQIIIIQQ")
+_DOC_ALIGN = 4096
+_SCHEME_IDS = {"turbo_prod": 0, "turbo_mse": 1}
+
+
+def _align_up(x: int, a: int) -> int:
+    return -(-x // a) * a
 
 
 class CAGStore:
@@ -296,6 +319,158 @@ class CAGStore:
             if ev is not None:
                 ev.synchronize()
         return out, doc_len
+
+    # ---- one file per document ----------------------------------------------------------------
+    def container_path(self, doc_id: str, scheme: Scheme) -> Path:
+        return self.store_dir / f"{self._doc_hash(doc_id)[:16]}_{scheme}.tqdoc"
+
+    def export_container(self, doc_id: str, num_layers: int, scheme: Scheme,
+                         head_shape: tuple[int, int] = (2, 64)) -> Path:
+        """Gather the per-layer files of a stored document into one versioned, self-describing
+        file that can be streamed front to back (layout at the top of this module).  Host only."""
+        if scheme not in _SCHEME_IDS:
+            raise ValueError("containers hold the compressed schemes")
+        layers = [l for l in range(num_layers) if self.exists(doc_id, l, scheme)]
+        if not layers:
+            raise FileNotFoundError(f"No pre-computed KV: doc={doc_id} scheme={scheme}")
+        cfg = self._make_cfg_from_shape(head_shape)
+        page = int(self._layout(scheme, cfg).page_size_bytes)
+        manifest = self._load_manifest()
+        sizes = set()
+        for l in layers:
+            self._verify_manifest(doc_id, l, scheme, head_shape, manifest)
+            sizes.add(self._pool_path(doc_id, l, scheme).stat().st_size)
+        if len(sizes) != 1:
+            raise RuntimeError(f"doc_id={doc_id!r}: layers of different sizes {sorted(sizes)}")
+        layer_bytes = sizes.pop()
+        n = int(torch.load(self._meta_path(doc_id, layers[0], scheme), weights_only=False)["num_tokens"])
+        if layer_bytes != self._pool_bytes(scheme, n, cfg):
+            raise RuntimeError(f"doc_id={doc_id!r}: {layer_bytes}-byte pools do not hold {n} tokens of head shape "
+                               f"{tuple(head_shape)}")
+        stride = _align_up(layer_bytes, _DOC_ALIGN)
+        header_bytes = _align_up(_DOC_FIXED.size + 8 * len(layers) + 4, _DOC_ALIGN)
+        final, tmp = self.container_path(doc_id, scheme), self.container_path(doc_id, scheme).with_suffix(".tmp")
+        table = b""
+        with tmp.open("wb") as f:
+            f.truncate(header_bytes + stride * len(layers))
+            for i, l in enumerate(layers):
+                data = self._pool_path(doc_id, l, scheme).read_bytes()
+                table += struct.pack("<II", l, zlib.crc32(data))
+                f.seek(header_bytes + i * stride)
+                f.write(data)
+            head = _DOC_FIXED.pack(_DOC_MAGIC, _DOC_VERSION, header_bytes, _SCHEME_IDS[scheme], len(layers), n,
+                                   cfg.num_kv_heads, cfg.head_dim, cfg.block_size, page, layer_bytes, stride) + table
+            f.seek(0)
+            f.write(head + struct.pack("<I", zlib.crc32(head)))
+        tmp.replace(final)
+        return final
+
+    @staticmethod
+    def read_container_header(f) -> dict:
+        """Parse and check the header of an open container; raises RuntimeError on a file that is
+        not a container of this version or whose header bytes were damaged."""
+        fixed = f.read(_DOC_FIXED.size)
+        if len(fixed) != _DOC_FIXED.size:
+            raise RuntimeError("container: file shorter than its header")
+        (magic, version, header_bytes, scheme_id, num_layers, n, h, d, block, page, layer_bytes,
+         stride) = _DOC_FIXED.unpack(fixed)
+        if magic != _DOC_MAGIC:
+            raise RuntimeError("container: bad magic (not a document container)")
+        if version != _DOC_VERSION:
+            raise RuntimeError(f"container: version {version}, this build reads version {_DOC_VERSION}")
+        if num_layers > (1 << 16) or header_bytes < _DOC_FIXED.size + 8 * num_layers + 4:
+            raise RuntimeError("container: implausible header")
+        table = f.read(8 * num_layers)
+        crc = f.read(4)
+        if len(table) != 8 * num_layers or len(crc) != 4 or struct.unpack("<I", crc)[0] != zlib.crc32(fixed + table):
+            raise RuntimeError("container: header checksum mismatch")
+        pairs = [struct.unpack_from("<II", table, 8 * i) for i in range(num_layers)]
+        scheme = {v: k for k, v in _SCHEME_IDS.items()}.get(scheme_id)
+        if scheme is None:
+            raise RuntimeError(f"container: unknown scheme id {scheme_id}")
+        return {"scheme": scheme, "num_tokens": n, "head_shape": (h, d), "block_size": block,
+                "page_size_bytes": page, "layer_bytes": layer_bytes, "layer_stride": stride,
+                "header_bytes": header_bytes, "layers": [p[0] for p in pairs], "crc32": [p[1] for p in pairs]}
+
+    def _stream_container(self, doc_id: str, scheme: Scheme, head_shape, verify: bool, consume) -> int:
+        """Read a container front to back: layer i goes file -> pinned buffer (i & 1) -> device on
+        the copy stream while ``consume(layer, pool, copied_event, header)`` of layer i - 1 is
+        still running.  Returns the document length."""
+        path = self.container_path(doc_id, scheme)
+        if not path.exists():
+            raise FileNotFoundError(f"No container: doc={doc_id} scheme={scheme}")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(dev)
+        with path.open("rb", buffering=0) as f:
+            hd = self.read_container_header(f)
+            cfg = self._make_cfg_from_shape(hd["head_shape"])
+            page = int(self._layout(scheme, cfg).page_size_bytes)
+            want = self._pool_bytes(scheme, hd["num_tokens"], cfg)
+            if hd["scheme"] != scheme or (head_shape is not None and tuple(head_shape) != tuple(hd["head_shape"])):
+                raise RuntimeError(f"container holds {hd['scheme']} with head shape {hd['head_shape']}, asked for "
+                                   f"{scheme} {tuple(head_shape) if head_shape else ''}")
+            if hd["block_size"] != cfg.block_size or hd["page_size_bytes"] != page or hd["layer_bytes"] != want:
+                raise RuntimeError(f"container pages ({hd['block_size']} tokens, {hd['page_size_bytes']} bytes, "
+                                   f"{hd['layer_bytes']} per layer) do not match this build "
+                                   f"({cfg.block_size}, {page}, {want})")
+            nbytes = hd["layer_bytes"]
+            in_flight: list[torch.cuda.Event | None] = [None, None]
+            for i, l in enumerate(hd["layers"]):
+                if in_flight[i & 1] is not None:
+                    in_flight[i & 1].synchronize()  # the staging buffer is free again
+                host = self._staging(i & 1, nbytes)
+                f.seek(hd["header_bytes"] + i * hd["layer_stride"])
+                view = memoryview(host.numpy())[:nbytes]
+                if f.readinto(view) != nbytes:
+                    raise RuntimeError(f"{path}: truncated at layer {l}")
+                if verify and zlib.crc32(view) != hd["crc32"][i]:
+                    raise RuntimeError(f"{path}: checksum mismatch in layer {l}")
+                pool = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                done = torch.cuda.Event()
+                with torch.cuda.stream(self._copy_stream):
+                    pool.copy_(host[:nbytes], non_blocking=True)
+                    done.record()
+                in_flight[i & 1] = done
+                consume(l, pool, done, hd)
+            for ev in in_flight:
+                if ev is not None:
+                    ev.synchronize()
+        return hd["num_tokens"]
+
+    def load_container_pools(self, doc_id: str, scheme: Scheme, head_shape: tuple[int, int] | None = None,
+                             verify: bool = False) -> tuple[list, int]:
+        """[(layer, pool)] on the device (pages stay compressed) and the document length."""
+        out = []
+        dev = torch.device("cuda", torch.cuda.current_device())
+
+        def consume(l, pool, done, hd):
+            torch.cuda.current_stream(dev).wait_event(done)
+            out.append((l, pool))
+        n = self._stream_container(doc_id, scheme, head_shape, verify, consume)
+        return out, n
+
+    def load_container_hnd(self, doc_id: str, scheme: Scheme, head_shape: tuple[int, int] | None = None,
+                           verify: bool = False) -> tuple[list, int]:
+        """``load_layers_hnd`` from a container: [(layer, key, value)] with [1, H, N, D] fp16 tensors."""
+        out = []
+        dev = torch.device("cuda", torch.cuda.current_device())
+        state = {}
+
+        def consume(l, pool, done, hd):
+            if not state:
+                h, d = hd["head_shape"]
+                state["cfg"] = self._make_cfg_from_shape((h, d))
+                state["layout"] = self._layout(scheme, state["cfg"])
+                state["slots"] = torch.arange(hd["num_tokens"], dtype=torch.int32, device=dev)
+            h, d = hd["head_shape"]
+            torch.cuda.current_stream(dev).wait_event(done)
+            k = torch.empty(1, h, hd["num_tokens"], d, device=dev, dtype=torch.float16)
+            v = torch.empty_like(k)
+            self.tq.dequant_hnd(scheme, pool, state["slots"], k, v, state["layout"], state["cfg"])
+            out.append((l, k, v))
+        n = self._stream_container(doc_id, scheme, head_shape, verify, consume)
+        return out, n
 
     def build_dynamic_cache(self, doc_id: str, num_layers: int, scheme: Scheme,
                             head_shape: tuple[int, int] = (2, 64)):
