@@ -32,6 +32,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import os
 import struct
 import time
 import zlib
@@ -57,6 +58,8 @@ _DOC_MAGIC = b"TQCAGDOC"
 _DOC_VERSION = 1
 _DOC_FIXED = struct.Struct("<8sIIIIQIIIIQQ")
 _DOC_ALIGN = 4096
+_READ_RING = 8      # pinned staging buffers a container load keeps in flight
+_READ_THREADS = 4   # reader threads (file reads release the interpreter lock)
 _SCHEME_IDS = {"turbo_prod": 0, "turbo_mse": 1}
 
 
@@ -70,7 +73,8 @@ class CAGStore:
         self.store_dir.mkdir(parents=True, exist_ok=True)
         self.tq = TurboQuantWrapper(lib_path)
         self._manifest_path = self.store_dir / _MANIFEST
-        self._pinned: list[torch.Tensor | None] = [None, None]  # two staging buffers, used in turn
+        self._pinned: list[torch.Tensor | None] = [None, None]  # staging buffers, used in turn
+        self._readers = None
         self._copy_stream: torch.cuda.Stream | None = None
 
     # ---- names and manifest -------------------------------------------------------------------
@@ -196,7 +200,15 @@ class CAGStore:
         return pool_p.stat().st_size
 
     # ---- online: load -------------------------------------------------------------------------
+    def _reader_pool(self):
+        if self._readers is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._readers = ThreadPoolExecutor(max_workers=_READ_THREADS, thread_name_prefix="cagstore-read")
+        return self._readers
+
     def _staging(self, which: int, nbytes: int) -> torch.Tensor:
+        while len(self._pinned) <= which:
+            self._pinned.append(None)
         buf = self._pinned[which]
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, pin_memory=True)
@@ -393,9 +405,10 @@ class CAGStore:
                 "header_bytes": header_bytes, "layers": [p[0] for p in pairs], "crc32": [p[1] for p in pairs]}
 
     def _stream_container(self, doc_id: str, scheme: Scheme, head_shape, verify: bool, consume) -> int:
-        """Read a container front to back: layer i goes file -> pinned buffer (i & 1) -> device on
-        the copy stream while ``consume(layer, pool, copied_event, header)`` of layer i - 1 is
-        still running.  Returns the document length."""
+        """Read a container front to back: a few reader threads fill a ring of pinned buffers with
+        the next layers (positional reads) while layer i goes pinned buffer -> device on the copy
+        stream and ``consume(layer, pool, copied_event, header)`` runs.  Returns the document
+        length."""
         path = self.container_path(doc_id, scheme)
         if not path.exists():
             raise FileNotFoundError(f"No container: doc={doc_id} scheme={scheme}")
@@ -414,28 +427,52 @@ class CAGStore:
                 raise RuntimeError(f"container pages ({hd['block_size']} tokens, {hd['page_size_bytes']} bytes, "
                                    f"{hd['layer_bytes']} per layer) do not match this build "
                                    f"({cfg.block_size}, {page}, {want})")
-            nbytes = hd["layer_bytes"]
-            in_flight: list[torch.cuda.Event | None] = [None, None]
-            for i, l in enumerate(hd["layers"]):
-                if in_flight[i & 1] is not None:
-                    in_flight[i & 1].synchronize()  # the staging buffer is free again
-                host = self._staging(i & 1, nbytes)
-                f.seek(hd["header_bytes"] + i * hd["layer_stride"])
-                view = memoryview(host.numpy())[:nbytes]
-                if f.readinto(view) != nbytes:
-                    raise RuntimeError(f"{path}: truncated at layer {l}")
+            nbytes, fd = hd["layer_bytes"], f.fileno()
+            ring = min(_READ_RING, len(hd["layers"]))
+            hosts = [self._staging(j, nbytes) for j in range(ring)]
+
+            def read_layer(i: int) -> None:
+                # positional reads: the reader threads share the descriptor
+                view = memoryview(hosts[i % ring].numpy())[:nbytes]
+                off, got = hd["header_bytes"] + i * hd["layer_stride"], 0
+                while got < nbytes:
+                    k = os.preadv(fd, [view[got:]], off + got)
+                    if k <= 0:
+                        raise RuntimeError(f"{path}: truncated at layer {hd['layers'][i]}")
+                    got += k
                 if verify and zlib.crc32(view) != hd["crc32"][i]:
-                    raise RuntimeError(f"{path}: checksum mismatch in layer {l}")
-                pool = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-                done = torch.cuda.Event()
-                with torch.cuda.stream(self._copy_stream):
-                    pool.copy_(host[:nbytes], non_blocking=True)
-                    done.record()
-                in_flight[i & 1] = done
-                consume(l, pool, done, hd)
-            for ev in in_flight:
-                if ev is not None:
-                    ev.synchronize()
+                    raise RuntimeError(f"{path}: checksum mismatch in layer {hd['layers'][i]}")
+
+            readers = self._reader_pool()
+            reads = {i: readers.submit(read_layer, i) for i in range(ring)}
+            copied: list[torch.cuda.Event | None] = [None] * ring
+            try:
+                for i, l in enumerate(hd["layers"]):
+                    reads.pop(i).result()
+                    pool = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                    done = torch.cuda.Event()
+                    with torch.cuda.stream(self._copy_stream):
+                        pool.copy_(hosts[i % ring][:nbytes], non_blocking=True)
+                        done.record()
+                    copied[i % ring] = done
+                    # the buffer of the previous layer is free once its copy has finished: hand it to
+                    # the reader of the layer one ring ahead of it
+                    if i >= 1 and i - 1 + ring < len(hd["layers"]):
+                        copied[(i - 1) % ring].synchronize()
+                        reads[i - 1 + ring] = readers.submit(read_layer, i - 1 + ring)
+                    consume(l, pool, done, hd)
+            finally:
+                for fut in reads.values():
+                    fut.cancel()
+                for fut in reads.values():
+                    if not fut.cancelled():
+                        try:
+                            fut.result()
+                        except Exception:
+                            pass
+                for ev in copied:
+                    if ev is not None:
+                        ev.synchronize()
         return hd["num_tokens"]
 
     def load_container_pools(self, doc_id: str, scheme: Scheme, head_shape: tuple[int, int] | None = None,
