@@ -68,6 +68,19 @@ typedef struct TQTurbomsePageLayout {
     size_t page_size_bytes;
 } TQTurbomsePageLayout;
 
+/* include/tq_qjl.cuh:22-35 (48 bytes).  The QJL-1bit scheme is compiled into the reference
+ * library but not exported through its C API; the entry points below give it one. */
+typedef struct TQQJLPageLayout {
+    size_t page_size_bytes;
+    size_t k1_codes_offset; /* 1 sign bit per dimension */
+    size_t k_scales_offset; /* fp16 RMS per token-head */
+    size_t v4_codes_offset; /* 4-bit codes, the turbo_prod V codebook */
+    size_t v_scales_offset;
+    int k1_bytes_per_token_head;
+    int v4_bytes_per_token_head;
+    int scale_bytes_per_token_head;
+} TQQJLPageLayout;
+
 /* ------------------------------------------------------------------------ */
 /* Part 1 — the reference surface                                           */
 /* ------------------------------------------------------------------------ */
@@ -127,6 +140,25 @@ int tq_launch_turbo_mse_fused_attention_output(const tq_half* query, const uint8
 
 #define TQ_SCHEME_TURBO_PROD 0
 #define TQ_SCHEME_TURBO_MSE 1
+#define TQ_SCHEME_QJL 2 /* layout argument: TQQJLPageLayout*; logits are <q', k'> without 1/sqrt(head_dim) */
+
+/* QJL-1bit: K = sign bit per rotated dimension + fp16 RMS (18 bytes per token-head at head_dim
+ * 128), V = 4-bit codes + fp16 RMS (66 bytes); the rotation's sign pattern has no per-head
+ * term and the attention logits are not scaled by 1/sqrt(head_dim).  Same argument meaning as
+ * the turbo_prod entry points.
+ * src/tq_qjl.cpp:7-34 (layout), src/cuda/tq_qjl_kernels.cu:69-170 (pack), :172-244 (dequant),
+ * :256-373 (fused attention), launchers :380-438. */
+int tq_make_qjl_layout(const TQConfig* cfg, TQQJLPageLayout* out_layout);
+int tq_launch_qjl_pack_kv(const tq_half* key, const tq_half* value, const int32_t* slot_mapping,
+                          uint8_t* page_pool, const TQQJLPageLayout* layout, const TQConfig* cfg,
+                          int num_tokens, tq_stream_t stream);
+int tq_launch_qjl_dequant_kv(const uint8_t* page_pool, const int32_t* slot_mapping, tq_half* out_key,
+                             tq_half* out_value, const TQQJLPageLayout* layout, const TQConfig* cfg,
+                             int num_tokens, tq_stream_t stream);
+int tq_launch_qjl_fused_attention_output(const tq_half* query, const uint8_t* page_pool,
+                                         const int32_t* slot_mapping, tq_half* output,
+                                         const TQQJLPageLayout* layout, const TQConfig* cfg,
+                                         int num_queries, int num_kv_tokens, tq_stream_t stream);
 
 /* Floats per (sequence, query head) in a split-KV partial: the rotated-domain
  * unnormalised accumulator acc[128], then the running maximum m (natural-log

@@ -105,8 +105,28 @@ def mse_layout(cfg: Config) -> MseLayout:
     return out
 
 
+class QjlLayout(C.Structure):
+    """include/tq_qjl.cuh:22-35"""
+    _fields_ = [(n, C.c_size_t) for n in ("page_size_bytes", "k1_codes_offset", "k_scales_offset",
+                                          "v4_codes_offset", "v_scales_offset")] + \
+               [(n, C.c_int) for n in ("k1_bytes_per_token_head", "v4_bytes_per_token_head",
+                                       "scale_bytes_per_token_head")]
+
+
+def qjl_layout(cfg: Config) -> QjlLayout:
+    out = QjlLayout()
+    lib().orc_qjl_layout(C.byref(cfg), C.byref(out))
+    return out
+
+
 def layout_for(scheme: str, cfg: Config):
+    if scheme == "qjl":
+        return qjl_layout(cfg)
     return prod_layout(cfg) if scheme == "turbo_prod" else mse_layout(cfg)
+
+
+def _fn(scheme: str, op: str):
+    return getattr(lib(), {"turbo_prod": "orc_prod_", "turbo_mse": "orc_mse_", "qjl": "orc_qjl_"}[scheme] + op)
 
 
 def cb3() -> np.ndarray:
@@ -145,7 +165,7 @@ def pack(scheme: str, key, value, slots, cfg: Config, pool: np.ndarray | None = 
         pool = np.zeros(num_pages(slots, cfg.block_size) * lay.page_size_bytes, np.uint8)
     kn = np.zeros(k.shape, np.float32) if trace else None
     vn = np.zeros(k.shape, np.float32) if trace else None
-    fn = lib().orc_prod_pack if scheme == "turbo_prod" else lib().orc_mse_pack
+    fn = _fn(scheme, "pack")
     fn(_p(k), _p(v), _p(slots), _p(pool), C.byref(lay), C.byref(cfg), C.c_int(n),
        _p(kn), _p(vn))
     return (pool, kn, vn) if trace else pool
@@ -157,7 +177,7 @@ def dequant(scheme: str, pool, slots, cfg: Config):
     lay = layout_for(scheme, cfg)
     shape = (n, cfg.num_kv_heads, cfg.head_dim)
     ok, ov = np.zeros(shape, np.uint16), np.zeros(shape, np.uint16)
-    fn = lib().orc_prod_dequant if scheme == "turbo_prod" else lib().orc_mse_dequant
+    fn = _fn(scheme, "dequant")
     fn(_p(pool), _p(slots), _p(ok), _p(ov), C.byref(lay), C.byref(cfg), C.c_int(n))
     return ok.view(np.float16), ov.view(np.float16)
 
@@ -180,7 +200,7 @@ def attn(scheme: str, query, pool, slots, cfg: Config):
     nq, nkv = q.shape[0], slots.shape[0]
     lay = layout_for(scheme, cfg)
     out = np.zeros(q.shape, np.uint16)
-    fn = lib().orc_prod_attn if scheme == "turbo_prod" else lib().orc_mse_attn
+    fn = _fn(scheme, "attn")
     fn(_p(q), _p(pool), _p(slots), _p(out), C.byref(lay), C.byref(cfg),
        C.c_int(nq), C.c_int(nkv))
     return out.view(np.float16)
@@ -193,7 +213,7 @@ def attn_state(scheme: str, query, pool, slots, cfg: Config):
     nq, nkv = q.shape[0], slots.shape[0]
     lay = layout_for(scheme, cfg)
     out = np.zeros((nq, cfg.num_kv_heads, cfg.head_dim + 2), np.float32)
-    fn = lib().orc_prod_attn_f32 if scheme == "turbo_prod" else lib().orc_mse_attn_f32
+    fn = _fn(scheme, "attn_f32")
     fn(_p(q), _p(pool), _p(slots), _p(out), C.byref(lay), C.byref(cfg),
        C.c_int(nq), C.c_int(nkv))
     return out

@@ -694,3 +694,165 @@ void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
         free(vr);
     }
 }
+
+/* ------------------------------------------------------------------------- */
+/* QJL-1bit (compiled into the reference library, not exported by its C API) */
+/* ------------------------------------------------------------------------- */
+
+/* src/tq_qjl.cpp:7-34 */
+void orc_qjl_layout(const OrcConfig* c, OrcQjlLayout* l) {
+    memset(l, 0, sizeof *l);
+    l->k1_bytes_per_token_head = (c->head_dim + 7) / 8;
+    l->v4_bytes_per_token_head = (c->head_dim * 4 + 7) / 8;
+    l->scale_bytes_per_token_head = 2;
+    size_t cells = (size_t)c->block_size * c->num_kv_heads, at = 0;
+    l->k1_codes_offset = at;
+    at = up(at + cells * l->k1_bytes_per_token_head, 2);
+    l->k_scales_offset = at;
+    at += cells * 2;
+    l->v4_codes_offset = at;
+    at = up(at + cells * l->v4_bytes_per_token_head, 2);
+    l->v_scales_offset = at;
+    at += cells * 2;
+    l->page_size_bytes = up(at, 2);
+}
+
+typedef struct {
+    uint8_t* k1;
+    uint16_t* ks;
+    uint8_t* v4;
+    uint16_t* vs;
+} QjlCell;
+
+/* tq_qjl_kernels.cu:92-111 and tq_qjl.cuh:40-47 */
+static QjlCell qjl_cell(const uint8_t* pool, const OrcQjlLayout* l,
+                        const OrcConfig* c, int slot, int head) {
+    int blk = slot / c->block_size, tib = slot % c->block_size;
+    uint8_t* page = (uint8_t*)pool + (size_t)blk * l->page_size_bytes;
+    size_t th = (size_t)tib * c->num_kv_heads + head;
+    QjlCell p;
+    p.k1 = page + l->k1_codes_offset + th * l->k1_bytes_per_token_head;
+    p.ks = (uint16_t*)(page + l->k_scales_offset + th * l->scale_bytes_per_token_head);
+    p.v4 = page + l->v4_codes_offset + th * l->v4_bytes_per_token_head;
+    p.vs = (uint16_t*)(page + l->v_scales_offset + th * l->scale_bytes_per_token_head);
+    return p;
+}
+
+/* tq_qjl_kernels.cu:124-169.  The sign hash (:18-21) is the turbo_prod hash with
+ * head 0: the rotation does not depend on the kv head. */
+void orc_qjl_pack(const uint16_t* key, const uint16_t* value,
+                  const int32_t* slots, uint8_t* pool, const OrcQjlLayout* lay,
+                  const OrcConfig* cfg, int n, float* dbg_kn, float* dbg_vn) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t) {
+        for (int h = 0; h < H; ++h) {
+            float sk[128], sv[128], red[128];
+            int vidx[128];
+            size_t base = ((size_t)t * H + h) * d;
+            QjlCell p = qjl_cell(pool, lay, cfg, slots[t], h);
+            rotate_fwd(key + base, 0, d, sk);
+            rotate_fwd(value + base, 0, d, sv);
+            for (int i = 0; i < d; ++i) red[i] = sk[i] * sk[i];
+            float krms = sqrtf(tree_sum(red, d) / (float)d);
+            if (krms < 1e-8f) krms = 1e-8f;
+            *p.ks = f2h(krms);
+            for (int i = 0; i < d; ++i) red[i] = sv[i] * sv[i];
+            float vrms = sqrtf(tree_sum(red, d) / (float)d);
+            if (vrms < 1e-8f) vrms = 1e-8f;
+            *p.vs = f2h(vrms);
+            for (int j = 0; j < lay->k1_bytes_per_token_head; ++j) p.k1[j] = 0;
+            for (int i = 0; i < d; ++i) {
+                float kn = sk[i] / krms;
+                float vn = clampf(sv[i] / vrms, -2.75f, 2.75f);
+                if (kn >= 0.0f) p.k1[i >> 3] |= (uint8_t)(1u << (i & 7)); /* tq_shared_device.cuh:23-32 */
+                vidx[i] = orc_nearest_v4(vn);
+                if (dbg_kn) dbg_kn[base + i] = kn;
+                if (dbg_vn) dbg_vn[base + i] = vn;
+            }
+            for (int j = 0; j < d / 2; ++j)
+                p.v4[j] = (uint8_t)((vidx[2 * j + 1] << 4) | vidx[2 * j]);
+        }
+    }
+}
+
+/* tq_qjl_kernels.cu:231-236 */
+static void qjl_decode_rot(const QjlCell* p, int d, float* k, float* v) {
+    float ks = h2f(*p->ks), vs = h2f(*p->vs);
+    for (int i = 0; i < d; ++i) {
+        k[i] = ((p->k1[i >> 3] >> (i & 7)) & 1 ? 1.0f : -1.0f) * ks;
+        v[i] = kCb4[nib_get(p->v4, i)] * vs;
+    }
+}
+
+/* tq_qjl_kernels.cu:196-243 */
+void orc_qjl_dequant(const uint8_t* pool, const int32_t* slots,
+                     uint16_t* out_key, uint16_t* out_value,
+                     const OrcQjlLayout* lay, const OrcConfig* cfg, int n) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for schedule(static) num_threads(nthreads())
+    for (int t = 0; t < n; ++t)
+        for (int h = 0; h < H; ++h) {
+            float k[128], v[128];
+            QjlCell p = qjl_cell(pool, lay, cfg, slots[t], h);
+            qjl_decode_rot(&p, d, k, v);
+            size_t base = ((size_t)t * H + h) * d;
+            rotate_inv_store(k, 0, d, out_key + base);
+            rotate_inv_store(v, 0, d, out_value + base);
+        }
+}
+
+/* tq_qjl_kernels.cu:287-357 -- token-serial online softmax; logit = tree sum of
+ * q'[i] * (+-ks), not scaled by 1/sqrt(D) (:335). */
+static void qjl_attn_state(const uint16_t* q, const uint8_t* pool,
+                           const int32_t* slots, const OrcQjlLayout* lay,
+                           const OrcConfig* cfg, int h, int nkv, float* state) {
+    const int d = cfg->head_dim;
+    float qrot[128], acc[128], red[128];
+    rotate_fwd(q, 0, d, qrot);
+    for (int i = 0; i < d; ++i) acc[i] = 0.0f;
+    float m = -1e30f, l = 0.0f;
+    for (int t = 0; t < nkv; ++t) {
+        QjlCell p = qjl_cell(pool, lay, cfg, slots[t], h);
+        float ks = h2f(*p.ks), vs = h2f(*p.vs);
+        for (int i = 0; i < d; ++i)
+            red[i] = qrot[i] * (((p.k1[i >> 3] >> (i & 7)) & 1 ? 1.0f : -1.0f) * ks);
+        float logit = tree_sum(red, d);
+        float m_new = fmaxf(m, logit);
+        float a = expf(m - m_new), b = expf(logit - m_new);
+        l = fmaf(l, a, b);
+        m = m_new;
+        for (int i = 0; i < d; ++i)
+            acc[i] = fmaf(b, kCb4[nib_get(p.v4, i)] * vs, acc[i] * a);
+    }
+    memcpy(state, acc, sizeof(float) * d);
+    state[d] = m;
+    state[d + 1] = l;
+}
+
+void orc_qjl_attn_f32(const uint16_t* query, const uint8_t* pool,
+                      const int32_t* slots, float* out_f32,
+                      const OrcQjlLayout* lay, const OrcConfig* cfg, int nq,
+                      int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            size_t r = (size_t)qi * H + h;
+            qjl_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv, out_f32 + r * (d + 2));
+        }
+}
+
+void orc_qjl_attn(const uint16_t* query, const uint8_t* pool,
+                  const int32_t* slots, uint16_t* out, const OrcQjlLayout* lay,
+                  const OrcConfig* cfg, int nq, int nkv) {
+    const int d = cfg->head_dim, H = cfg->num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
+    for (int qi = 0; qi < nq; ++qi)
+        for (int h = 0; h < H; ++h) {
+            float st[130];
+            size_t r = (size_t)qi * H + h;
+            qjl_attn_state(query + r * d, pool, slots, lay, cfg, h, nkv, st);
+            attn_finish(st, 0, d, out + r * d);
+        }
+}

@@ -41,7 +41,16 @@ typedef struct {
         v_codes_offset, k_norms_offset, v_norms_offset, page_size_bytes;
 } OrcMseLayout;
 
+/* include/tq_qjl.cuh:22-35 */
+typedef struct {
+    size_t page_size_bytes, k1_codes_offset, k_scales_offset, v4_codes_offset,
+        v_scales_offset;
+    int k1_bytes_per_token_head, v4_bytes_per_token_head,
+        scale_bytes_per_token_head;
+} OrcQjlLayout;
+
 void orc_default_config(OrcConfig* cfg);
+void orc_qjl_layout(const OrcConfig* cfg, OrcQjlLayout* out);
 void orc_prod_layout(const OrcConfig* cfg, OrcProdLayout* out);
 void orc_mse_layout(const OrcConfig* cfg, OrcMseLayout* out);
 
@@ -124,6 +133,22 @@ void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
 /* src/tq_block_table.cpp:24-39 — slot = physical_block*block_size + t. */
 void orc_build_slot_map(const int32_t* blocks, int num_tokens_before,
                         int append_tokens, int block_size, int32_t* slots);
+
+/* QJL-1bit (src/cuda/tq_qjl_kernels.cu): pack :69-170, dequant :172-244, fused
+ * attention :256-373 (logits <q', k'> without 1/sqrt(D)). */
+void orc_qjl_pack(const uint16_t* key, const uint16_t* value,
+                  const int32_t* slots, uint8_t* pool, const OrcQjlLayout* lay,
+                  const OrcConfig* cfg, int n, float* dbg_kn, float* dbg_vn);
+void orc_qjl_dequant(const uint8_t* pool, const int32_t* slots,
+                     uint16_t* out_key, uint16_t* out_value,
+                     const OrcQjlLayout* lay, const OrcConfig* cfg, int n);
+void orc_qjl_attn(const uint16_t* query, const uint8_t* pool,
+                  const int32_t* slots, uint16_t* out, const OrcQjlLayout* lay,
+                  const OrcConfig* cfg, int nq, int nkv);
+void orc_qjl_attn_f32(const uint16_t* query, const uint8_t* pool,
+                      const int32_t* slots, float* out_f32,
+                      const OrcQjlLayout* lay, const OrcConfig* cfg, int nq,
+                      int nkv);
 
 #ifdef __cplusplus
 }

@@ -3,7 +3,8 @@
 Needs a CUDA GPU and ``oracle/_ref/libturboquant_ref.so`` (the unmodified
 reference sources compiled for sm_100 by ``make -C oracle ref``).  Run once:
 
-    python tests/golden/make_golden.py [out_dir]
+    python tests/golden/make_golden.py [out_dir]          # turbo_prod / turbo_mse: <case>.npz
+    python tests/golden/make_golden.py --qjl [out_dir]    # QJL-1bit: qjl_<case>.npz
 
 For every case it draws seeded inputs with numpy, runs the reference's
 pack / dequant / logits / fused-attention entry points through its C API
@@ -49,7 +50,52 @@ def sha(a: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
+class Qjl(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in ("page_size_bytes", "k1", "ks", "v4", "vs")] + \
+               [(n, C.c_int) for n in ("kb", "vb", "sb")]
+
+
+def main_qjl(out_dir: Path) -> None:
+    """QJL-1bit: the reference compiles the kernels (src/cuda/tq_qjl_kernels.cu) but does not
+    export them; oracle/ref_qjl_shim.cu, built into the same library, forwards to its launchers."""
+    out_dir.mkdir(parents=True, exist_ok=True)
+    lib = C.CDLL(str(ROOT / "oracle" / "_ref" / "libturboquant_ref.so"))
+    dev = torch.device("cuda:0")
+    for case in CASES:
+        name, n, h, nq = case["name"], case["n"], case["h"], case["nq"]
+        key, value, query, slots = make_inputs(case)
+        cfg, lay = Cfg(), Qjl()
+        lib.tq_make_default_config(C.byref(cfg))
+        cfg.num_kv_heads, cfg.head_dim = h, 128
+        assert lib.tq_make_qjl_layout(C.byref(cfg), C.byref(lay)) == 0
+        npages = int(slots.max()) // 16 + 1
+        dk = torch.from_numpy(key.view(np.int16)).to(dev)
+        dv = torch.from_numpy(value.view(np.int16)).to(dev)
+        dq = torch.from_numpy(query.view(np.int16)).to(dev)
+        ds = torch.from_numpy(slots).to(dev)
+        pool = torch.zeros(npages * lay.page_size_bytes, dtype=torch.uint8, device=dev)
+        ok = torch.zeros(n, h, 128, dtype=torch.int16, device=dev)
+        ov = torch.zeros_like(ok)
+        oa = torch.zeros(nq, h, 128, dtype=torch.int16, device=dev)
+        assert lib.tq_launch_qjl_pack_kv(p(dk), p(dv), p(ds), p(pool), C.byref(lay), C.byref(cfg), n, None) == 0
+        assert lib.tq_launch_qjl_dequant_kv(p(pool), p(ds), p(ok), p(ov), C.byref(lay), C.byref(cfg), n, None) == 0
+        assert lib.tq_launch_qjl_fused_attention_output(p(dq), p(pool), p(ds), p(oa), C.byref(lay), C.byref(cfg),
+                                                        nq, n, None) == 0
+        torch.cuda.synchronize()
+        k_np, v_np = ok.cpu().numpy().view(np.uint16), ov.cpu().numpy().view(np.uint16)
+        keep = n if case.get("store_inputs") else min(n, 48)
+        out = {"key_sha": sha(key), "value_sha": sha(value), "query_sha": sha(query), "slots": slots,
+               "page_size_bytes": np.array([lay.page_size_bytes]), "qjl_pool": pool.cpu().numpy(),
+               "qjl_dequant_sha": np.array([sha(k_np), sha(v_np)]),
+               "qjl_dequant_key_head": k_np[:keep], "qjl_dequant_value_head": v_np[:keep],
+               "qjl_attn": oa.cpu().numpy().view(np.uint16)}
+        np.savez_compressed(out_dir / f"qjl_{name}.npz", **out)
+        print("wrote", f"qjl_{name}", {k: getattr(v, "shape", None) for k, v in out.items()})
+
+
 def main() -> None:
+    if len(sys.argv) > 1 and sys.argv[1] == "--qjl":
+        return main_qjl(Path(sys.argv[2]) if len(sys.argv) > 2 else HERE)
     out_dir = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE
     out_dir.mkdir(parents=True, exist_ok=True)
     lib = C.CDLL(str(ROOT / "oracle" / "_ref" / "libturboquant_ref.so"))

@@ -21,7 +21,8 @@ OURS = ROOT / "turborag_b200" / "lib" / "libturboquant.so"
 pytestmark = pytest.mark.gpu
 
 
-from turborag_b200.wrapper import TQConfig, TQTurboProdPageLayout, TQTurbomsePageLayout  # noqa: E402
+from turborag_b200.wrapper import (TQConfig, TQQJLPageLayout, TQTurboProdPageLayout,  # noqa: E402
+                                   TQTurbomsePageLayout)
 
 
 def _p(t):
@@ -41,7 +42,7 @@ def _time(fn, iters=5, warmup=2):
     return e0.elapsed_time(e1) / iters * 1e3  # us
 
 
-@pytest.mark.parametrize("scheme", ["prod", "mse"])
+@pytest.mark.parametrize("scheme", ["prod", "mse", "qjl"])
 @pytest.mark.parametrize("n,nq", [(1143, 8), (32768, 8)])
 def test_against_reference_kernels(n, nq, scheme):
     if not REF.exists():
@@ -68,26 +69,32 @@ def test_against_reference_kernels(n, nq, scheme):
         cfg = TQConfig()
         lib.tq_make_default_config(C.byref(cfg))
         cfg.num_kv_heads, cfg.head_dim = h, 128
-        lay_s = TQTurboProdPageLayout() if scheme == "prod" else TQTurbomsePageLayout()
-        getattr(lib, f"tq_make_turbo_{scheme}_layout")(C.byref(cfg), C.byref(lay_s))
+        # QJL: the reference compiles the kernels without exporting them; its library here carries
+        # oracle/ref_qjl_shim.cu, which forwards the same symbol names to the reference's launchers
+        prefix = "tq_launch_qjl" if scheme == "qjl" else f"tq_launch_turbo_{scheme}"
+        lay_s = {"prod": TQTurboProdPageLayout, "mse": TQTurbomsePageLayout, "qjl": TQQJLPageLayout}[scheme]()
+        make = "tq_make_qjl_layout" if scheme == "qjl" else f"tq_make_turbo_{scheme}_layout"
+        if not hasattr(lib, make):
+            pytest.skip("reference library was built without the QJL entry points (make -C oracle ref)")
+        getattr(lib, make)(C.byref(cfg), C.byref(lay_s))
         lay = C.byref(lay_s)
         page_bytes = lay_s.page_size_bytes
-        assert page_bytes == (4288 if scheme == "prod" else 4608)
+        assert page_bytes == {"prod": 4288, "mse": 4608, "qjl": 2688}[scheme]
         pool = torch.zeros(pages * page_bytes, dtype=torch.uint8, device=dev)
         ok = torch.zeros(n, h, 128, dtype=torch.float16, device=dev)
         ov = torch.zeros_like(ok)
         oa = torch.zeros(nq, h, 128, dtype=torch.float16, device=dev)
 
         def pack():
-            assert getattr(lib, f"tq_launch_turbo_{scheme}_pack_kv")(_p(key), _p(value), _p(slots), _p(pool), lay,
+            assert getattr(lib, f"{prefix}_pack_kv")(_p(key), _p(value), _p(slots), _p(pool), lay,
                                                     C.byref(cfg), n, None) == 0, lib.tq_last_error()
 
         def dequant():
-            assert getattr(lib, f"tq_launch_turbo_{scheme}_dequant_kv")(_p(pool), _p(slots), _p(ok), _p(ov), lay,
+            assert getattr(lib, f"{prefix}_dequant_kv")(_p(pool), _p(slots), _p(ok), _p(ov), lay,
                                                        C.byref(cfg), n, None) == 0, lib.tq_last_error()
 
         def attend():
-            assert getattr(lib, f"tq_launch_turbo_{scheme}_fused_attention_output")(
+            assert getattr(lib, f"{prefix}_fused_attention_output")(
                 _p(query), _p(pool), _p(slots), _p(oa), lay, C.byref(cfg), nq, n, None) == 0, lib.tq_last_error()
 
         times[name] = (_time(pack), _time(dequant), _time(attend))
@@ -100,7 +107,7 @@ def test_against_reference_kernels(n, nq, scheme):
     err = np.abs(r[3] - o[3]).max(axis=-1) / np.maximum(np.abs(r[3]).max(axis=-1), 1e-6)
     assert err.max() < 2e-3, f"attention differs from the reference kernels: {err.max():.3e}"
     tr, to = times["reference"], times["ours"]
-    print(f"\nturbo_{scheme} n={n} nq={nq} H={h}  (us: pack, dequant, fused attention)\n"
+    print(f"\n{scheme} n={n} nq={nq} H={h}  (us: pack, dequant, fused attention)\n"
           f"  reference kernels: {tr[0]:9.1f} {tr[1]:9.1f} {tr[2]:9.1f}\n"
           f"  this library:      {to[0]:9.1f} {to[1]:9.1f} {to[2]:9.1f}\n"
           f"  ratio:             {tr[0] / to[0]:9.1f} {tr[1] / to[1]:9.1f} {tr[2] / to[2]:9.1f}   "

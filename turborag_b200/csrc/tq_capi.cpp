@@ -120,7 +120,24 @@ tq::PageGeom geom_mse(const TQTurbomsePageLayout& l, const TQConfig& cfg) {
     return g;
 }
 
+tq::PageGeom geom_qjl(const TQQJLPageLayout& l, const TQConfig& cfg) {
+    if (l.k1_bytes_per_token_head != 16 || l.v4_bytes_per_token_head != 64 ||
+        l.scale_bytes_per_token_head != 2)
+        throw std::runtime_error("qjl: layout does not match head_dim 128");
+    tq::PageGeom g{};
+    g.page_size = l.page_size_bytes;
+    g.k_codes = static_cast<unsigned>(l.k1_codes_offset);
+    g.v_codes = static_cast<unsigned>(l.v4_codes_offset);
+    g.k_scales = static_cast<unsigned>(l.k_scales_offset);
+    g.v_scales = static_cast<unsigned>(l.v_scales_offset);
+    g.k_res = 0;
+    g.block_size = cfg.block_size;
+    g.num_kv_heads = cfg.num_kv_heads;
+    return g;
+}
+
 tq::PageGeom geom_for(int scheme, const void* layout, const TQConfig& cfg) {
+    if (scheme == TQ_SCHEME_QJL) return geom_qjl(*static_cast<const TQQJLPageLayout*>(layout), cfg);
     if (scheme == TQ_SCHEME_TURBO_PROD)
         return geom_prod(*static_cast<const TQTurboProdPageLayout*>(layout), cfg);
     if (scheme == TQ_SCHEME_TURBO_MSE)
@@ -224,7 +241,7 @@ extern "C" int tq_launch_turbo_prod_pack_kv(const tq_half* key, const tq_half* v
         check_shape(*cfg, "turbo_prod");
         check_align(key, 16, "key");
         check_align(value, 16, "value");
-        tq::launch_pack(true, key, value, slot_mapping, page_pool, geom_prod(*layout, *cfg),
+        tq::launch_pack(TQ_SCHEME_TURBO_PROD, key, value, slot_mapping, page_pool, geom_prod(*layout, *cfg),
                         cfg->head_dim, num_tokens, static_cast<cudaStream_t>(stream));
     });
 }
@@ -239,7 +256,7 @@ extern "C" int tq_launch_turbo_prod_dequant_kv(const uint8_t* page_pool, const i
         check_shape(*cfg, "turbo_prod");
         check_align(out_key, 4, "out_key");
         check_align(out_value, 4, "out_value");
-        tq::launch_dequant(true, page_pool, slot_mapping, out_key, out_value,
+        tq::launch_dequant(TQ_SCHEME_TURBO_PROD, page_pool, slot_mapping, out_key, out_value,
                            geom_prod(*layout, *cfg), cfg->head_dim, num_tokens, false,
                            static_cast<cudaStream_t>(stream));
     });
@@ -280,7 +297,7 @@ extern "C" int tq_launch_turbo_mse_pack_kv(const tq_half* key, const tq_half* va
         check_shape(*cfg, "turbo_mse pack");
         check_align(key, 16, "key");
         check_align(value, 16, "value");
-        tq::launch_pack(false, key, value, slot_mapping, page_pool, geom_mse(*layout, *cfg),
+        tq::launch_pack(TQ_SCHEME_TURBO_MSE, key, value, slot_mapping, page_pool, geom_mse(*layout, *cfg),
                         cfg->head_dim, num_tokens, static_cast<cudaStream_t>(stream));
     });
 }
@@ -294,7 +311,7 @@ extern "C" int tq_launch_turbo_mse_dequant_kv(const uint8_t* page_pool, const in
         check_shape(*cfg, "turbo_mse dequant");
         check_align(out_key, 4, "out_key");
         check_align(out_value, 4, "out_value");
-        tq::launch_dequant(false, page_pool, slot_mapping, out_key, out_value,
+        tq::launch_dequant(TQ_SCHEME_TURBO_MSE, page_pool, slot_mapping, out_key, out_value,
                            geom_mse(*layout, *cfg), cfg->head_dim, num_tokens, false,
                            static_cast<cudaStream_t>(stream));
     });
@@ -310,6 +327,67 @@ extern "C" int tq_launch_turbo_mse_fused_attention_output(
         ref_attention(TQ_SCHEME_TURBO_MSE, query, page_pool, slot_mapping, output, nullptr,
                       geom_mse(*layout, *cfg), *cfg, num_queries, num_kv_tokens,
                       static_cast<cudaStream_t>(stream));
+    });
+}
+
+// ---- QJL-1bit (compiled but unexported in the reference: src/cuda/tq_qjl_kernels.cu) -------
+
+extern "C" int tq_make_qjl_layout(const TQConfig* cfg, TQQJLPageLayout* out) {
+    if (!cfg || !out) return -1;
+    TQQJLPageLayout l{};
+    l.k1_bytes_per_token_head = (cfg->head_dim + 7) / 8;
+    l.v4_bytes_per_token_head = (cfg->head_dim * 4 + 7) / 8;
+    l.scale_bytes_per_token_head = 2;
+    const size_t cells = static_cast<size_t>(cfg->block_size) * cfg->num_kv_heads;
+    size_t at = 0;
+    l.k1_codes_offset = at;
+    at = align_up(at + cells * l.k1_bytes_per_token_head, 2);
+    l.k_scales_offset = at;
+    at += cells * 2;
+    l.v4_codes_offset = at;
+    at = align_up(at + cells * l.v4_bytes_per_token_head, 2);
+    l.v_scales_offset = at;
+    at += cells * 2;
+    l.page_size_bytes = align_up(at, 2);
+    *out = l;
+    return 0;
+}
+
+extern "C" int tq_launch_qjl_pack_kv(const tq_half* key, const tq_half* value, const int32_t* slot_mapping,
+                                     uint8_t* page_pool, const TQQJLPageLayout* layout, const TQConfig* cfg,
+                                     int num_tokens, tq_stream_t stream) {
+    if (!key || !value || !slot_mapping || !page_pool || !layout || !cfg) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "QJL");
+        check_align(key, 16, "key");
+        check_align(value, 16, "value");
+        tq::launch_pack(TQ_SCHEME_QJL, key, value, slot_mapping, page_pool, geom_qjl(*layout, *cfg),
+                        cfg->head_dim, num_tokens, static_cast<cudaStream_t>(stream));
+    });
+}
+
+extern "C" int tq_launch_qjl_dequant_kv(const uint8_t* page_pool, const int32_t* slot_mapping,
+                                        tq_half* out_key, tq_half* out_value, const TQQJLPageLayout* layout,
+                                        const TQConfig* cfg, int num_tokens, tq_stream_t stream) {
+    if (!page_pool || !slot_mapping || !out_key || !out_value || !layout || !cfg) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "QJL");
+        check_align(out_key, 4, "out_key");
+        check_align(out_value, 4, "out_value");
+        tq::launch_dequant(TQ_SCHEME_QJL, page_pool, slot_mapping, out_key, out_value, geom_qjl(*layout, *cfg),
+                           cfg->head_dim, num_tokens, false, static_cast<cudaStream_t>(stream));
+    });
+}
+
+extern "C" int tq_launch_qjl_fused_attention_output(const tq_half* query, const uint8_t* page_pool,
+                                                    const int32_t* slot_mapping, tq_half* output,
+                                                    const TQQJLPageLayout* layout, const TQConfig* cfg,
+                                                    int num_queries, int num_kv_tokens, tq_stream_t stream) {
+    if (!query || !page_pool || !slot_mapping || !output || !layout || !cfg) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "QJL");
+        ref_attention(TQ_SCHEME_QJL, query, page_pool, slot_mapping, output, nullptr, geom_qjl(*layout, *cfg),
+                      *cfg, num_queries, num_kv_tokens, static_cast<cudaStream_t>(stream));
     });
 }
 
@@ -438,7 +516,7 @@ extern "C" int tq_dequant_kv_hnd(int scheme, const uint8_t* page_pool, const int
         check_shape(*cfg, "dequant_kv_hnd");
         check_align(out_key, 4, "out_key");
         check_align(out_value, 4, "out_value");
-        tq::launch_dequant(scheme == TQ_SCHEME_TURBO_PROD, page_pool, slot_mapping, out_key, out_value,
+        tq::launch_dequant(scheme, page_pool, slot_mapping, out_key, out_value,
                            geom_for(scheme, layout, *cfg), cfg->head_dim, num_tokens, true,
                            static_cast<cudaStream_t>(stream));
     });

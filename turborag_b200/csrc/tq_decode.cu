@@ -240,15 +240,29 @@ struct BlockRaw {
     float ks0, ks1, re0, re1, vs0, vs1;  // scales of token rows g and g+8
 };
 
-template <bool PROD>
+// QJL-1bit rows are 16 bytes of sign bits: the lane's 32 dims are word tig of the row.
+__device__ __forceinline__ uint32_t ld4(const uint8_t* p, bool aligned) {
+    if (aligned) return __ldg(reinterpret_cast<const uint32_t*>(p));
+    uint32_t v = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v |= static_cast<uint32_t>(p[i]) << (8 * i);
+    return v;
+}
+
+template <bool PROD, bool QJL = false>
 __device__ __forceinline__ void load_block(const DecodeParams& p, int b, int h, int tb, int t_end,
                                            int lane, bool aligned, BlockRaw& r) {
     const int g = lane >> 2, tig = lane & 3;
     const int last = t_end - 1;  // rows past the end re-read the last token (masked later)
     const Cell c0 = token_cell(p, token_slot(p, b, min(tb + g, last)), h);
     const Cell c1 = token_cell(p, token_slot(p, b, min(tb + g + 8, last)), h);
-    r.k0 = ld16(c0.page + p.geo.k_codes + c0.th * 64 + 16 * tig, aligned);
-    r.k1 = ld16(c1.page + p.geo.k_codes + c1.th * 64 + 16 * tig, aligned);
+    if (QJL) {
+        r.k0 = make_uint4(ld4(c0.page + p.geo.k_codes + c0.th * 16 + 4 * tig, aligned), 0u, 0u, 0u);
+        r.k1 = make_uint4(ld4(c1.page + p.geo.k_codes + c1.th * 16 + 4 * tig, aligned), 0u, 0u, 0u);
+    } else {
+        r.k0 = ld16(c0.page + p.geo.k_codes + c0.th * 64 + 16 * tig, aligned);
+        r.k1 = ld16(c1.page + p.geo.k_codes + c1.th * 64 + 16 * tig, aligned);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int t = tb + 2 * tig + (i & 1) + 8 * (i >> 1);
@@ -351,7 +365,18 @@ __device__ __forceinline__ void group_sync(int bar_id, int nthreads) {
 
 // One 16-token block for one kv head: QK^T (+ residual-sign product), online softmax, PV.
 // MODE 1 writes logits instead.
-template <bool PROD, int MODE, bool LUT = false>
+// half2(bit I of ~nw ? -1 : +1, bit J ...) from the complemented sign word: a set sign bit is +1.0
+// (tq_qjl_kernels.cu:235, 298), so a set bit of nw = ~w puts the fp16 sign bit on top of 1.0.
+template <int I, int J>
+__device__ __forceinline__ uint32_t sign_half2(uint32_t nw) {
+    uint32_t lo;
+    if constexpr (I <= 15) lo = nw << (15 - I);
+    else lo = nw >> (I - 15);
+    const uint32_t hi = nw << (31 - J);
+    return (lo & 0x8000u) | (hi & 0x80000000u) | 0x3C003C00u;
+}
+
+template <bool PROD, int MODE, bool LUT = false, bool QJL = false>
 __device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
                                               const BlockRaw& cur, int tb, int t_end,
                                               WarpState& st) {
@@ -395,6 +420,19 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
                 mma16816(s1, e00, e10, e01, e11, qf[n][0], qf[n][1]);
             }
         }
+    } else if constexpr (QJL) {
+        // MMA s = 2wi + hf takes dims 8wi + {2hf, 2hf+4 | 2hf+1, 2hf+5} of the lane's 32 (the
+        // pairing of the query fragments): operands are +-1.0 straight from the sign bits
+        const uint32_t n0 = ~kw0[0], n1 = ~kw1[0];
+#define TQ_QJL_STEP(SV)                                                                           \
+    mma16816(s1, sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n0),  \
+             sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n1),      \
+             sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n0),  \
+             sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n1),  \
+             qf[SV][0], qf[SV][1])
+        TQ_QJL_STEP(0); TQ_QJL_STEP(1); TQ_QJL_STEP(2); TQ_QJL_STEP(3);
+        TQ_QJL_STEP(4); TQ_QJL_STEP(5); TQ_QJL_STEP(6); TQ_QJL_STEP(7);
+#undef TQ_QJL_STEP
     } else {
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
@@ -527,7 +565,7 @@ struct CtaRange {
 // split): the whole CTA in the general kernel, one half of the CTA in the paged fast path.
 // `group_smem` is the group's first per-warp region, `qsm` a scratch of H*8*128 halves that is
 // dead once the fragments are built, `warp` the warp's index inside the group.
-template <bool PROD, int MODE, bool LUT = false>
+template <bool PROD, int MODE, bool LUT = false, bool QJL = false>
 __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* group_smem,
                                                 int warp_bytes, __half* qsm, int warp, int seq,
                                                 int split, int bar_id, int bar_threads,
@@ -550,7 +588,9 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     // one warp per (kv head, column); lane holds 4 consecutive elements
     const float c = inv_sqrt_dim(p.head_dim);
     const float alpha_k = PROD ? TQ_ALPHA3 : TQ_ALPHA4;
-    const float qscale = ((MODE == 0) ? c * c * kLog2e : c * c) / alpha_k;
+    // QJL: +-1 operands (no table scale), logits <q', k'> without 1/sqrt(D) (tq_qjl_kernels.cu:335),
+    // rotation sign without a head term (:18-21)
+    const float qscale = QJL ? c * kLog2e : ((MODE == 0) ? c * c * kLog2e : c * c) / alpha_k;
     for (int col = stream; col < 8; col += p.streams) {
         float x[4] = {0.f, 0.f, 0.f, 0.f};
         if (col < nq) {
@@ -571,7 +611,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                     x[e] = (lane & m) ? o - x[e] : x[e] + o;
                 }
             }
-            const float sc = (h & 1) ? -qscale : qscale;
+            const float sc = (!QJL && (h & 1)) ? -qscale : qscale;
 #pragma unroll
             for (int e = 0; e < 4; ++e) x[e] *= sc;
         }
@@ -707,13 +747,13 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int warp_
 
 // General kernel: any slot mapping / block size / alignment; one block of register prefetch.
 // MODE 0: attention partials, MODE 1: logits only (turbo_prod).
-template <bool PROD, int MODE>
+template <bool PROD, int MODE, bool QJL = false>
 __global__ void __launch_bounds__(256, 2)
 decode_kernel(DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     BlockCtx ctx;
     CtaRange r;
-    decode_prologue<PROD, MODE>(p, smem_raw, kWarpSmemBytes,
+    decode_prologue<PROD, MODE, false, QJL>(p, smem_raw, kWarpSmemBytes,
                                 reinterpret_cast<__half*>(smem_raw + (blockDim.x >> 5) * kWarpSmemBytes),
                                 threadIdx.x >> 5, blockIdx.y, blockIdx.x, 0, 0, ctx, r);
     WarpState st;
@@ -723,14 +763,14 @@ decode_kernel(DecodeParams p) {
     BlockRaw cur;
     int blk = r.blk_lo + r.stream;
     if (blk < r.blk_hi)
-        load_block<PROD>(p, r.b, ctx.h, r.t_begin + 16 * blk, r.t_end, ctx.lane, aligned, cur);
+        load_block<PROD, QJL>(p, r.b, ctx.h, r.t_begin + 16 * blk, r.t_end, ctx.lane, aligned, cur);
     for (; blk < r.blk_hi; blk += p.streams) {
         const int tb = r.t_begin + 16 * blk;
         BlockRaw nxt = cur;
         if (blk + p.streams < r.blk_hi)
-            load_block<PROD>(p, r.b, ctx.h, r.t_begin + 16 * (blk + p.streams), r.t_end, ctx.lane,
+            load_block<PROD, QJL>(p, r.b, ctx.h, r.t_begin + 16 * (blk + p.streams), r.t_end, ctx.lane,
                              aligned, nxt);
-        process_block<PROD, MODE>(p, ctx, cur, tb, r.t_end, st);
+        process_block<PROD, MODE, false, QJL>(p, ctx, cur, tb, r.t_end, st);
         cur = nxt;
     }
     if (MODE == 1) return;
@@ -904,7 +944,7 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ partials, in
                                           long long part_stride, long long seq_stride, int rows_per_seq,
                                           __half* __restrict__ output, float* __restrict__ partials_out,
                                           int row, int num_q_heads, int num_kv_heads, int ref_layout,
-                                          int head_dim, int lane, const PeerOut* peer) {
+                                          int head_dim, int lane, const PeerOut* peer, int head_sign = 1) {
     const int seq = row / rows_per_seq, r = row - seq * rows_per_seq;
     const float* base = partials + seq * seq_stride + static_cast<long long>(r) * TQ_PARTIAL_STRIDE;
     float mmax = kInitMaxLogit;
@@ -959,7 +999,7 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ partials, in
         }
     }
     const float c = inv_sqrt_dim(head_dim);
-    const float s0 = (h & 1) ? -c : c;  // element 4*lane+e: sign + iff (e+h) even
+    const float s0 = (head_sign && (h & 1)) ? -c : c;  // element 4*lane+e: sign + iff (e+h) even (QJL: e even)
     const long long orow = static_cast<long long>(seq) * rows_per_seq +
                            (ref_layout ? gq * num_kv_heads + h : r);
     __half2* dst = reinterpret_cast<__half2*>(output + orow * kHeadDim + 4 * lane);
@@ -973,7 +1013,7 @@ __global__ void __launch_bounds__(128)
 merge_kernel(const float* __restrict__ partials, int num_parts, long long part_stride,
              long long seq_stride, int rows_per_seq, __half* __restrict__ output,
              float* __restrict__ partials_out, int rows, int num_q_heads, int num_kv_heads,
-             int ref_layout, int head_dim, PeerOut peer) {
+             int ref_layout, int head_dim, PeerOut peer, int head_sign) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (peer.world > 0) {
@@ -997,7 +1037,7 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
     }
     if (row >= rows) return;
     merge_row(partials, num_parts, part_stride, seq_stride, rows_per_seq, output, partials_out, row,
-              num_q_heads, num_kv_heads, ref_layout, head_dim, lane, nullptr);
+              num_q_heads, num_kv_heads, ref_layout, head_dim, lane, nullptr, head_sign);
 }
 
 // Dynamic shared memory above 48 KB has to be opted into once per device.
@@ -1012,6 +1052,8 @@ void set_smem_attr_once() {
     check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0, true>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     const int fast_bytes = kFastSmemBytes;
 #define TQ_FAST_ATTR(PRODV, HV)                                                               \
@@ -1045,14 +1087,14 @@ size_t decode_workspace_bytes(int batch, int num_q_heads, int num_splits) {
 
 void launch_merge(const float* partials, int num_parts, void* output, float* partials_out,
                   int rows, int num_q_heads, int num_kv_heads, int ref_query_layout,
-                  int head_dim, cudaStream_t stream) {
+                  int head_dim, cudaStream_t stream, int head_sign) {
     if (rows <= 0) return;
     // parts laid out [num_parts, rows, 130]
     const long long part_stride = static_cast<long long>(rows) * TQ_PARTIAL_STRIDE;
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
         partials, num_parts, part_stride, static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE,
         num_q_heads, static_cast<__half*>(output), partials_out, rows, num_q_heads, num_kv_heads,
-        ref_query_layout, head_dim, PeerOut{});
+        ref_query_layout, head_dim, PeerOut{}, head_sign);
     check_launch("merge_partials");
 }
 
@@ -1062,7 +1104,7 @@ void launch_merge_splits(const float* partials, int splits, void* output, int ro
     const long long part_stride = static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE;
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(partials, splits, part_stride, part_stride * splits,
                                                    num_q_heads, static_cast<__half*>(output), nullptr,
-                                                   rows, num_q_heads, num_kv_heads, 0, head_dim, PeerOut{});
+                                                   rows, num_q_heads, num_kv_heads, 0, head_dim, PeerOut{}, 1);
     check_launch("merge splits");
 }
 
@@ -1073,6 +1115,11 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
         throw std::runtime_error("decode: num_q_heads must be a multiple of num_kv_heads");
     if (a.batch <= 0 || a.num_q_heads <= 0) return;
     const bool prod = a.scheme == TQ_SCHEME_TURBO_PROD;
+    const bool qjl = a.scheme == TQ_SCHEME_QJL;
+    // records of the QJL scheme live in a rotation without the per-head sign; the stand-alone merges
+    // (tq_merge_partials, the peer exchange) apply that sign, so QJL partials are not handed out
+    if (qjl && (a.peer.world > 0 || a.partials_out || a.logits_out))
+        throw std::runtime_error("decode: partials, logits and the peer exchange serve turbo_prod and turbo_mse only");
     const int G = a.num_q_heads / H;
     const int qgroups = (G + 7) / 8;
     const int streams = (8 % H == 0) ? 8 / H : 1;
@@ -1102,6 +1149,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
         if (bs > 0 && (bs & (bs - 1)) == 0)
             for (int sft = 0; sft < 31; ++sft)
                 if ((1 << sft) == bs) p.bs_shift = sft;
+        // (QJL pages, 1344 H bytes with 16-byte K rows and 64-byte V rows, satisfy the same test)
         p.aligned16 = (reinterpret_cast<uintptr_t>(a.pool) & 15) == 0 && (a.geo.page_size & 15) == 0 &&
                       (a.geo.k_codes & 15) == 0 && (a.geo.v_codes & 15) == 0;
     }
@@ -1132,7 +1180,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     p.splits = splits;
 
     const dim3 grid(splits, a.batch, qgroups);
-    const bool fast = a.block_tables && !a.slot_mapping && a.geo.block_size == 16 && p.aligned16 &&
+    const bool fast = !qjl && a.block_tables && !a.slot_mapping && a.geo.block_size == 16 && p.aligned16 &&
                       (H == 1 || H == 2 || H == 4 || H == 8) && (a.geo.k_scales & 15) == 0 &&
                       (a.geo.v_scales & 15) == 0 && (!prod || (a.geo.k_res & 15) == 0) &&
                       a.kv_begin >= 0 && (a.kv_begin & 15) == 0;
@@ -1155,10 +1203,12 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 #undef TQ_FAST_LAUNCH
     } else if (prod) {
         decode_kernel<true, 0><<<grid, warps * 32, smem, stream>>>(p);
+    } else if (qjl) {
+        decode_kernel<false, 0, true><<<grid, warps * 32, smem, stream>>>(p);
     } else {
         decode_kernel<false, 0><<<grid, warps * 32, smem, stream>>>(p);
     }
-    check_launch(prod ? "turbo_prod decode" : "turbo_mse decode");
+    check_launch(prod ? "turbo_prod decode" : qjl ? "qjl decode" : "turbo_mse decode");
 
     // merge the splits of every (sequence, query head) row
     const int rows = a.batch * a.num_q_heads;
@@ -1166,7 +1216,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
         ws, splits, part_stride, part_stride * splits, a.num_q_heads,
         static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
-        a.ref_query_layout, a.head_dim, a.peer);
+        a.ref_query_layout, a.head_dim, a.peer, qjl ? 0 : 1);
     check_launch("decode merge");
     if (owned) check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(decode workspace)");
 }

@@ -8,6 +8,9 @@
 // 16..64, then every lane stores eight half2 values; the eight lanes of a row
 // cover one 32-byte sector per store.  Output is bit-identical to the
 // reference.  An [H, N, D] output order is available for Hugging Face caches.
+// The QJL-1bit scheme (qjl_dequant_kv_kernel, src/cuda/tq_qjl_kernels.cu:172-244) is the third
+// instance: K is one sign bit per dimension times the row's RMS, V as in turbo_prod, and the
+// rotation has no per-head sign.
 #include "tq_common.cuh"
 #include "tq_launch.h"
 
@@ -52,7 +55,8 @@ __device__ __forceinline__ void inverse_and_store(float2 (&x)[8], float* buf, in
     }
 }
 
-template <bool PROD>
+// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit
+template <int S>
 __global__ void __launch_bounds__(kDqWarps * 32)
 dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restrict__ slot_mapping,
                   __half* __restrict__ out_key, __half* __restrict__ out_value, PageGeom geo,
@@ -61,6 +65,7 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
     __shared__ __align__(16) float xchg[kDqWarps][kXchgWarpFloats];
     __shared__ float lut3[8 * 32];
     __shared__ float lut4[16 * 32];
+    constexpr bool PROD = S == 0, QJL = S == 2;
     for (int i = threadIdx.x; i < 8 * 32; i += blockDim.x) lut3[i] = kLevels3[i >> 5];
     for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) lut4[i] = kLevels4[i >> 5];
     __syncthreads();
@@ -94,7 +99,10 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         const int tib = slot - blk * geo.block_size;
         const uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
         const unsigned int th = static_cast<unsigned int>(tib * H + r.h);
-        r.kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
+        if (QJL)  // 16 sign bits: dims 16l .. 16l+15
+            r.kc = make_uint2(__ldg(reinterpret_cast<const unsigned short*>(page + geo.k_codes + th * 16 + 2 * l)), 0u);
+        else
+            r.kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
         r.vc = load_codes(page + geo.v_codes + th * 64 + 8 * l, al);
         r.ks = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.k_scales + th * 2)));
         r.vs = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.v_scales + th * 2)));
@@ -110,7 +118,7 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         if (g + warps_total < groups) fetch(g + warps_total, nxt);
 
         const float re = cur.re;
-        const int h = cur.h;
+        const int h = QJL ? 0 : cur.h;  // the QJL rotation has no head term (tq_qjl_kernels.cu:18-21)
         float2 x[8];
         auto level_k = [&](uint32_t nib) {
             if (PROD) return __fadd_rn(lut3[(nib & 7u) * 32 + lane], (nib & 8u) ? re : -re);
@@ -121,8 +129,13 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         const float2 ks2 = make_float2(cur.ks, cur.ks), vs2 = make_float2(cur.vs, cur.vs);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t b8 = ((k < 4 ? cur.kc.x : cur.kc.y) >> (8 * (k & 3))) & 0xFFu;
-            x[k] = mul2(make_float2(level_k(b8 & 0xFu), level_k(b8 >> 4)), ks2);
+            if (QJL) {  // (bit ? +1 : -1) * ks   (tq_qjl_kernels.cu:235)
+                x[k] = make_float2((cur.kc.x >> (2 * k)) & 1u ? cur.ks : -cur.ks,
+                                   (cur.kc.x >> (2 * k + 1)) & 1u ? cur.ks : -cur.ks);
+            } else {
+                const uint32_t b8 = ((k < 4 ? cur.kc.x : cur.kc.y) >> (8 * (k & 3))) & 0xFFu;
+                x[k] = mul2(make_float2(level_k(b8 & 0xFu), level_k(b8 >> 4)), ks2);
+            }
         }
         inverse_and_store(x, buf, lane, c, h, out_key + cur.out_row * kHeadDim, cur.valid);
 
@@ -138,7 +151,7 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
 
 }  // namespace
 
-void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* out_key,
+void launch_dequant(int scheme, const uint8_t* pool, const int32_t* slots, void* out_key,
                     void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,
                     cudaStream_t stream) {
     if (num_tokens <= 0) return;
@@ -148,15 +161,20 @@ void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* 
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
-    if (prod)
-        dequant_kv_kernel<true><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
+    if (scheme == TQ_SCHEME_TURBO_PROD)
+        dequant_kv_kernel<0><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
+            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
+            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+    else if (scheme == TQ_SCHEME_TURBO_MSE)
+        dequant_kv_kernel<1><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
             pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
             head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
     else
-        dequant_kv_kernel<false><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
+        dequant_kv_kernel<2><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
             pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
             head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
-    check_launch(prod ? "turbo_prod dequant_kv" : "turbo_mse dequant_kv");
+    check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod dequant_kv"
+                 : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse dequant_kv" : "qjl dequant_kv");
 }
 
 }  // namespace tq

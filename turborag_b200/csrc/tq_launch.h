@@ -24,12 +24,12 @@ void set_last_error(const char* msg);
 // does not belong to head_dim 128).
 PageGeom geom_from_layout(int scheme, const void* layout, const TQConfig& cfg);
 
-void launch_pack(bool prod, const void* key, const void* value, const int32_t* slots,
+void launch_pack(int scheme, const void* key, const void* value, const int32_t* slots,
                  uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,
                  cudaStream_t stream);
 
 // hnd: write [H, N, D] instead of [N, H, D].
-void launch_dequant(bool prod, const uint8_t* pool, const int32_t* slots, void* out_key,
+void launch_dequant(int scheme, const uint8_t* pool, const int32_t* slots, void* out_key,
                     void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,
                     cudaStream_t stream);
 
@@ -68,9 +68,11 @@ struct DecodeArgs {
 void launch_decode(const DecodeArgs& a, cudaStream_t stream);
 int decode_num_splits(int batch, int max_kv_tokens, int num_kv_heads, int block_size);
 size_t decode_workspace_bytes(int batch, int num_q_heads, int num_splits);
+// head_sign: 1 when the rotation's sign pattern alternates with the kv head (turbo_prod,
+// turbo_mse), 0 when it does not (QJL).
 void launch_merge(const float* partials, int num_parts, void* output, float* partials_out,
                   int rows, int num_q_heads, int num_kv_heads, int ref_query_layout,
-                  int head_dim, cudaStream_t stream);
+                  int head_dim, cudaStream_t stream, int head_sign = 1);
 
 // Merge of split partials laid out [sequence][split][num_q_heads][130] (what the decode and
 // prefill kernels write), rows = sequences * num_q_heads.

@@ -7,6 +7,9 @@
 // the 128-point transform runs in registers around one shared-memory re-deal,
 // and code bytes leave as 8-byte stores (64 contiguous bytes per token-head).
 // Results are bit-identical to the reference's arithmetic; see tq_common.cuh.
+// The QJL-1bit scheme (qjl_pack_kv_kernel, src/cuda/tq_qjl_kernels.cu:69-170) is the third
+// instance of the same kernel: K keeps one sign bit per rotated dimension and the row's RMS, V
+// is quantised as in turbo_prod, and the rotation has no per-head sign.
 #include "tq_common.cuh"
 #include "tq_launch.h"
 
@@ -140,11 +143,14 @@ __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t
     }
 }
 
-template <bool PROD>
+// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit
+template <int S>
 __global__ void __launch_bounds__(kPackWarps * 32)
 pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, int head_dim, long long num_rows, int pool_aligned8) {
+    constexpr bool PROD = S == 0, QJL = S == 2;
+    constexpr bool TREE128 = PROD || QJL;  // sum of squares: 128-leaf tree (prod, QJL) or 64 pair leaves (mse)
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
     __shared__ __align__(128) uint8_t lutK[PROD ? kCellsK * kLutRowBytes : 16];
     __shared__ __align__(128) uint8_t lutV[kCellsV * kLutRowBytes];
@@ -167,7 +173,9 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         const long long row = valid ? row_raw : num_rows - 1;  // keep all lanes converged
         const long long tok = row / H;
         const int h = static_cast<int>(row - tok * H);
-        const float cs = (h & 1) ? -c : c;  // odd heads: the whole rotated row is negated
+        // odd heads: the whole rotated row is negated; the QJL sign hash has no head term
+        // (tq_qjl_kernels.cu:18-21)
+        const float cs = (!QJL && (h & 1)) ? -c : c;
 
         const uint4* kp = key + row * 16 + 2 * l;
         const uint4* vp = value + row * 16 + 2 * l;
@@ -191,7 +199,42 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         for (int j = 0; j < 8; ++j) y[j] = mul2(y[j], cs2);
 
         uint32_t kbytes[8];
-        if (PROD) {
+        if (QJL) {
+            float2 sq[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
+            const float krms = rms_from_sum(tree128(sq));
+            // bit = (k / krms >= 0) (tq_qjl_kernels.cu:155): krms > 0 and the quotient of a rotated
+            // fp16 row cannot underflow, so this is the sign of k itself (-0 counts as >= 0)
+            uint32_t w0 = 0u, w1 = 0u;  // byte j & 3 of w(j >> 2): this lane's 2 bits of sign byte 2j + (l >> 2)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t two = (y[j].x >= 0.0f ? 1u : 0u) | (y[j].y >= 0.0f ? 2u : 0u);
+                const uint32_t at = two << (2 * (l & 3) + 8 * (j & 3));
+                if (j < 4) w0 |= at; else w1 |= at;
+            }
+#pragma unroll
+            for (int m = 1; m <= 2; m <<= 1) {
+                w0 |= __shfl_xor_sync(0xffffffffu, w0, m);
+                w1 |= __shfl_xor_sync(0xffffffffu, w1, m);
+            }
+            // lanes 0-3 hold the even sign bytes, lanes 4-7 the odd ones
+            const uint32_t o0 = __shfl_xor_sync(0xffffffffu, w0, 4), o1 = __shfl_xor_sync(0xffffffffu, w1, 4);
+            if (valid && l == 0) {
+                const uint4 bits = make_uint4(__byte_perm(w0, o0, 0x5140), __byte_perm(w0, o0, 0x7362),
+                                              __byte_perm(w1, o1, 0x5140), __byte_perm(w1, o1, 0x7362));
+                uint8_t* dst = page + geo.k_codes + th * 16;
+                if (pool_aligned8) {
+                    reinterpret_cast<uint2*>(dst)[0] = make_uint2(bits.x, bits.y);
+                    reinterpret_cast<uint2*>(dst)[1] = make_uint2(bits.z, bits.w);
+                } else {
+                    const uint32_t wds[4] = {bits.x, bits.y, bits.z, bits.w};
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) dst[i] = static_cast<uint8_t>(wds[i >> 2] >> (8 * (i & 3)));
+                }
+                *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
+            }
+        } else if (PROD) {
             float2 sq[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
@@ -227,8 +270,9 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             if (valid && l == 0)
                 *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
         }
-        store_codes(kbytes, code_buf, page + geo.k_codes + th * 64, lane, valid,
-                    pool_aligned8 != 0);
+        if (!QJL)
+            store_codes(kbytes, code_buf, page + geo.k_codes + th * 64, lane, valid,
+                        pool_aligned8 != 0);
 
         // ---------------- V ----------------
         fwht_phase1_from_half(v_lo, v_hi, x);
@@ -237,7 +281,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = mul2(y[j], cs2);
         float vrms;
-        if (PROD) {
+        if (TREE128) {
             float2 sq[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
@@ -265,7 +309,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 
 }  // namespace
 
-void launch_pack(bool prod, const void* key, const void* value, const int32_t* slots,
+void launch_pack(int scheme, const void* key, const void* value, const int32_t* slots,
                  uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,
                  cudaStream_t stream) {
     if (num_tokens <= 0) return;
@@ -275,15 +319,16 @@ void launch_pack(bool prod, const void* key, const void* value, const int32_t* s
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
-    if (prod)
-        pack_kv_kernel<true><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
-            static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
-            head_dim, rows, aligned);
-    else
-        pack_kv_kernel<false><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
-            static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
-            head_dim, rows, aligned);
-    check_launch(prod ? "turbo_prod pack_kv" : "turbo_mse pack_kv");
+#define TQ_PACK_LAUNCH(SV)                                                                     \
+    pack_kv_kernel<SV><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
+        static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,    \
+        head_dim, rows, aligned)
+    if (scheme == TQ_SCHEME_TURBO_PROD) TQ_PACK_LAUNCH(0);
+    else if (scheme == TQ_SCHEME_TURBO_MSE) TQ_PACK_LAUNCH(1);
+    else TQ_PACK_LAUNCH(2);
+#undef TQ_PACK_LAUNCH
+    check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod pack_kv"
+                 : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse pack_kv" : "qjl pack_kv");
 }
 
 }  // namespace tq

@@ -17,7 +17,7 @@ import torch
 PKG = Path(__file__).resolve().parent
 DEFAULT_LIB_PATH = PKG / "lib" / "libturboquant.so"
 
-SCHEME_ID = {"turbo_prod": 0, "turbo_mse": 1}
+SCHEME_ID = {"turbo_prod": 0, "turbo_mse": 1, "qjl": 2}
 PARTIAL_STRIDE = 130
 INT32_MAX = 2**31 - 1
 
@@ -44,10 +44,18 @@ TQTurbomsePageLayout = _struct(
         "code_bytes_per_token_head", "norm_bytes_per_token_head", "k_codes_offset",
         "v_codes_offset", "k_norms_offset", "v_norms_offset", "page_size_bytes")])
 
+TQQJLPageLayout = _struct(
+    "TQQJLPageLayout", "include/tq_qjl.cuh:22-35",
+    [(n, C.c_size_t) for n in (
+        "page_size_bytes", "k1_codes_offset", "k_scales_offset", "v4_codes_offset", "v_scales_offset")] +
+    [(n, C.c_int) for n in (
+        "k1_bytes_per_token_head", "v4_bytes_per_token_head", "scale_bytes_per_token_head")])
+
 _P = C.c_void_p
 _CFG = C.POINTER(TQConfig)
 _PROD = C.POINTER(TQTurboProdPageLayout)
 _MSE = C.POINTER(TQTurbomsePageLayout)
+_QJL = C.POINTER(TQQJLPageLayout)
 
 # symbol -> (restype, argtypes); every symbol declared in include/turboquant.h
 SIGNATURES = {
@@ -65,6 +73,10 @@ SIGNATURES = {
     "tq_launch_turbo_mse_dequant_kv": (C.c_int, [_P, _P, _P, _P, _MSE, _CFG, C.c_int, _P]),
     "tq_launch_turbo_mse_fused_attention_output":
         (C.c_int, [_P, _P, _P, _P, _MSE, _CFG, C.c_int, C.c_int, _P]),
+    "tq_make_qjl_layout": (C.c_int, [_CFG, _QJL]),
+    "tq_launch_qjl_pack_kv": (C.c_int, [_P, _P, _P, _P, _QJL, _CFG, C.c_int, _P]),
+    "tq_launch_qjl_dequant_kv": (C.c_int, [_P, _P, _P, _P, _QJL, _CFG, C.c_int, _P]),
+    "tq_launch_qjl_fused_attention_output": (C.c_int, [_P, _P, _P, _P, _QJL, _CFG, C.c_int, C.c_int, _P]),
     "tq_decode_num_splits": (C.c_int, [C.c_int] * 4),
     "tq_decode_workspace_bytes": (C.c_size_t, [C.c_int] * 3),
     "tq_decode_paged": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _P, _P, _CFG, C.c_int,
@@ -159,7 +171,15 @@ class TurboQuantWrapper:
             raise RuntimeError("tq_make_turbo_mse_layout failed")
         return layout
 
+    def make_qjl_layout_for(self, cfg: TQConfig) -> TQQJLPageLayout:
+        layout = TQQJLPageLayout()
+        if self._lib.tq_make_qjl_layout(C.byref(cfg), C.byref(layout)) != 0:
+            raise RuntimeError("Failed to build the QJL layout.")
+        return layout
+
     def layout_for_scheme(self, scheme: str, cfg: TQConfig):
+        if scheme == "qjl":
+            return self.make_qjl_layout_for(cfg)
         return self.make_layout_for(cfg) if scheme == "turbo_prod" else self.make_mse_layout_for(cfg)
 
     # -- turbo_prod ---------------------------------------------------------------
@@ -212,6 +232,28 @@ class TurboQuantWrapper:
         _cuda(query, page_pool, slot_mapping, output)
         self._call("turbo_mse", "fused_attn_output",
                    self._lib.tq_launch_turbo_mse_fused_attention_output,
+                   _ptr(query), _ptr(page_pool), _ptr(slot_mapping), _ptr(output),
+                   C.byref(layout), C.byref(cfg), num_queries, num_kv_tokens, C.c_void_p(stream))
+
+    # -- QJL-1bit (src/cuda/tq_qjl_kernels.cu; not bound by the reference's wrapper) --------------
+    def qjl_pack(self, key, value, slot_mapping, page_pool, layout, cfg, stream: int = 0) -> None:
+        _cuda(key, value, slot_mapping, page_pool)
+        self._call("qjl", "pack_kv", self._lib.tq_launch_qjl_pack_kv,
+                   _ptr(key), _ptr(value), _ptr(slot_mapping), _ptr(page_pool),
+                   C.byref(layout), C.byref(cfg), key.shape[0], C.c_void_p(stream))
+
+    def qjl_dequant(self, page_pool, slot_mapping, out_key, out_value, layout, cfg,
+                    stream: int = 0) -> None:
+        _cuda(page_pool, slot_mapping, out_key, out_value)
+        self._call("qjl", "dequant_kv", self._lib.tq_launch_qjl_dequant_kv,
+                   _ptr(page_pool), _ptr(slot_mapping), _ptr(out_key), _ptr(out_value),
+                   C.byref(layout), C.byref(cfg), out_key.shape[0], C.c_void_p(stream))
+
+    def qjl_fused_attn_output(self, query, page_pool, slot_mapping, output, layout, cfg,
+                              num_queries: int, num_kv_tokens: int, stream: int = 0) -> None:
+        """Logits are <q', k'> without 1/sqrt(head_dim) (tq_qjl_kernels.cu:335)."""
+        _cuda(query, page_pool, slot_mapping, output)
+        self._call("qjl", "fused_attn_output", self._lib.tq_launch_qjl_fused_attention_output,
                    _ptr(query), _ptr(page_pool), _ptr(slot_mapping), _ptr(output),
                    C.byref(layout), C.byref(cfg), num_queries, num_kv_tokens, C.c_void_p(stream))
 
