@@ -289,6 +289,7 @@ struct WarpState {
 
 struct BlockCtx {
     uint32_t qf[8][2];  // B fragments of the rotated, pre-scaled queries
+    uint32_t qlo[8][2];  // QJL only: fp16 remainders of the same values
     BytePools pool3, mag4;
     float inv_alpha_v;
     uint8_t* warp_smem;   // per-warp shared region (merge record at the end; fast path: ring)
@@ -424,15 +425,20 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         // MMA s = 2wi + hf takes dims 8wi + {2hf, 2hf+4 | 2hf+1, 2hf+5} of the lane's 32 (the
         // pairing of the query fragments): operands are +-1.0 straight from the sign bits
         const uint32_t n0 = ~kw0[0], n1 = ~kw1[0];
-#define TQ_QJL_STEP(SV)                                                                           \
-    mma16816(s1, sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n0),  \
-             sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n1),      \
-             sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n0),  \
-             sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n1),  \
-             qf[SV][0], qf[SV][1])
+#define TQ_QJL_STEP(SV)                                                                                  \
+    {                                                                                                    \
+        const uint32_t a0 = sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n0);     \
+        const uint32_t a1 = sign_half2<8 * (SV >> 1) + 2 * (SV & 1), 8 * (SV >> 1) + 2 * (SV & 1) + 4>(n1);     \
+        const uint32_t a2 = sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n0); \
+        const uint32_t a3 = sign_half2<8 * (SV >> 1) + 2 * (SV & 1) + 1, 8 * (SV >> 1) + 2 * (SV & 1) + 5>(n1); \
+        mma16816(s1, a0, a1, a2, a3, qf[SV][0], qf[SV][1]);                                              \
+        mma16816(s2, a0, a1, a2, a3, c.qlo[SV][0], c.qlo[SV][1]);                                        \
+    }
         TQ_QJL_STEP(0); TQ_QJL_STEP(1); TQ_QJL_STEP(2); TQ_QJL_STEP(3);
         TQ_QJL_STEP(4); TQ_QJL_STEP(5); TQ_QJL_STEP(6); TQ_QJL_STEP(7);
 #undef TQ_QJL_STEP
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s1[e] += s2[e];  // hi and lo parts of the query
     } else {
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
@@ -616,8 +622,17 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
             for (int e = 0; e < 4; ++e) x[e] *= sc;
         }
         __half2* dst = reinterpret_cast<__half2*>(qsm + (h * 8 + col) * kHeadDim + 4 * lane);
-        dst[0] = __floats2half2_rn(x[0], x[1]);
-        dst[1] = __floats2half2_rn(x[2], x[3]);
+        const __half2 hi0 = __floats2half2_rn(x[0], x[1]), hi1 = __floats2half2_rn(x[2], x[3]);
+        dst[0] = hi0;
+        dst[1] = hi1;
+        if (QJL) {
+            // the fp16 rounding of q' that the other schemes tolerate is 11 times larger against
+            // unscaled logits: keep the remainder as a second fp16 fragment set (q' = hi + lo)
+            const float2 h0 = __half22float2(hi0), h1 = __half22float2(hi1);
+            __half2* dlo = dst + (H * 8 * kHeadDim) / 2;
+            dlo[0] = __floats2half2_rn(x[0] - h0.x, x[1] - h0.y);
+            dlo[1] = __floats2half2_rn(x[2] - h1.x, x[3] - h1.y);
+        }
     }
     group_sync(bar_id, bar_threads);
 
@@ -637,6 +652,13 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                 const __half2 b23 = __halves2half2(qrow[base + 1], qrow[base + 5]);
                 ctx.qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
                 ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
+                if (QJL) {
+                    const __half* qlo = qrow + H * 8 * kHeadDim;
+                    const __half2 l01 = __halves2half2(qlo[base], qlo[base + 4]);
+                    const __half2 l23 = __halves2half2(qlo[base + 1], qlo[base + 5]);
+                    ctx.qlo[s][0] = *reinterpret_cast<const uint32_t*>(&l01);
+                    ctx.qlo[s][1] = *reinterpret_cast<const uint32_t*>(&l23);
+                }
             }
         }
     }
@@ -1053,8 +1075,8 @@ void set_smem_attr_once() {
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     check_cuda(cudaFuncSetAttribute(decode_kernel<true, 1>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
-    check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0, true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
+    check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0, true>,  // two query scratches: 8 heads need 68 KB
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, 73728), "smem attr");
     const int fast_bytes = kFastSmemBytes;
 #define TQ_FAST_ATTR(PRODV, HV)                                                               \
     check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<PRODV, HV>,                         \
@@ -1124,7 +1146,9 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     const int qgroups = (G + 7) / 8;
     const int streams = (8 % H == 0) ? 8 / H : 1;
     const int warps = H * streams;
-    const size_t smem = static_cast<size_t>(warps) * kWarpSmemBytes + H * 8 * kHeadDim * sizeof(__half);
+    // per-warp regions, then the query scratch (QJL: a second one for the fp16 remainders)
+    const size_t smem = static_cast<size_t>(warps) * kWarpSmemBytes +
+                        (a.scheme == TQ_SCHEME_QJL ? 2 : 1) * H * 8 * kHeadDim * sizeof(__half);
 
     DecodeParams p{};
     p.query = static_cast<const __half*>(a.query);
