@@ -174,6 +174,34 @@ void ref_attention(int scheme, const void* query, const uint8_t* pool, const int
 }  // namespace
 
 namespace tq {
+void* scratch_alloc(size_t bytes, cudaStream_t stream, const char* what) {
+    static cudaMemPool_t pools[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64) throw std::runtime_error("scratch: device index out of range");
+    cudaMemPool_t pool;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!pools[dev]) {
+            cudaMemPoolProps props{};
+            props.allocType = cudaMemAllocationTypePinned;
+            props.handleTypes = cudaMemHandleTypeNone;
+            props.location.type = cudaMemLocationTypeDevice;
+            props.location.id = dev;
+            check_cuda(cudaMemPoolCreate(&pools[dev], &props), "cudaMemPoolCreate(scratch)");
+            unsigned long long keep = 1ull << 30;
+            check_cuda(cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep),
+                       "cudaMemPoolSetAttribute(release threshold)");
+        }
+        pool = pools[dev];
+    }
+    void* p = nullptr;
+    check_cuda(cudaMallocFromPoolAsync(&p, bytes, pool, stream), what);
+    return p;
+}
+void scratch_free(void* p, cudaStream_t stream, const char* what) { check_cuda(cudaFreeAsync(p, stream), what); }
+
 void set_last_error(const char* msg) { set_error(msg); }
 PageGeom geom_from_layout(int scheme, const void* layout, const TQConfig& cfg) {
     return geom_for(scheme, layout, cfg);

@@ -1193,9 +1193,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     float* ws = static_cast<float*>(a.workspace);
     bool owned = false;
     if (!ws) {
-        void* tmp = nullptr;
-        check_cuda(cudaMallocAsync(&tmp, need, stream), "cudaMallocAsync(decode workspace)");
-        ws = static_cast<float*>(tmp);
+        ws = static_cast<float*>(scratch_alloc(need, stream, "scratch_alloc(decode workspace)"));
         owned = true;
     } else if (a.workspace_bytes < need) {
         throw std::runtime_error("decode: workspace too small, need " + std::to_string(need) + " bytes");
@@ -1242,7 +1240,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
         static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
         a.ref_query_layout, a.head_dim, a.peer, qjl ? 0 : 1);
     check_launch("decode merge");
-    if (owned) check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(decode workspace)");
+    if (owned) scratch_free(ws, stream, "scratch_free(decode workspace)");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1254,7 +1252,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 // allocation can fail or fragment it), a real-time loop that cannot afford the implicit
 // synchronisation an allocation may cause, or code that runs while a CUDA stream is being
 // captured.  tq_decode_paged_static serves them: same arithmetic as tq_decode_paged, but the
-// split-KV partials go to the fixed array below instead of a caller buffer or cudaMallocAsync.
+// split-KV partials go to the fixed array below instead of a caller buffer or the library's stream-ordered scratch pool.
 //
 // The array is part of the loaded module: every GPU that loads the library holds these
 // bytes until the process exits.  All calls on a device share it, and it keeps whatever the

@@ -18,6 +18,13 @@ namespace tq {
 void check_launch(const char* name);
 void check_cuda(cudaError_t e, const char* what);
 int sm_count();
+// Stream-ordered scratch memory for calls that were not given a workspace.  It comes from a
+// memory pool the library owns (one per device, created on first use) whose release threshold
+// keeps up to 1 GiB cached across synchronisations: the driver's default pool returns its
+// memory to the system at every synchronise, and the next call then pays milliseconds to map it
+// again.  Nothing here touches the process-wide default pool.
+void* scratch_alloc(size_t bytes, cudaStream_t stream, const char* what);
+void scratch_free(void* p, cudaStream_t stream, const char* what);
 // Stores a message for tq_last_error() of the calling thread.
 void set_last_error(const char* msg);
 // Page geometry from a TQTurboProdPageLayout* / TQTurbomsePageLayout* (throws on a layout that

@@ -673,8 +673,8 @@ void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* bl
     const size_t part_bytes = static_cast<size_t>(q_rows) * splits * TQ_PARTIAL_STRIDE * sizeof(float);
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     uint8_t* ws = nullptr;
-    check_cuda(cudaMallocAsync(reinterpret_cast<void**>(&ws), up(q_bytes) + 2 * up(kv_bytes) + part_bytes, stream),
-               "cudaMallocAsync(prefill workspace)");
+    ws = static_cast<decltype(ws)>(scratch_alloc(up(q_bytes) + 2 * up(kv_bytes) + part_bytes, stream,
+                                                 "scratch_alloc(prefill workspace)"));
     __half* q_rot = reinterpret_cast<__half*>(ws);
     __half* ck_rot = reinterpret_cast<__half*>(ws + up(q_bytes));
     __half* cv_rot = reinterpret_cast<__half*>(ws + up(q_bytes) + up(kv_bytes));
@@ -719,7 +719,7 @@ void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* bl
     prefill_tc_kernel<<<dim3(mtiles, H * splits, batch), kThreadsTc, kSmemTc, stream>>>(p);
     check_launch("turbo_mse prefill (tcgen05)");
     launch_merge_splits(partials, splits, output, static_cast<int>(q_rows), hq, H, head_dim, stream);
-    check_cuda(cudaFreeAsync(ws, stream), "cudaFreeAsync(prefill workspace)");
+    scratch_free(ws, stream, "scratch_free(prefill workspace)");
 }
 
 }  // namespace tq
