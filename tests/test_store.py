@@ -92,7 +92,7 @@ def test_reference_store_and_wrapper_accept_this_library(tmp_path, lib_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse", "fp16"])
+@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse", "qjl", "fp16"])
 def test_store_round_trip_on_gpu(tmp_path, lib_path, scheme):
     from turborag_b200.store import CAGStore
     dev = torch.device("cuda:0")
@@ -117,7 +117,9 @@ def test_store_round_trip_on_gpu(tmp_path, lib_path, scheme):
             assert torch.equal(dk, k) and torch.equal(dv, v)
         else:
             rel = ((dk.float() - k.float()).pow(2).mean() / k.float().pow(2).mean()).item()
-            assert rel < 0.35  # the reference's own round-trip bound (tests/test_cag.py:240-246)
+            # the reference's own round-trip bound (tests/test_cag.py:240-246); one sign bit per K
+            # dimension keeps 1 - 2/pi of the energy as error
+            assert rel < (0.45 if scheme == "qjl" else 0.35)
         direct.append((dk, dv))
     # all layers, [1, H, N, D], reads overlapped with dequant: same bits as the layer-by-layer path
     got, doc_len = st.load_layers_hnd("doc", layers + 2, scheme, (h, d))
@@ -133,10 +135,14 @@ def test_store_round_trip_on_gpu(tmp_path, lib_path, scheme):
     q = torch.randn(8, h, d, device=dev, generator=g).half()
     out = st.fused_attention(q, pool, slots, n, scheme, (h, d))
     dk, dv = direct[1]
-    ref = torch.softmax(torch.einsum("qhd,nhd->hqn", q.float(), dk.float()) * d ** -0.5, dim=-1)
+    # QJL logits are not scaled by 1/sqrt(d) (tq_qjl_kernels.cu:335)
+    ref = torch.softmax(torch.einsum("qhd,nhd->hqn", q.float(), dk.float()) * (1.0 if scheme == "qjl" else d ** -0.5), dim=-1)
     ref = torch.einsum("hqn,nhd->qhd", ref, dv.float())
     err = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
-    assert err < 5e-3, err  # against attention over the dequantised fp16 tensors
+    # against attention over the dequantised fp16 tensors; with QJL's unscaled logits the fp16 rounding
+    # of those tensors alone moves the softmax weights by a few parts per thousand (the kernel itself
+    # is held to 2e-3 against the oracle in tests/test_qjl.py)
+    assert err < (3e-2 if scheme == "qjl" else 5e-3), err
     if scheme != "fp16":
         pools = [st.load_document("doc", l, scheme, (h, d))[0] for l in range(layers)]
         qb = torch.randn(layers, 16, d, device=dev, generator=g).half()
@@ -194,7 +200,7 @@ def test_container_header_and_damage_detection(tmp_path, lib_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse"])
+@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse", "qjl"])
 def test_container_load_matches_per_layer_files(tmp_path, lib_path, scheme):
     from turborag_b200.store import CAGStore
     dev = torch.device("cuda:0")

@@ -43,7 +43,7 @@ import torch
 
 from .wrapper import TQConfig, TurboQuantWrapper
 
-Scheme = Literal["fp16", "turbo_prod", "turbo_mse"]
+Scheme = Literal["fp16", "turbo_prod", "turbo_mse", "qjl"]  # "qjl": not in the reference's store
 _MANIFEST = "manifest.json"
 
 # One-file-per-document container (not in the reference, whose per-layer files carry no header):
@@ -60,7 +60,7 @@ _DOC_FIXED = struct.Struct("<8sIIIIQIIIIQQ")
 _DOC_ALIGN = 4096
 _READ_RING = 8      # pinned staging buffers a container load keeps in flight
 _READ_THREADS = 4   # reader threads (file reads release the interpreter lock)
-_SCHEME_IDS = {"turbo_prod": 0, "turbo_mse": 1}
+_SCHEME_IDS = {"turbo_prod": 0, "turbo_mse": 1, "qjl": 2}
 
 
 def _align_up(x: int, a: int) -> int:
@@ -160,6 +160,8 @@ class CAGStore:
             return self.tq.make_layout_for(cfg)
         if scheme == "turbo_mse":
             return self.tq.make_mse_layout_for(cfg)
+        if scheme == "qjl":
+            return self.tq.make_qjl_layout_for(cfg)
         raise ValueError(f"Unknown scheme: {scheme}")
 
     def _pool_bytes(self, scheme: Scheme, num_tokens: int, cfg: TQConfig) -> int:
@@ -188,7 +190,7 @@ class CAGStore:
             cfg = self._make_cfg(key)
             layout = self._layout(scheme, cfg)
             pool = torch.zeros(self._pool_bytes(scheme, n, cfg), dtype=torch.uint8, device=key.device)
-            (self.tq.pack if scheme == "turbo_prod" else self.tq.mse_pack)(
+            {"turbo_prod": self.tq.pack, "turbo_mse": self.tq.mse_pack, "qjl": self.tq.qjl_pack}[scheme](
                 key.contiguous(), value.contiguous(), slots, pool, layout, cfg)
             host = torch.empty(pool.numel(), dtype=torch.uint8, pin_memory=True)
             host.copy_(pool, non_blocking=True)
@@ -267,7 +269,7 @@ class CAGStore:
         h, d = head_shape
         out_k = torch.empty(n, h, d, device=slots.device, dtype=torch.float16)
         out_v = torch.empty_like(out_k)
-        (self.tq.dequant if scheme == "turbo_prod" else self.tq.mse_dequant)(
+        {"turbo_prod": self.tq.dequant, "turbo_mse": self.tq.mse_dequant, "qjl": self.tq.qjl_dequant}[scheme](
             pool, slots, out_k, out_v, self._layout(scheme, cfg), cfg)
         return out_k, out_v
 
@@ -530,7 +532,8 @@ class CAGStore:
             return torch.bmm(attn, v).permute(1, 0, 2).to(query.dtype)
         cfg = self._make_cfg_from_shape(head_shape)
         output = torch.empty_like(query)
-        fn = self.tq.fused_attn_output if scheme == "turbo_prod" else self.tq.mse_fused_attn_output
+        fn = {"turbo_prod": self.tq.fused_attn_output, "turbo_mse": self.tq.mse_fused_attn_output,
+              "qjl": self.tq.qjl_fused_attn_output}[scheme]
         fn(query.contiguous(), pool, slots, output, self._layout(scheme, cfg), cfg, query.shape[0], N)
         return output
 
