@@ -290,6 +290,7 @@ struct WarpState {
 struct BlockCtx {
     uint32_t qf[8][2];  // B fragments of the rotated, pre-scaled queries
     uint32_t qlo[8][2];  // QJL only: fp16 remainders of the same values
+    const uint4* qsign;  // fast path, turbo_prod: this head's query fragments in the (d, d+4) pairing, [4][32]
     BytePools pool3, mag4;
     float inv_alpha_v;
     uint8_t* warp_smem;   // per-warp shared region (merge record at the end; fast path: ring)
@@ -377,7 +378,7 @@ __device__ __forceinline__ uint32_t sign_half2(uint32_t nw) {
     return (lo & 0x8000u) | (hi & 0x80000000u) | 0x3C003C00u;
 }
 
-template <bool PROD, int MODE, bool LUT = false, bool QJL = false>
+template <bool PROD, int MODE, bool LUT = false, bool QJL = false, bool SIGNQ = false>
 __device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
                                               const BlockRaw& cur, int tb, int t_end,
                                               WarpState& st) {
@@ -407,12 +408,26 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
                 const uint32_t e01 = lut_v(c.lut, kw0[wi], c.lane_k, sb);
                 const uint32_t e11 = lut_v(c.lut, kw1[wi], c.lane_k, sb);
                 mma16816(s1, e00, e10, e01, e11, qf[n][0], qf[n][1]);
-                if ((n & 1) == 0) {
-                    sign_pairs(kw0[wi], sg0);
-                    sign_pairs(kw1[wi], sg1);
+                if constexpr (SIGNQ) {
+                    // Residual signs paired (d, d+4): one shift on the multiplier pipe and one logic
+                    // op per register (the table's (d, d+1) pairing costs a permute more, and the
+                    // logic pipe is the busiest one).  The matching query fragments are not kept in
+                    // registers: one 16-byte shared load per code word fetches them.
+                    if ((n & 1) == 0) {
+                        const uint4 qs = c.qsign[wi * 32 + c.lane];
+                        unpack_sign(kw0[wi], sg0);
+                        unpack_sign(kw1[wi], sg1);
+                        mma16816(s2, sg0[0], sg1[0], sg0[1], sg1[1], qs.x, qs.y);
+                        mma16816(s2, sg0[2], sg1[2], sg0[3], sg1[3], qs.z, qs.w);
+                    }
+                } else {
+                    if ((n & 1) == 0) {
+                        sign_pairs(kw0[wi], sg0);
+                        sign_pairs(kw1[wi], sg1);
+                    }
+                    mma16816(s2, sg0[2 * (n & 1)], sg1[2 * (n & 1)], sg0[2 * (n & 1) + 1],
+                             sg1[2 * (n & 1) + 1], qf[n][0], qf[n][1]);
                 }
-                mma16816(s2, sg0[2 * (n & 1)], sg1[2 * (n & 1)], sg0[2 * (n & 1) + 1],
-                         sg1[2 * (n & 1) + 1], qf[n][0], qf[n][1]);
             } else {
                 const uint32_t e00 = lut_v(c.lut, kw0[wi], c.lane_v, sa);
                 const uint32_t e10 = lut_v(c.lut, kw1[wi], c.lane_v, sa);
@@ -575,7 +590,7 @@ template <bool PROD, int MODE, bool LUT = false, bool QJL = false>
 __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* group_smem,
                                                 int warp_bytes, __half* qsm, int warp, int seq,
                                                 int split, int bar_id, int bar_threads,
-                                                BlockCtx& ctx, CtaRange& r) {
+                                                BlockCtx& ctx, CtaRange& r, uint4* qsign_group = nullptr) {
     const int lane = threadIdx.x & 31;
     const int H = p.geo.num_kv_heads;
     const int h = warp % H, stream = warp / H;
@@ -661,6 +676,24 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                 }
             }
         }
+    }
+    ctx.qsign = nullptr;
+    if (qsign_group) {
+        // fragments in the (d, d+4) pairing for the residual-sign MMAs: word wi of the lane's 32 dims
+        // -> (q[0],q[4]) (q[1],q[5]) | (q[2],q[6]) (q[3],q[7]); written once per kv head
+        const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
+        if (stream == 0) {
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const __half* q8 = qrow + 8 * wi;
+                const __half2 f0 = __halves2half2(q8[0], q8[4]), f1 = __halves2half2(q8[1], q8[5]);
+                const __half2 f2 = __halves2half2(q8[2], q8[6]), f3 = __halves2half2(q8[3], q8[7]);
+                qsign_group[(h * 4 + wi) * 32 + lane] =
+                    make_uint4(*reinterpret_cast<const uint32_t*>(&f0), *reinterpret_cast<const uint32_t*>(&f1),
+                               *reinterpret_cast<const uint32_t*>(&f2), *reinterpret_cast<const uint32_t*>(&f3));
+            }
+        }
+        ctx.qsign = qsign_group + h * 4 * 32;
     }
     // fp16(alpha * level) split into high-byte and low-byte pools, entries 0-3 | 4-7
     // (tests/test_abi.py recomputes them from the level tables)
@@ -827,6 +860,13 @@ constexpr int kFastGroupWarps = 8;
 constexpr int kFastGroups = 2;
 constexpr int kFastGroupBytes = kFastGroupWarps * kFastWarpBytes;
 constexpr int kFastSmemBytes = kLutBytes + kFastGroups * kFastGroupBytes;
+// turbo_prod, up to 4 kv heads: the residual-sign query fragments of each group (2 KB per head) sit
+// behind the rings; with 8 heads they would not fit and the table pairing serves the signs too
+constexpr int kSignFragBytesPerHead = 4 * 32 * 16;
+__host__ __device__ constexpr bool sign_frags(bool prod, int heads) { return prod && heads <= 4; }
+__host__ __device__ constexpr int fast_smem_bytes(bool prod, int heads) {
+    return kFastSmemBytes + (sign_frags(prod, heads) ? kFastGroups * heads * kSignFragBytesPerHead : 0);
+}
 static_assert(kFastGroupBytes >= kMaxHeads * 8 * kHeadDim * 2, "the query scratch reuses the ring");
 
 template <bool PROD, int H>
@@ -845,9 +885,13 @@ decode_paged16_kernel(DecodeParams p) {
     const int bar_id = 1 + group, bar_threads = kFastGroupWarps * 32;
     BlockCtx ctx;
     CtaRange r;
+    constexpr bool kSignQ = sign_frags(PROD, H);
+    uint4* qsign_group = kSignQ ? reinterpret_cast<uint4*>(smem_raw + kFastSmemBytes +
+                                                           group * H * kSignFragBytesPerHead)
+                                : nullptr;
     decode_prologue<PROD, 0, true>(p, group_smem, kFastWarpBytes, reinterpret_cast<__half*>(group_smem),
                                    (threadIdx.x >> 5) % kFastGroupWarps, seq, split, bar_id,
-                                   bar_threads, ctx, r);
+                                   bar_threads, ctx, r, qsign_group);
     ctx.lut = smem_raw;
     group_sync(bar_id, bar_threads);  // the query scratch is dead: the ring may be filled
     WarpState st;
@@ -953,7 +997,7 @@ decode_paged16_kernel(DecodeParams p) {
             if (tb + g >= r.t_end) cur.ks0 = cur.vs0 = cur.re0 = 0.0f;
             if (tb + g + 8 >= r.t_end) cur.ks1 = cur.vs1 = cur.re1 = 0.0f;
         }
-        process_block<PROD, 0, true>(p, ctx, cur, tb, r.t_end, st);
+        process_block<PROD, 0, true, false, kSignQ>(p, ctx, cur, tb, r.t_end, st);
         __syncwarp();  // every lane is done reading this stage before it is refilled
         stage = stage == kStages - 1 ? 0 : stage + 1;
     }
@@ -1077,10 +1121,10 @@ void set_smem_attr_once() {
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "smem attr");
     check_cuda(cudaFuncSetAttribute(decode_kernel<false, 0, true>,  // two query scratches: 8 heads need 68 KB
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 73728), "smem attr");
-    const int fast_bytes = kFastSmemBytes;
 #define TQ_FAST_ATTR(PRODV, HV)                                                               \
     check_cuda(cudaFuncSetAttribute(decode_paged16_kernel<PRODV, HV>,                         \
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, fast_bytes), \
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                                    fast_smem_bytes(PRODV, HV)),                              \
                "smem attr")
     TQ_FAST_ATTR(true, 1); TQ_FAST_ATTR(true, 2); TQ_FAST_ATTR(true, 4); TQ_FAST_ATTR(true, 8);
     TQ_FAST_ATTR(false, 1); TQ_FAST_ATTR(false, 2); TQ_FAST_ATTR(false, 4); TQ_FAST_ATTR(false, 8);
@@ -1209,8 +1253,8 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (fast) {
         const dim3 fgrid((a.batch * splits + kFastGroups - 1) / kFastGroups, 1, qgroups);
 #define TQ_FAST_LAUNCH(PRODV, HV)                                                                \
-    decode_paged16_kernel<PRODV, HV><<<fgrid, kFastGroups * kFastGroupWarps * 32, kFastSmemBytes, \
-                                       stream>>>(p)
+    decode_paged16_kernel<PRODV, HV><<<fgrid, kFastGroups * kFastGroupWarps * 32,                \
+                                       fast_smem_bytes(PRODV, HV), stream>>>(p)
         if (prod) {
             if (H == 1) TQ_FAST_LAUNCH(true, 1);
             else if (H == 2) TQ_FAST_LAUNCH(true, 2);
