@@ -83,6 +83,18 @@ def run_question(model, cache, question, steps):
     return logits
 
 
+def generate_like_reference(model, cache, question, n_prefix, steps):
+    """The call the reference's runner makes (tq_backend/benchmark.py:250-262): question tokens only,
+    positions continuing after the document, attention mask over document + question."""
+    q_len = question.shape[1]
+    pos = torch.arange(n_prefix, n_prefix + q_len, device=question.device).unsqueeze(0)
+    mask = torch.ones(1, n_prefix + q_len, device=question.device, dtype=torch.long)
+    with torch.no_grad():
+        out = model.generate(input_ids=question, attention_mask=mask, past_key_values=cache, position_ids=pos,
+                             max_new_tokens=steps, do_sample=False, temperature=None, top_p=None)
+    return out[0, q_len:].tolist()
+
+
 def test_cache_layer_reports_prefix_plus_tail():
     cache = ab.compressed_prefix_cache(300, 2)
     assert cache.get_seq_length() == 300
@@ -101,6 +113,9 @@ def test_host_logic_matches_model_attention_cpu():
     with torch.no_grad():
         past = model(doc, use_cache=True).past_key_values
     ref = run_question(model, past, question, steps=3)
+    with torch.no_grad():
+        past = model(doc, use_cache=True).past_key_values
+    ref_tokens = generate_like_reference(model, past, question, 77, steps=5)
 
     with torch.no_grad():
         past = model(doc, use_cache=True).past_key_values
@@ -134,12 +149,14 @@ def test_host_logic_matches_model_attention_cpu():
     AttentionInterface.register(ab.ATTENTION_NAME, on_cpu)
     try:
         got = run_question(model, ab.compressed_prefix_cache(77, 2), question, steps=3)
+        got_tokens = generate_like_reference(model, ab.compressed_prefix_cache(77, 2), question, 77, steps=5)
     finally:
         AttentionInterface.register(ab.ATTENTION_NAME, real)
         ab.uninstall(model)
     for r, o in zip(ref, got):
         assert (r - o).abs().max() < 2e-2 * r.abs().max()
         assert r.argmax() == o.argmax()
+    assert got_tokens == ref_tokens and len(ref_tokens) == 5  # model.generate drives the cache layer too
 
 
 def test_unattached_layer_raises():
@@ -168,13 +185,25 @@ def test_model_logits_match_dequantised_cache(tmp_path):
     cache, n = store.build_dynamic_cache("doc", 2, "turbo_mse", (2, 128))
     assert n == 300
     ref = run_question(model, cache, question, steps=4)
+    cache, _ = store.build_dynamic_cache("doc", 2, "turbo_mse", (2, 128))
+    ref_tokens = generate_like_reference(model, cache, question, 300, steps=6)
     # this module: the pages stay compressed
-    pools = [store.load_document("doc", l, "turbo_mse", (2, 128))[0] for l in range(2)]
-    cache = ab.install(model, pools, 300, store.tq)
+    cache, n2 = store.attach_to_model(model, "doc", 2, (2, 128))
+    assert n2 == 300
     try:
         got = run_question(model, cache, question, steps=4)
+        got_tokens = generate_like_reference(model, ab.compressed_prefix_cache(300, 2), question, 300, steps=6)
     finally:
         ab.uninstall(model)
     assert store.tq.mse_prefill_status() == 0
+    assert got_tokens == ref_tokens, (got_tokens, ref_tokens)
+    # the same document from the one-file container
+    store.export_container("doc", 2, "turbo_mse", (2, 128))
+    cache, _ = store.attach_to_model(model, "doc", 2, (2, 128))
+    try:
+        again = run_question(model, cache, question, steps=1)
+    finally:
+        ab.uninstall(model)
+    assert torch.equal(again[0], got[0]) and torch.equal(again[1], got[1])
     for r, o in zip(ref, got):
         assert (r - o).abs().max() < 2e-2 * r.abs().max(), (r - o).abs().max() / r.abs().max()
