@@ -150,6 +150,11 @@ def test_host_logic_matches_model_attention_cpu():
     try:
         got = run_question(model, ab.compressed_prefix_cache(77, 2), question, steps=3)
         got_tokens = generate_like_reference(model, ab.compressed_prefix_cache(77, 2), question, 77, steps=5)
+        # the question in two chunks: the second one meets an older fp16 tail
+        cache2 = ab.compressed_prefix_cache(77, 2)
+        with torch.no_grad():
+            model(question[:, :5], past_key_values=cache2, use_cache=True)
+            two_chunks = model(question[:, 5:], past_key_values=cache2, use_cache=True).logits[0, -1].float()
     finally:
         AttentionInterface.register(ab.ATTENTION_NAME, real)
         ab.uninstall(model)
@@ -157,6 +162,7 @@ def test_host_logic_matches_model_attention_cpu():
         assert (r - o).abs().max() < 2e-2 * r.abs().max()
         assert r.argmax() == o.argmax()
     assert got_tokens == ref_tokens and len(ref_tokens) == 5  # model.generate drives the cache layer too
+    assert (two_chunks - ref[0]).abs().max() < 2e-2 * ref[0].abs().max()
 
 
 def test_unattached_layer_raises():
@@ -165,7 +171,8 @@ def test_unattached_layer_raises():
 
 
 @pytest.mark.gpu
-def test_model_logits_match_dequantised_cache(tmp_path):
+@pytest.mark.parametrize("scheme", ["turbo_mse", "turbo_prod"])
+def test_model_logits_match_dequantised_cache(tmp_path, scheme):
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     from turborag_b200.store import CAGStore
@@ -180,15 +187,15 @@ def test_model_logits_match_dequantised_cache(tmp_path):
     for l in range(2):
         k, v = layer_kv(past, l)
         store.pack_document("doc", l, k[0].permute(1, 0, 2).contiguous(), v[0].permute(1, 0, 2).contiguous(),
-                            "turbo_mse")
+                            scheme)
     # the reference's flow: stored pages -> fp16 DynamicCache -> the model's own attention
-    cache, n = store.build_dynamic_cache("doc", 2, "turbo_mse", (2, 128))
+    cache, n = store.build_dynamic_cache("doc", 2, scheme, (2, 128))
     assert n == 300
     ref = run_question(model, cache, question, steps=4)
-    cache, _ = store.build_dynamic_cache("doc", 2, "turbo_mse", (2, 128))
+    cache, _ = store.build_dynamic_cache("doc", 2, scheme, (2, 128))
     ref_tokens = generate_like_reference(model, cache, question, 300, steps=6)
     # this module: the pages stay compressed
-    cache, n2 = store.attach_to_model(model, "doc", 2, (2, 128))
+    cache, n2 = store.attach_to_model(model, "doc", 2, (2, 128), scheme)
     assert n2 == 300
     try:
         got = run_question(model, cache, question, steps=4)
@@ -198,8 +205,8 @@ def test_model_logits_match_dequantised_cache(tmp_path):
     assert store.tq.mse_prefill_status() == 0
     assert got_tokens == ref_tokens, (got_tokens, ref_tokens)
     # the same document from the one-file container
-    store.export_container("doc", 2, "turbo_mse", (2, 128))
-    cache, _ = store.attach_to_model(model, "doc", 2, (2, 128))
+    store.export_container("doc", 2, scheme, (2, 128))
+    cache, _ = store.attach_to_model(model, "doc", 2, (2, 128), scheme)
     try:
         again = run_question(model, cache, question, steps=1)
     finally:

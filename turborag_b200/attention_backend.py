@@ -6,10 +6,12 @@ the model's attention reads 16 bits per element again.  This module keeps the do
 turbo_mse pages as the KV cache of the prefix and registers an attention function with
 ``transformers.AttentionInterface`` that reads those pages directly:
 
-* the question chunk (``Sq`` new tokens, causal inside the chunk) goes through
-  ``tq_mse_prefill_paged`` -- prefix pages decoded on the fly, chunk K/V in fp16;
-* every generated token goes through ``tq_decode_paged`` over the prefix (a split-KV record)
-  and an fp16 pass over the short tail of new tokens, merged by their log-sum-exp weights.
+* a turbo_mse document's question chunk (``Sq`` new tokens, causal inside the chunk) goes
+  through ``tq_mse_prefill_paged`` -- prefix pages decoded on the fly, chunk K/V in fp16;
+* everything else -- a turbo_prod document's question chunk, every generated token, a later
+  chunk -- goes through ``tq_decode_paged`` over the prefix (split-KV records, the new tokens x
+  query heads laid out as the GQA group of their kv head) and a causal fp32 pass over the short
+  fp16 tail of new tokens, merged by their log-sum-exp weights.
 
 Pieces:
   ``CompressedPrefixLayer``  cache layer: reports prefix + tail as its length (positions, masks),
@@ -37,8 +39,8 @@ PARTIAL_STRIDE = 130
 
 @dataclass
 class LayerPrefix:
-    """One layer's stored document: turbo_mse pages with identity slots (page p holds tokens
-    16 p .. 16 p + 15, the order ``CAGStore.pack_document`` writes)."""
+    """One layer's stored document: turbo_prod or turbo_mse pages with identity slots (page p
+    holds tokens 16 p .. 16 p + 15, the order ``CAGStore.pack_document`` writes)."""
     pool: torch.Tensor          # uint8 [pages * page_size_bytes]
     num_tokens: int
     block_table: torch.Tensor   # int32 [1, pages]
@@ -48,8 +50,8 @@ class LayerPrefix:
 class _Runtime:
     """What the attention function needs besides its arguments (one per installed model)."""
 
-    def __init__(self, tq: TurboQuantWrapper, cfg: TQConfig, layout) -> None:
-        self.tq, self.cfg, self.layout = tq, cfg, layout
+    def __init__(self, tq: TurboQuantWrapper, cfg: TQConfig, layout, scheme: str = "turbo_mse") -> None:
+        self.tq, self.cfg, self.layout, self.scheme = tq, cfg, layout, scheme
 
 
 def _layer_base():
@@ -89,11 +91,14 @@ def _attention_modules(model):
     return mods
 
 
-def install(model, pools: list[torch.Tensor], num_tokens: int, tq: TurboQuantWrapper | None = None):
-    """Attach a stored document (``pools[l]`` = layer l's turbo_mse pool as loaded by
-    ``CAGStore.load_document``) to ``model`` and route its attention through this module.
+def install(model, pools: list[torch.Tensor], num_tokens: int, tq: TurboQuantWrapper | None = None,
+            scheme: str = "turbo_mse"):
+    """Attach a stored document (``pools[l]`` = layer l's turbo_mse or turbo_prod pool as loaded
+    by ``CAGStore.load_document``) to ``model`` and route its attention through this module.
     Returns the cache to pass as ``past_key_values``."""
     register()
+    if scheme not in ("turbo_mse", "turbo_prod"):
+        raise ValueError("compressed-prefix attention serves turbo_mse and turbo_prod documents")
     tq = tq or TurboQuantWrapper()
     mods = _attention_modules(model)
     if len(mods) != len(pools):
@@ -104,12 +109,12 @@ def install(model, pools: list[torch.Tensor], num_tokens: int, tq: TurboQuantWra
         raise ValueError("the compressed attention path needs head_dim 128")
     cfg = tq.default_config()
     cfg.num_kv_heads, cfg.head_dim = num_kv, head_dim
-    layout = tq.make_mse_layout_for(cfg)
-    rt = _Runtime(tq, cfg, layout)
+    layout = tq.layout_for_scheme(scheme, cfg)
+    rt = _Runtime(tq, cfg, layout, scheme)
     pages = (num_tokens + cfg.block_size - 1) // cfg.block_size
     for m, pool in zip(mods, pools):
         if not pool.is_cuda or pool.dtype != torch.uint8 or pool.numel() != pages * layout.page_size_bytes:
-            raise ValueError("pool is not a device-resident turbo_mse pool of this document")
+            raise ValueError(f"pool is not a device-resident {scheme} pool of this document")
         if abs(m.scaling - 1.0 / math.sqrt(head_dim)) > 1e-9:
             raise ValueError("softmax scale differs from 1 / sqrt(head_dim)")
         dev = pool.device
@@ -130,20 +135,44 @@ def uninstall(model, attn_implementation: str = "eager") -> None:
 
 
 def _tail_attention(query, key, value, scaling: float):
-    """fp32 attention of one query token over the fp16 tail; returns (out [Hq, D], lse [Hq])."""
-    hq, hkv = query.shape[0], key.shape[0]
+    """Causal fp32 attention of the last ``Sq`` positions over the fp16 tail: ``query``
+    [Hq, Sq, D], ``key`` / ``value`` [Hkv, T, D] with the queries at tail positions T - Sq .. T - 1.
+    Returns (out [Hq, Sq, D], lse [Hq, Sq])."""
+    hq, sq, _ = query.shape
+    hkv, t, _ = key.shape
     g = hq // hkv
-    q = query.float().view(hkv, g, -1)
-    s = torch.matmul(q, key.float().transpose(1, 2)) * scaling        # [Hkv, G, T]
+    q = query.float().reshape(hkv, g * sq, -1)
+    s = torch.matmul(q, key.float().transpose(1, 2)).view(hkv, g, sq, t) * scaling
+    if sq > 1:
+        pos = torch.arange(t - sq, t, device=query.device).view(sq, 1)
+        s = s.masked_fill(torch.arange(t, device=query.device).view(1, t) > pos, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
-    o = torch.matmul(torch.exp(s - lse.unsqueeze(-1)), value.float())  # [Hkv, G, D]
-    return o.view(hq, -1), lse.view(hq)
+    o = torch.matmul(torch.exp(s - lse.unsqueeze(-1)).view(hkv, g * sq, t), value.float())
+    return o.reshape(hq, sq, -1), lse.reshape(hq, sq)
+
+
+def _prefix_attention(rt: _Runtime, prefix: LayerPrefix, query, stream: int):
+    """Attention of every (new token, query head) over the compressed pages alone: the Sq x G rows
+    of a kv head form its GQA group in one paged decode.  ``query`` [Hq, Sq, D] fp16.  Returns
+    (out [Hq, Sq, D] fp32, lse [Hq, Sq]) from the split-KV records."""
+    hq, sq, d = query.shape
+    hkv = rt.cfg.num_kv_heads
+    g = hq // hkv
+    rows = query.reshape(hkv, g * sq, d).reshape(1, hkv * g * sq, d).contiguous()  # row h * (G Sq) + (g, s)
+    rec = torch.empty(1, rows.shape[1], PARTIAL_STRIDE, dtype=torch.float32, device=query.device)
+    rt.tq.decode_paged(rt.scheme, rows, prefix.pool, prefix.block_table, prefix.seq_lens, rt.layout, rt.cfg,
+                       partials_out=rec, stream=stream)
+    out = torch.empty(rows.shape[1], d, dtype=torch.float16, device=query.device)
+    rt.tq.merge_partials(rec.view(1, rows.shape[1], PARTIAL_STRIDE), out, rows.shape[1], hkv, stream=stream)
+    lse = rec[0, :, 128] + torch.log(rec[0, :, 129])
+    return out.float().view(hq, sq, d), lse.view(hq, sq)
 
 
 def turborag_mse_attention(module, query, key, value, attention_mask=None, dropout: float = 0.0,
                            scaling: float | None = None, sliding_window=None, **kwargs):
     """``AttentionInterface`` function: ``query`` [1, Hq, Sq, 128], ``key`` / ``value`` the fp16
-    tail the cache layer returned [1, Hkv, T, 128].  Returns ([1, Sq, Hq, 128], None)."""
+    tail the cache layer returned [1, Hkv, T, 128] (it ends with the Sq new tokens).  Returns
+    ([1, Sq, Hq, 128], None)."""
     prefix: LayerPrefix | None = getattr(module, "_tq_prefix", None)
     rt: _Runtime | None = getattr(module, "_tq_runtime", None)
     if prefix is None or rt is None:
@@ -156,9 +185,11 @@ def turborag_mse_attention(module, query, key, value, attention_mask=None, dropo
         raise ValueError("softmax scale differs from 1 / sqrt(head_dim)")
     _, hq, sq, d = query.shape
     tail = key.shape[2]
+    if tail < sq:
+        raise ValueError("the cache layer returned fewer tail positions than new tokens")
     tq, cfg, layout = rt.tq, rt.cfg, rt.layout
     stream = torch.cuda.current_stream(query.device).cuda_stream
-    if sq == tail:
+    if sq == tail and getattr(rt, "scheme", "turbo_mse") == "turbo_mse":
         # the question chunk: causal inside the chunk, every chunk token sees the whole prefix
         q = query.transpose(1, 2).contiguous()                     # [1, Sq, Hq, D]
         ck = key.transpose(1, 2).contiguous()                      # [1, Sq, Hkv, D]
@@ -167,21 +198,12 @@ def turborag_mse_attention(module, query, key, value, attention_mask=None, dropo
         tq.mse_prefill_paged(q, prefix.pool, prefix.block_table, prefix.seq_lens, ck, cv, out,
                              layout, cfg, stream=stream)
         return out, None
-    if sq == 1:
-        # one generated token: split-KV record over the pages, fp16 pass over the tail
-        q = query[:, :, 0, :].contiguous()                         # [1, Hq, D]
-        rec = torch.empty(1, hq, PARTIAL_STRIDE, dtype=torch.float32, device=query.device)
-        tq.decode_paged("turbo_mse", q, prefix.pool, prefix.block_table, prefix.seq_lens, layout, cfg,
-                        partials_out=rec, stream=stream)
-        o_p = torch.empty(hq, d, dtype=torch.float16, device=query.device)
-        tq.merge_partials(rec.view(1, hq, PARTIAL_STRIDE), o_p, hq, cfg.num_kv_heads, stream=stream)
-        lse_p = rec[0, :, 128] + torch.log(rec[0, :, 129])
-        o_t, lse_t = _tail_attention(q[0], key[0], value[0], 1.0 / math.sqrt(d))
-        w_p = torch.sigmoid(lse_p - lse_t).unsqueeze(-1)
-        out = (w_p * o_p.float() + (1.0 - w_p) * o_t).to(torch.float16)
-        return out.view(1, 1, hq, d), None
-    raise NotImplementedError("a chunk after the first one (Sq > 1 with an older tail) is not supported: "
-                              "run the question as one chunk, then decode token by token")
+    # split-KV records over the pages, causal fp32 pass over the fp16 tail, log-sum-exp merge
+    o_p, lse_p = _prefix_attention(rt, prefix, query[0].contiguous(), stream)
+    o_t, lse_t = _tail_attention(query[0], key[0], value[0], 1.0 / math.sqrt(d))
+    w_p = torch.sigmoid(lse_p - lse_t).unsqueeze(-1)
+    out = (w_p * o_p + (1.0 - w_p) * o_t).to(torch.float16)          # [Hq, Sq, D]
+    return out.transpose(0, 1).unsqueeze(0).contiguous(), None
 
 
 _registered = False

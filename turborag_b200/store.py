@@ -521,22 +521,24 @@ class CAGStore:
             cache.update(k, v, l)
         return cache, doc_len
 
-    def attach_to_model(self, model, doc_id: str, num_layers: int, head_shape: tuple[int, int] = (2, 128)):
-        """Serve a stored turbo_mse document to a Hugging Face model WITHOUT dequantising it: loads the
-        compressed pools (from the one-file container when there is one, else from the per-layer
-        files), hangs them on the model's attention layers and returns ``(cache, doc_num_tokens)``;
-        pass ``cache`` as ``past_key_values`` (see ``turborag_b200/attention_backend.py``).  The
-        counterpart of ``build_dynamic_cache`` for a model whose attention reads the pages directly."""
+    def attach_to_model(self, model, doc_id: str, num_layers: int, head_shape: tuple[int, int] = (2, 128),
+                        scheme: Scheme = "turbo_mse"):
+        """Serve a stored turbo_mse / turbo_prod document to a Hugging Face model WITHOUT dequantising
+        it: loads the compressed pools (from the one-file container when there is one, else from the
+        per-layer files), hangs them on the model's attention layers and returns
+        ``(cache, doc_num_tokens)``; pass ``cache`` as ``past_key_values`` (see
+        ``turborag_b200/attention_backend.py``).  The counterpart of ``build_dynamic_cache`` for a
+        model whose attention reads the pages directly."""
         from . import attention_backend
-        if self.container_path(doc_id, "turbo_mse").exists():
-            loaded, n = self.load_container_pools(doc_id, "turbo_mse", head_shape)
+        if self.container_path(doc_id, scheme).exists():
+            loaded, n = self.load_container_pools(doc_id, scheme, head_shape)
             pools = [pool for _, pool in loaded]
         else:
             pools, n = [], 0
             for l in range(num_layers):
-                pool, _, n = self.load_document(doc_id, l, "turbo_mse", head_shape)
+                pool, _, n = self.load_document(doc_id, l, scheme, head_shape)
                 pools.append(pool)
-        return attention_backend.install(model, pools, n, self.tq), n
+        return attention_backend.install(model, pools, n, self.tq, scheme), n
 
     # ---- attention over stored pages ------------------------------------------------------------
     def fused_attention(self, query: torch.Tensor, pool, slots: torch.Tensor, N: int, scheme: Scheme,
