@@ -60,8 +60,8 @@ template <int S>
 __global__ void __launch_bounds__(kDqWarps * 32)
 dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restrict__ slot_mapping,
                   __half* __restrict__ out_key, __half* __restrict__ out_value, PageGeom geo,
-                  int head_dim, long long num_rows, long long num_tokens, int hnd,
-                  int pool_aligned8) {
+                  IndexDiv div_heads, IndexDiv div_block, int head_dim, long long num_rows,
+                  long long num_tokens, int hnd, int pool_aligned8) {
     __shared__ __align__(16) float xchg[kDqWarps][kXchgWarpFloats];
     __shared__ float lut3[8 * 32];
     __shared__ float lut4[16 * 32];
@@ -92,10 +92,10 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         const long long row_raw = g * 4 + rr;
         r.valid = row_raw < num_rows;
         const long long row = r.valid ? row_raw : num_rows - 1;
-        const long long tok = row / H;
+        const long long tok = index_div(row, div_heads);
         r.h = static_cast<int>(row - tok * H);
         const int slot = __ldg(slot_mapping + tok);
-        const int blk = slot / geo.block_size;
+        const int blk = index_div(slot, div_block);
         const int tib = slot - blk * geo.block_size;
         const uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
         const unsigned int th = static_cast<unsigned int>(tib * H + r.h);
@@ -164,15 +164,18 @@ void launch_dequant(int scheme, const uint8_t* pool, const int32_t* slots, void*
     if (scheme == TQ_SCHEME_TURBO_PROD)
         dequant_kv_kernel<0><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
             pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
+            num_tokens, hnd ? 1 : 0, aligned);
     else if (scheme == TQ_SCHEME_TURBO_MSE)
         dequant_kv_kernel<1><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
             pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
+            num_tokens, hnd ? 1 : 0, aligned);
     else
         dequant_kv_kernel<2><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
             pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            head_dim, rows, num_tokens, hnd ? 1 : 0, aligned);
+            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
+            num_tokens, hnd ? 1 : 0, aligned);
     check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod dequant_kv"
                  : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse dequant_kv" : "qjl dequant_kv");
 }

@@ -25,24 +25,27 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 // The reference scans the levels for the smallest distance (first index wins ties).  That is
 // the same as counting the decision thresholds that are <= x, where the thresholds are exact
 // fp32 numbers: M_j on the positive side, TMID at the centre and, on the negative side, the
-// float just above -N_j (there the scan moves up for x > -N_j).  x * 16/3 + magic rounds x to
-// a cell of width 3/16 in the low mantissa bits; thresholds are further apart than that, so a
-// cell holds at most one.  A table row per cell gives (threshold in the cell or +inf, number
-// of thresholds below the cell): code = base + (x >= threshold) -- one fma, two integer ops,
+// float just above -N_j (there the scan moves up for x > -N_j).  x * 16/3 + magic maps x to
+// a cell of width 3/16 (any monotonic map would do); thresholds are further apart than that,
+// so a cell holds at most one.  The magic constant's exponent puts the cell number at mantissa
+// bits 7.. , which is the byte offset of a 128-byte table row: the row address is one and-or of
+// the fma's result.  A table row per cell gives (threshold in the cell or +inf, number
+// of thresholds below the cell): code = base + (x >= threshold) -- one fma, one logic op,
 // one load, one compare, one add, and no sign handling.  Rows are 128 bytes of replicas: 16
 // x 8 bytes for the 4-bit table (the two half-warps of a 64-bit load are separate wavefronts),
 // 8 x 16 bytes for the 3-bit table, so no lookup ever conflicts.
 constexpr float kCellScale = 16.0f / 3.0f;
 constexpr int kCellsV = 128, kCellsK = 32;          // |x| <= sqrt(128) -> |cell| <= 61; K is clamped to 2.5
-constexpr float kMagicV = 8388608.0f + 64.0f;       // low 7 mantissa bits = cell + 64
-constexpr float kMagicK = 8388608.0f + 16.0f;       // low 5 mantissa bits = cell + 16
+constexpr float kMagicV = 65536.0f + 64.5f;         // ulp 2^-7: mantissa bits 7..13 = floor(x*16/3 + 64.5)
+constexpr float kMagicK = 65536.0f + 16.5f;         // mantissa bits 7..11 = floor(x*16/3 + 16.5)
 constexpr int kLutRowBytes = 128;
+constexpr uint32_t kRowMaskV = (kCellsV - 1) * kLutRowBytes, kRowMaskK = (kCellsK - 1) * kLutRowBytes;
 
 __device__ __forceinline__ uint32_t cell_v(float x) {
-    return __float_as_uint(__fmaf_rn(x, kCellScale, kMagicV)) & (kCellsV - 1);
+    return (__float_as_uint(__fmaf_rn(x, kCellScale, kMagicV)) & kRowMaskV) / kLutRowBytes;
 }
 __device__ __forceinline__ uint32_t cell_k(float x) {
-    return __float_as_uint(__fmaf_rn(x, kCellScale, kMagicK)) & (kCellsK - 1);
+    return (__float_as_uint(__fmaf_rn(x, kCellScale, kMagicK)) & kRowMaskK) / kLutRowBytes;
 }
 __device__ __forceinline__ float next_up_of_negated(float n) {  // smallest float above -n, n > 0
     return -__uint_as_float(__float_as_uint(n) - 1u);
@@ -97,7 +100,7 @@ __device__ void build_luts(uint8_t* lutK, uint8_t* lutV, bool need_k) {
 // `rep` = (lane % 16) * 8, this lane's replica inside a row.
 __device__ __forceinline__ uint32_t quant_v4_lut(float x, const uint8_t* lutV, uint32_t rep) {
     const uint32_t u = __float_as_uint(__fmaf_rn(x, kCellScale, kMagicV));
-    const float2 e = *reinterpret_cast<const float2*>(lutV + (((u << 7) & ((kCellsV - 1) << 7)) | rep));
+    const float2 e = *reinterpret_cast<const float2*>(lutV + ((u & kRowMaskV) | rep));
     return __float_as_uint(e.y) + (x >= e.x ? 1u : 0u);
 }
 
@@ -106,18 +109,20 @@ __device__ __forceinline__ uint32_t quant_v4_lut(float x, const uint8_t* lutV, u
 __device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK, uint32_t rep, float& e) {
     const float xc = fminf(fmaxf(kn, -2.5f), 2.5f);
     const uint32_t u = __float_as_uint(__fmaf_rn(xc, kCellScale, kMagicK));
-    const float4 t = *reinterpret_cast<const float4*>(lutK + (((u << 7) & ((kCellsK - 1) << 7)) | rep));
+    const float4 t = *reinterpret_cast<const float4*>(lutK + ((u & kRowMaskK) | rep));
     const bool above = xc >= t.x;
     e = __fsub_rn(xc, above ? t.z : t.y);
     return (__float_as_uint(t.w) + (above ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
 }
 
-// Squares that feed the reference's summation tree.  They are scalar multiplies on purpose: the
-// assembler contracts a packed mul.rn.f32x2 into the packed add that consumes it (observed: the
-// first tree level came out as fma(x, x, y*y)), which changes the sum in its last bit for about
-// half of the rows; the scalar mul.rn.f32 is never contracted.
-__device__ __forceinline__ float2 square2(const float2& v) {
-    return make_float2(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y));
+// Squares that feed the reference's summation tree.  A packed mul.rn.f32x2 whose only consumer
+// is a packed add gets contracted by the assembler (observed: the first tree level came out as
+// fma(x, x, y*y)), which changes the sum in its last bit for about half of the rows.  A packed
+// fma with a zero addend rounds the same product once (x*x + 0 == RN(x*x)), is a single
+// instruction for two squares, and an fma feeding an add is never contracted.  The zero is a
+// kernel argument so that the fma cannot be simplified back into a multiply at compile time.
+__device__ __forceinline__ float2 square2(const float2& v, const float2& zero) {
+    return fma2(v, v, zero);
 }
 
 // Move a row's 64 code bytes from "lane l' holds byte l'+8j" to "lane l holds
@@ -148,7 +153,8 @@ template <int S>
 __global__ void __launch_bounds__(kPackWarps * 32)
 pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
-               PageGeom geo, int head_dim, long long num_rows, int pool_aligned8) {
+               PageGeom geo, IndexDiv div_heads, IndexDiv div_block, int head_dim,
+               long long num_rows, int pool_aligned8, float zero) {
     constexpr bool PROD = S == 0, QJL = S == 2;
     constexpr bool TREE128 = PROD || QJL;  // sum of squares: 128-leaf tree (prod, QJL) or 64 pair leaves (mse)
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
@@ -163,6 +169,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
     uint8_t* code_buf = reinterpret_cast<uint8_t*>(buf);
     const int H = geo.num_kv_heads;
     const float c = inv_sqrt_dim(head_dim);
+    const float2 zero2 = make_float2(zero, zero);
     const long long groups = (num_rows + 3) >> 2;
     const long long warps_total = static_cast<long long>(gridDim.x) * kPackWarps;
 
@@ -171,7 +178,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         const long long row_raw = g * 4 + rr;
         const bool valid = row_raw < num_rows;
         const long long row = valid ? row_raw : num_rows - 1;  // keep all lanes converged
-        const long long tok = row / H;
+        const long long tok = index_div(row, div_heads);
         const int h = static_cast<int>(row - tok * H);
         // odd heads: the whole rotated row is negated; the QJL sign hash has no head term
         // (tq_qjl_kernels.cu:18-21)
@@ -183,7 +190,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         const uint4 v_lo = ld_stream(vp), v_hi = ld_stream(vp + 1);
         const int slot = __ldg(slot_mapping + tok);
 
-        const int blk = slot / geo.block_size;
+        const int blk = index_div(slot, div_block);
         const int tib = slot - blk * geo.block_size;
         uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
         const unsigned int th = static_cast<unsigned int>(tib * H + h);
@@ -202,7 +209,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         if (QJL) {
             float2 sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j], zero2);
             const float krms = rms_from_sum(tree128(sq));
             // bit = (k / krms >= 0) (tq_qjl_kernels.cu:155): krms > 0 and the quotient of a rotated
             // fp16 row cannot underflow, so this is the sign of k itself (-0 counts as >= 0)
@@ -237,7 +244,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         } else if (PROD) {
             float2 sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j], zero2);
             const float krms = rms_from_sum(tree128(sq));
             const float kr = __frcp_rn(krms);
             float2 e2[8];
@@ -248,7 +255,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 const uint32_t n0 = quant_k3_lut(kn.x, lutK, rep_k, e0);
                 const uint32_t n1 = quant_k3_lut(kn.y, lutK, rep_k, e1);
                 kbytes[j] = n0 | (n1 << 4);
-                e2[j] = square2(make_float2(e0, e1));
+                e2[j] = square2(make_float2(e0, e1), zero2);
             }
             const float rms_e = rms_from_sum(tree128(e2));
             if (valid && l == 0) {
@@ -284,7 +291,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         if (TREE128) {
             float2 sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j]);
+            for (int j = 0; j < 8; ++j) sq[j] = square2(y[j], zero2);
             vrms = rms_from_sum(tree128(sq));
         } else {
             float pr[8];
@@ -322,7 +329,7 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
 #define TQ_PACK_LAUNCH(SV)                                                                     \
     pack_kv_kernel<SV><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
         static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,    \
-        head_dim, rows, aligned)
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, aligned, 0.0f)
     if (scheme == TQ_SCHEME_TURBO_PROD) TQ_PACK_LAUNCH(0);
     else if (scheme == TQ_SCHEME_TURBO_MSE) TQ_PACK_LAUNCH(1);
     else TQ_PACK_LAUNCH(2);
