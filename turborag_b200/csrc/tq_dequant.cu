@@ -55,13 +55,15 @@ __device__ __forceinline__ void inverse_and_store(float2 (&x)[8], float* buf, in
     }
 }
 
-// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit
-template <int S>
+// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit.  ALIGNED8: pool base and page size are multiples of
+// 8 bytes, so a lane's 8 code bytes are one load.  It is a template argument because as a run-time
+// flag both load sequences end up in the instruction stream, predicated.
+template <int S, bool ALIGNED8>
 __global__ void __launch_bounds__(kDqWarps * 32)
 dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restrict__ slot_mapping,
                   __half* __restrict__ out_key, __half* __restrict__ out_value, PageGeom geo,
                   IndexDiv div_heads, IndexDiv div_block, int head_dim, long long num_rows,
-                  long long num_tokens, int hnd, int pool_aligned8) {
+                  long long num_tokens, int hnd) {
     __shared__ __align__(16) float xchg[kDqWarps][kXchgWarpFloats];
     __shared__ float lut3[8 * 32];
     __shared__ float lut4[16 * 32];
@@ -77,7 +79,7 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
     const float c = inv_sqrt_dim(head_dim);
     const long long groups = (num_rows + 3) >> 2;
     const long long warps_total = static_cast<long long>(gridDim.x) * kDqWarps;
-    const bool al = pool_aligned8 != 0;
+    constexpr bool al = ALIGNED8;
 
     // Packed inputs of one row group for this lane; the next group's are fetched before the
     // current one is expanded so that the dependent slot -> page -> code loads stay hidden.
@@ -160,22 +162,16 @@ void launch_dequant(int scheme, const uint8_t* pool, const int32_t* slots, void*
     long long blocks = (groups + kDqWarps - 1) / kDqWarps;
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
-    const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
-    if (scheme == TQ_SCHEME_TURBO_PROD)
-        dequant_kv_kernel<0><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
-            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
-            num_tokens, hnd ? 1 : 0, aligned);
-    else if (scheme == TQ_SCHEME_TURBO_MSE)
-        dequant_kv_kernel<1><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
-            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
-            num_tokens, hnd ? 1 : 0, aligned);
-    else
-        dequant_kv_kernel<2><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(
-            pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,
-            make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,
-            num_tokens, hnd ? 1 : 0, aligned);
+    const bool aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
+#define TQ_DEQUANT_LAUNCH(SV, AL)                                                                 \
+    dequant_kv_kernel<SV, AL><<<static_cast<unsigned>(blocks), kDqWarps * 32, 0, stream>>>(         \
+        pool, slots, static_cast<__half*>(out_key), static_cast<__half*>(out_value), geo,          \
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows,          \
+        num_tokens, hnd ? 1 : 0)
+    if (scheme == TQ_SCHEME_TURBO_PROD) { if (aligned) TQ_DEQUANT_LAUNCH(0, true); else TQ_DEQUANT_LAUNCH(0, false); }
+    else if (scheme == TQ_SCHEME_TURBO_MSE) { if (aligned) TQ_DEQUANT_LAUNCH(1, true); else TQ_DEQUANT_LAUNCH(1, false); }
+    else { if (aligned) TQ_DEQUANT_LAUNCH(2, true); else TQ_DEQUANT_LAUNCH(2, false); }
+#undef TQ_DEQUANT_LAUNCH
     check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod dequant_kv"
                  : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse dequant_kv" : "qjl dequant_kv");
 }

@@ -148,13 +148,15 @@ __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t
     }
 }
 
-// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit
-template <int S>
+// S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit.  ALIGNED8: pool base and page size are multiples of
+// 8 bytes (code rows leave as 8-byte stores); a template argument so that the byte-store sequence
+// of the other case is not part of this kernel's instruction stream.
+template <int S, bool ALIGNED8>
 __global__ void __launch_bounds__(kPackWarps * 32)
 pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, IndexDiv div_heads, IndexDiv div_block, int head_dim,
-               long long num_rows, int pool_aligned8, float zero) {
+               long long num_rows, float zero) {
     constexpr bool PROD = S == 0, QJL = S == 2;
     constexpr bool TREE128 = PROD || QJL;  // sum of squares: 128-leaf tree (prod, QJL) or 64 pair leaves (mse)
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
@@ -231,7 +233,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 const uint4 bits = make_uint4(__byte_perm(w0, o0, 0x5140), __byte_perm(w0, o0, 0x7362),
                                               __byte_perm(w1, o1, 0x5140), __byte_perm(w1, o1, 0x7362));
                 uint8_t* dst = page + geo.k_codes + th * 16;
-                if (pool_aligned8) {
+                if (ALIGNED8) {
                     reinterpret_cast<uint2*>(dst)[0] = make_uint2(bits.x, bits.y);
                     reinterpret_cast<uint2*>(dst)[1] = make_uint2(bits.z, bits.w);
                 } else {
@@ -279,7 +281,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         }
         if (!QJL)
             store_codes(kbytes, code_buf, page + geo.k_codes + th * 64, lane, valid,
-                        pool_aligned8 != 0);
+                        ALIGNED8);
 
         // ---------------- V ----------------
         fwht_phase1_from_half(v_lo, v_hi, x);
@@ -310,7 +312,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
         if (valid && l == 0)
             *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
         store_codes(vbytes, code_buf, page + geo.v_codes + th * 64, lane, valid,
-                    pool_aligned8 != 0);
+                    ALIGNED8);
     }
 }
 
@@ -325,15 +327,17 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
     long long blocks = (groups + kPackWarps - 1) / kPackWarps;
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
-    const int aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
-#define TQ_PACK_LAUNCH(SV)                                                                     \
-    pack_kv_kernel<SV><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
+    const bool aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
+#define TQ_PACK_LAUNCH1(SV, AL)                                                                \
+    pack_kv_kernel<SV, AL><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
         static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,    \
-        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, aligned, 0.0f)
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f)
+#define TQ_PACK_LAUNCH(SV) do { if (aligned) TQ_PACK_LAUNCH1(SV, true); else TQ_PACK_LAUNCH1(SV, false); } while (0)
     if (scheme == TQ_SCHEME_TURBO_PROD) TQ_PACK_LAUNCH(0);
     else if (scheme == TQ_SCHEME_TURBO_MSE) TQ_PACK_LAUNCH(1);
     else TQ_PACK_LAUNCH(2);
 #undef TQ_PACK_LAUNCH
+#undef TQ_PACK_LAUNCH1
     check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod pack_kv"
                  : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse pack_kv" : "qjl pack_kv");
 }
