@@ -30,6 +30,35 @@
 namespace tq {
 namespace {
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// The paged decode kernel and the merge kernel are launched with the programmatic stream
+// serialisation attribute: each lets the next kernel in the stream start while it is still
+// running (pdl_launch_dependents at its top) and waits for everything before it in the stream
+// to complete (pdl_wait) before it reads an input or writes an output.  What overlaps is only
+// work that depends on nothing -- the next decode launch's operand-table build and block
+// scheduling run under this launch's tail and merge instead of after them.  Both instructions
+// do nothing in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+void launch_after_wait(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                       cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    check_cuda(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), "cudaLaunchKernelEx");
+}
+
 constexpr int kMaxHeads = 8;          // kv heads per CTA
 constexpr int kWarpSmemBytes = 4608;  // per-warp merge record: 36 floats x 32 lanes
 constexpr float kLog2e = 1.4426950408889634f;
@@ -874,8 +903,10 @@ __global__ void __launch_bounds__(kFastGroups * kFastGroupWarps * 32, 1)
 decode_paged16_kernel(DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kStreams = kFastGroupWarps / H;
-    build_operand_lut(smem_raw);
+    pdl_launch_dependents();
+    build_operand_lut(smem_raw);  // constants only: may run before the previous kernel is done
     __syncthreads();
+    pdl_wait();
     // work items (sequence, split) are numbered sequence-major; a CTA takes two neighbours
     const int group = threadIdx.x / (kFastGroupWarps * 32);
     const int item = blockIdx.x * kFastGroups + group;
@@ -1082,6 +1113,8 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
              int ref_layout, int head_dim, PeerOut peer, int head_sign) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
     if (peer.world > 0) {
         // Publishing variant: the row's merged record goes straight into slot `rank` of every
         // peer's buffer; the last CTA to finish raises this rank's flag on every peer.
@@ -1253,8 +1286,8 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (fast) {
         const dim3 fgrid((a.batch * splits + kFastGroups - 1) / kFastGroups, 1, qgroups);
 #define TQ_FAST_LAUNCH(PRODV, HV)                                                                \
-    decode_paged16_kernel<PRODV, HV><<<fgrid, kFastGroups * kFastGroupWarps * 32,                \
-                                       fast_smem_bytes(PRODV, HV), stream>>>(p)
+    launch_after_wait(decode_paged16_kernel<PRODV, HV>, fgrid, dim3(kFastGroups * kFastGroupWarps * 32), \
+                      fast_smem_bytes(PRODV, HV), stream, p)
         if (prod) {
             if (H == 1) TQ_FAST_LAUNCH(true, 1);
             else if (H == 2) TQ_FAST_LAUNCH(true, 2);
@@ -1279,10 +1312,10 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     // merge the splits of every (sequence, query head) row
     const int rows = a.batch * a.num_q_heads;
     const long long part_stride = static_cast<long long>(a.num_q_heads) * TQ_PARTIAL_STRIDE;
-    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
-        ws, splits, part_stride, part_stride * splits, a.num_q_heads,
-        static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
-        a.ref_query_layout, a.head_dim, a.peer, qjl ? 0 : 1);
+    launch_after_wait(merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream,
+                      static_cast<const float*>(ws), splits, part_stride, part_stride * splits, a.num_q_heads,
+                      static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
+                      a.ref_query_layout, a.head_dim, a.peer, qjl ? 0 : 1);
     check_launch("decode merge");
     if (owned) scratch_free(ws, stream, "scratch_free(decode workspace)");
 }
