@@ -1036,18 +1036,33 @@ decode_paged16_kernel(DecodeParams p) {
     decode_epilogue(p, kFastWarpBytes, ctx, r, st);
 }
 
-// One warp merges the parts of one (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
+// WPR warps merge the parts of one (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
+// With WPR == 1 a warp walks all parts itself (many rows, few parts: the serving shape).  With
+// WPR > 1 the CTA owns one row, warp `sub` takes parts sub, sub + WPR, .. and the warps' maxima
+// and weighted sums meet in `xchg` (WPR * kMergeXchgFloats floats of shared memory) -- one long
+// sequence split hundreds of ways would otherwise be a serial walk of hundreds of records.
+constexpr int kMergeXchgFloats = 132;
+template <int WPR>
 __device__ __forceinline__ void merge_row(const float* __restrict__ partials, int num_parts,
                                           long long part_stride, long long seq_stride, int rows_per_seq,
                                           __half* __restrict__ output, float* __restrict__ partials_out,
                                           int row, int num_q_heads, int num_kv_heads, int ref_layout,
-                                          int head_dim, int lane, const PeerOut* peer, int head_sign = 1) {
+                                          int head_dim, int lane, const PeerOut* peer, int head_sign = 1,
+                                          int sub = 0, float* xchg = nullptr) {
     const int seq = row / rows_per_seq, r = row - seq * rows_per_seq;
     const float* base = partials + seq * seq_stride + static_cast<long long>(r) * TQ_PARTIAL_STRIDE;
     float mmax = kInitMaxLogit;
-    for (int s = 0; s < num_parts; ++s) mmax = fmaxf(mmax, __ldg(base + s * part_stride + 128));
+    for (int s = sub; s < num_parts; s += WPR) mmax = fmaxf(mmax, __ldg(base + s * part_stride + 128));
+    if (WPR > 1) {
+        if (lane == 0) xchg[sub] = mmax;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < WPR; ++w) mmax = fmaxf(mmax, xchg[w]);
+        __syncthreads();  // the maxima are read before the sums overwrite them
+    }
     float acc[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
-    for (int s = 0; s < num_parts; ++s) {
+#pragma unroll 4
+    for (int s = sub; s < num_parts; s += WPR) {
         const float* ps = base + s * part_stride;
         const float w = __expf(__ldg(ps + 128) - mmax);
         l = fmaf(__ldg(ps + 129), w, l);
@@ -1057,6 +1072,23 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ partials, in
         acc[1] = fmaf(v0.y, w, acc[1]);
         acc[2] = fmaf(v1.x, w, acc[2]);
         acc[3] = fmaf(v1.y, w, acc[3]);
+    }
+    if (WPR > 1) {
+        float* mine = xchg + sub * kMergeXchgFloats;
+        *reinterpret_cast<float4*>(mine + 4 * lane) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (lane == 0) mine[128] = l;
+        __syncthreads();
+        if (sub != 0) return;  // warp 0 adds the warps' sums in a fixed order and finishes the row
+        l = xchg[128];
+#pragma unroll
+        for (int w = 1; w < WPR; ++w) {
+            const float4 o = *reinterpret_cast<const float4*>(xchg + w * kMergeXchgFloats + 4 * lane);
+            acc[0] += o.x;
+            acc[1] += o.y;
+            acc[2] += o.z;
+            acc[3] += o.w;
+            l += xchg[w * kMergeXchgFloats + 128];
+        }
     }
     if (partials_out) {
         float* po = partials_out + static_cast<long long>(row) * TQ_PARTIAL_STRIDE;
@@ -1106,20 +1138,25 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ partials, in
 
 // ---- merge: log-sum-exp over parts, normalise, inverse rotation, fp16 store ----
 // One warp per (sequence, query head) row; lane holds dims 4*lane..4*lane+3.
-__global__ void __launch_bounds__(128)
+template <int WPR>
+__global__ void __launch_bounds__(WPR == 1 ? 128 : WPR * 32)
 merge_kernel(const float* __restrict__ partials, int num_parts, long long part_stride,
              long long seq_stride, int rows_per_seq, __half* __restrict__ output,
              float* __restrict__ partials_out, int rows, int num_q_heads, int num_kv_heads,
              int ref_layout, int head_dim, PeerOut peer, int head_sign) {
+    __shared__ __align__(16) float xchg[WPR == 1 ? 4 : WPR * kMergeXchgFloats];
     const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int warp = threadIdx.x >> 5;
+    // WPR == 1: four rows per CTA, a warp each; otherwise the CTA's warps share one row
+    const int row = WPR == 1 ? blockIdx.x * (blockDim.x >> 5) + warp : blockIdx.x;
+    const int sub = WPR == 1 ? 0 : warp;
     pdl_launch_dependents();
     pdl_wait();
     if (peer.world > 0) {
         // Publishing variant: the row's merged record goes straight into slot `rank` of every
         // peer's buffer; the last CTA to finish raises this rank's flag on every peer.
-        if (row < rows) merge_row(partials, num_parts, part_stride, seq_stride, rows_per_seq, nullptr, nullptr,
-                                  row, num_q_heads, num_kv_heads, ref_layout, head_dim, lane, &peer);
+        if (row < rows) merge_row<WPR>(partials, num_parts, part_stride, seq_stride, rows_per_seq, nullptr, nullptr,
+                                       row, num_q_heads, num_kv_heads, ref_layout, head_dim, lane, &peer, 1, sub, xchg);
         __threadfence_system();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -1135,8 +1172,23 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
         return;
     }
     if (row >= rows) return;
-    merge_row(partials, num_parts, part_stride, seq_stride, rows_per_seq, output, partials_out, row,
-              num_q_heads, num_kv_heads, ref_layout, head_dim, lane, nullptr, head_sign);
+    merge_row<WPR>(partials, num_parts, part_stride, seq_stride, rows_per_seq, output, partials_out, row,
+                   num_q_heads, num_kv_heads, ref_layout, head_dim, lane, nullptr, head_sign, sub, xchg);
+}
+
+// Rows with many parts get a CTA of eight warps each, the others a warp each.
+constexpr int kMergeWideParts = 16, kMergeWideWarps = 8;
+template <bool PDL, typename... Args>
+void launch_merge_kernel(int rows, int num_parts, cudaStream_t stream, Args... args) {
+    const bool wide = num_parts >= kMergeWideParts;
+    const dim3 grid(wide ? rows : (rows + 3) / 4), block(wide ? kMergeWideWarps * 32 : 128);
+    if (PDL) {
+        if (wide) launch_after_wait(merge_kernel<kMergeWideWarps>, grid, block, 0, stream, args...);
+        else launch_after_wait(merge_kernel<1>, grid, block, 0, stream, args...);
+    } else {
+        if (wide) merge_kernel<kMergeWideWarps><<<grid, block, 0, stream>>>(args...);
+        else merge_kernel<1><<<grid, block, 0, stream>>>(args...);
+    }
 }
 
 // Dynamic shared memory above 48 KB has to be opted into once per device.
@@ -1190,7 +1242,7 @@ void launch_merge(const float* partials, int num_parts, void* output, float* par
     if (rows <= 0) return;
     // parts laid out [num_parts, rows, 130]
     const long long part_stride = static_cast<long long>(rows) * TQ_PARTIAL_STRIDE;
-    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(
+    launch_merge_kernel<false>(rows, num_parts, stream,
         partials, num_parts, part_stride, static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE,
         num_q_heads, static_cast<__half*>(output), partials_out, rows, num_q_heads, num_kv_heads,
         ref_query_layout, head_dim, PeerOut{}, head_sign);
@@ -1201,9 +1253,9 @@ void launch_merge_splits(const float* partials, int splits, void* output, int ro
                          int num_kv_heads, int head_dim, cudaStream_t stream) {
     if (rows <= 0) return;
     const long long part_stride = static_cast<long long>(num_q_heads) * TQ_PARTIAL_STRIDE;
-    merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(partials, splits, part_stride, part_stride * splits,
-                                                   num_q_heads, static_cast<__half*>(output), nullptr,
-                                                   rows, num_q_heads, num_kv_heads, 0, head_dim, PeerOut{}, 1);
+    launch_merge_kernel<false>(rows, splits, stream, partials, splits, part_stride, part_stride * splits,
+                               num_q_heads, static_cast<__half*>(output), static_cast<float*>(nullptr),
+                               rows, num_q_heads, num_kv_heads, 0, head_dim, PeerOut{}, 1);
     check_launch("merge splits");
 }
 
@@ -1312,7 +1364,7 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     // merge the splits of every (sequence, query head) row
     const int rows = a.batch * a.num_q_heads;
     const long long part_stride = static_cast<long long>(a.num_q_heads) * TQ_PARTIAL_STRIDE;
-    launch_after_wait(merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream,
+    launch_merge_kernel<true>(rows, splits, stream,
                       static_cast<const float*>(ws), splits, part_stride, part_stride * splits, a.num_q_heads,
                       static_cast<__half*>(a.output), a.partials_out, rows, a.num_q_heads, H,
                       a.ref_query_layout, a.head_dim, a.peer, qjl ? 0 : 1);
