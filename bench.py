@@ -118,6 +118,19 @@ def synth_kv(torch, n, h, dev, gen):
 # reference arm: the CPU port on host cores
 # -------------------------------------------------------------------------------------
 
+def host_threads():
+    """Threads the CPU arm may use: the cores this process is allowed on.  The oracle is told the
+    number explicitly -- launchers such as torchrun export OMP_NUM_THREADS=1 to every rank, which
+    would otherwise turn the all-cores baseline into a single-thread one."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    from oracle import oracle as O
+    O.set_threads(n)
+    return n
+
+
 def cpu_decode_sample(num_seqs, kv_tokens, hq, h, seed=0):
     """Build `num_seqs` packed sequences with the oracle and return a closure that runs one
     pass of oracle decode attention over them, plus the bytes it processes."""
@@ -148,7 +161,7 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     num_seqs = max(1, min(args.batch, 8))
     run, nbytes = cpu_decode_sample(num_seqs, args.kv_tokens, args.q_heads, args.kv_heads)
     for _ in range(args.warmup):
@@ -738,7 +751,7 @@ def cpu_baseline_and_parity(torch, tq, args, pools, tables, q_dev, out_dev, lay)
     tab = tables[0].cpu().numpy()
     q = q_dev[0].cpu().numpy()
     got = out_dev[0].cpu().numpy().astype(np.float32)
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     # calibrate on one sequence, then size the sample for roughly 10-20 s of CPU work
     t0 = time.perf_counter()
     O.decode_paged("turbo_prod", q[:1], pool, tab[:1], [N], cfg)
