@@ -505,18 +505,22 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     }
     }
     const bool ok0 = tb + g < t_end, ok1 = tb + g + 8 < t_end;
+    // per-token scaling on packed fp32 pairs (the two query columns of a row are a register pair)
     float lg[4];
-    lg[0] = s1[0] * cur.ks0;
-    lg[1] = s1[1] * cur.ks0;
-    lg[2] = s1[2] * cur.ks1;
-    lg[3] = s1[3] * cur.ks1;
-    if (PROD) {
-        // the sign product shares the 1/alpha-scaled query fragments
-        const float r0 = cur.ks0 * cur.re0 * TQ_ALPHA3, r1 = cur.ks1 * cur.re1 * TQ_ALPHA3;
-        lg[0] = fmaf(s2[0], r0, lg[0]);
-        lg[1] = fmaf(s2[1], r0, lg[1]);
-        lg[2] = fmaf(s2[2], r1, lg[2]);
-        lg[3] = fmaf(s2[3], r1, lg[3]);
+    {
+        float2 lo = mul2(make_float2(s1[0], s1[1]), make_float2(cur.ks0, cur.ks0));
+        float2 hi = mul2(make_float2(s1[2], s1[3]), make_float2(cur.ks1, cur.ks1));
+        if (PROD) {
+            // the sign product shares the 1/alpha-scaled query fragments
+            const float2 rr = mul2(mul2(make_float2(cur.ks0, cur.ks1), make_float2(cur.re0, cur.re1)),
+                                   make_float2(TQ_ALPHA3, TQ_ALPHA3));
+            lo = fma2(make_float2(s2[0], s2[1]), make_float2(rr.x, rr.x), lo);
+            hi = fma2(make_float2(s2[2], s2[3]), make_float2(rr.y, rr.y), hi);
+        }
+        lg[0] = lo.x;
+        lg[1] = lo.y;
+        lg[2] = hi.x;
+        lg[3] = hi.y;
     }
 
     if (MODE == 1) {
@@ -545,26 +549,40 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
     }
     const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-    const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+    const float2 dm = add2(make_float2(m_run[0], m_run[1]), make_float2(-mn0, -mn1));
+    const float al0 = ex2(dm.x), al1 = ex2(dm.y);
     m_run[0] = mn0;
     m_run[1] = mn1;
-    const float p0 = ex2(lg[0] - mn0), p1 = ex2(lg[1] - mn1);
-    const float p2 = ex2(lg[2] - mn0), p3 = ex2(lg[3] - mn1);
-    l_run[0] = fmaf(l_run[0], al0, p0 + p2);
-    l_run[1] = fmaf(l_run[1], al1, p1 + p3);
+    const float2 neg_mn = make_float2(-mn0, -mn1);
+    const float2 d01 = add2(make_float2(lg[0], lg[1]), neg_mn), d23 = add2(make_float2(lg[2], lg[3]), neg_mn);
+    const float p0 = ex2(d01.x), p1 = ex2(d01.y);
+    const float p2 = ex2(d23.x), p3 = ex2(d23.y);
+    {
+        const float2 ls = fma2(make_float2(l_run[0], l_run[1]), make_float2(al0, al1),
+                               add2(make_float2(p0, p1), make_float2(p2, p3)));
+        l_run[0] = ls.x;
+        l_run[1] = ls.y;
+    }
     if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
+        // packed multiplies: an accumulator tile's (col 2tig, col 2tig+1) pairs are register pairs
+        const float2 al = make_float2(al0, al1);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            o[j][0] *= al0;
-            o[j][1] *= al1;
-            o[j][2] *= al0;
-            o[j][3] *= al1;
+            const float2 a = mul2(make_float2(o[j][0], o[j][1]), al);
+            const float2 b = mul2(make_float2(o[j][2], o[j][3]), al);
+            o[j][0] = a.x;
+            o[j][1] = a.y;
+            o[j][2] = b.x;
+            o[j][3] = b.y;
         }
     }
     // P^T (k = token, n = query), V scale folded in
-    const float w0 = cur.vs0 * inv_alpha_v, w1 = cur.vs1 * inv_alpha_v;
-    const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * w0, p1 * w0));
-    const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * w1, p3 * w1));
+    const float2 wv = mul2(make_float2(cur.vs0, cur.vs1), make_float2(inv_alpha_v, inv_alpha_v));
+    const float w0 = wv.x, w1 = wv.y;
+    const float2 pw0 = mul2(make_float2(p0, p1), make_float2(w0, w0));
+    const float2 pw1 = mul2(make_float2(p2, p3), make_float2(w1, w1));
+    const uint32_t pb0 = movmatrix_trans(pack_half2(pw0.x, pw0.y));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(pw1.x, pw1.y));
 
     // ---- O^T += V^T P^T: A = V^T (rows = this lane's dims 16g + 2j + {0,1}, k = tokens) ----
     if constexpr (LUT) {
