@@ -161,9 +161,13 @@ int tq_launch_qjl_fused_attention_output(const tq_half* query, const uint8_t* pa
                                          int num_queries, int num_kv_tokens, tq_stream_t stream);
 
 /* Floats per (sequence, query head) in a split-KV partial: the rotated-domain
- * unnormalised accumulator acc[128], then the running maximum m (natural-log
- * logit units) and the denominator l.  Same triple the reference's fused
- * kernel carries in sh_m / sh_l / vaccum (tq_turbo_prod_kernels.cu:463-470). */
+ * unnormalised accumulator acc[128], then the softmax reference m (natural-log
+ * logit units) and the denominator l: acc = sum_t exp(logit_t - m) v_t,
+ * l = sum_t exp(logit_t - m).  Same triple the reference's fused kernel
+ * carries in sh_m / sh_l / vaccum (tq_turbo_prod_kernels.cu:463-470), except
+ * that m is only guaranteed to lie within 4 ln 2 below the largest logit, not
+ * to equal it; m + log(l) and acc / l do not depend on that choice, and they
+ * are all a merge uses. */
 #define TQ_PARTIAL_STRIDE 130
 
 /* Number of KV splits the decode kernels use for `batch` sequences of at most

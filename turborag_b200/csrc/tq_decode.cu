@@ -542,30 +542,28 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     }
 
     // ---- online softmax over the 16 tokens of the block ---------------------
+    // The reference m of exp2(logit - m) is the running maximum, which only has to stay within
+    // 2^kLazyBits of the true one: a block whose logits do not exceed m by more than that keeps
+    // m (p <= 2^kLazyBits, no cross-lane maximum, no rescale).  Otherwise -- the first blocks of
+    // a range and the occasional much larger logit -- the whole warp reduces the block maximum
+    // over the token lanes and rescales its sums, as a plain online softmax does every block.
+    constexpr float kLazyBits = 4.0f;
     float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
+    if (__any_sync(0xffffffffu, (mx0 > m_run[0] + kLazyBits) | (mx1 > m_run[1] + kLazyBits))) {
 #pragma unroll
-    for (int msk = 4; msk < 32; msk <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, msk));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
-    }
-    const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-    const float2 dm = add2(make_float2(m_run[0], m_run[1]), make_float2(-mn0, -mn1));
-    const float al0 = ex2(dm.x), al1 = ex2(dm.y);
-    m_run[0] = mn0;
-    m_run[1] = mn1;
-    const float2 neg_mn = make_float2(-mn0, -mn1);
-    const float2 d01 = add2(make_float2(lg[0], lg[1]), neg_mn), d23 = add2(make_float2(lg[2], lg[3]), neg_mn);
-    const float p0 = ex2(d01.x), p1 = ex2(d01.y);
-    const float p2 = ex2(d23.x), p3 = ex2(d23.y);
-    {
-        const float2 ls = fma2(make_float2(l_run[0], l_run[1]), make_float2(al0, al1),
-                               add2(make_float2(p0, p1), make_float2(p2, p3)));
+        for (int msk = 4; msk < 32; msk <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, msk));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, msk));
+        }
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float2 dm = add2(make_float2(m_run[0], m_run[1]), make_float2(-mn0, -mn1));
+        const float2 al = make_float2(ex2(dm.x), ex2(dm.y));
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+        const float2 ls = mul2(make_float2(l_run[0], l_run[1]), al);
         l_run[0] = ls.x;
         l_run[1] = ls.y;
-    }
-    if (__any_sync(0xffffffffu, (al0 != 1.0f) | (al1 != 1.0f))) {
         // packed multiplies: an accumulator tile's (col 2tig, col 2tig+1) pairs are register pairs
-        const float2 al = make_float2(al0, al1);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float2 a = mul2(make_float2(o[j][0], o[j][1]), al);
@@ -575,6 +573,15 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             o[j][2] = b.x;
             o[j][3] = b.y;
         }
+    }
+    const float2 neg_mn = make_float2(-m_run[0], -m_run[1]);
+    const float2 d01 = add2(make_float2(lg[0], lg[1]), neg_mn), d23 = add2(make_float2(lg[2], lg[3]), neg_mn);
+    const float p0 = ex2(d01.x), p1 = ex2(d01.y);
+    const float p2 = ex2(d23.x), p3 = ex2(d23.y);
+    {
+        const float2 ls = add2(make_float2(l_run[0], l_run[1]), add2(make_float2(p0, p1), make_float2(p2, p3)));
+        l_run[0] = ls.x;
+        l_run[1] = ls.y;
     }
     // P^T (k = token, n = query), V scale folded in
     const float2 wv = mul2(make_float2(cur.vs0, cur.vs1), make_float2(inv_alpha_v, inv_alpha_v));
