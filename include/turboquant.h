@@ -165,7 +165,7 @@ int tq_launch_qjl_fused_attention_output(const tq_half* query, const uint8_t* pa
  * logit units) and the denominator l: acc = sum_t exp(logit_t - m) v_t,
  * l = sum_t exp(logit_t - m).  Same triple the reference's fused kernel
  * carries in sh_m / sh_l / vaccum (tq_turbo_prod_kernels.cu:463-470), except
- * that m is only guaranteed to lie within 4 ln 2 below the largest logit, not
+ * that m is only guaranteed to lie within 1.5 ln 2 below the largest logit, not
  * to equal it; m + log(l) and acc / l do not depend on that choice, and they
  * are all a merge uses. */
 #define TQ_PARTIAL_STRIDE 130

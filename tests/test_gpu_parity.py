@@ -363,10 +363,10 @@ def test_partials_of_token_ranges_merge_to_full_attention(tq, oracle, dev, schem
     for hh in range(h):
         for gg in range(g):
             a, r_ = mine[hh * g + gg], st[gg, hh]
-            # the reference m of a record may sit up to 4 ln 2 below the largest logit (the kernel
-            # keeps it while a block stays within 2^4 of it); m + log(l) does not depend on it
+            # the reference m of a record may sit up to 1.5 ln 2 below the largest logit (the kernel
+            # keeps it while a block stays within 2^1.5 of it); m + log(l) does not depend on it
             tol_m = 2e-3 * max(1.0, abs(r_[128]))
-            assert -tol_m < r_[128] - a[128] < 4 * np.log(2) + tol_m
+            assert -tol_m < r_[128] - a[128] < 1.5 * np.log(2) + tol_m
             lse_a, lse_r = a[128] + np.log(a[129]), r_[128] + np.log(r_[129])
             assert abs(lse_a - lse_r) < 2e-3 * max(1.0, abs(lse_r))
             na, nr = a[:128] / a[129], r_[:128] / r_[129]

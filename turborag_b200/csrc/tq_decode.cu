@@ -545,9 +545,12 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
     // The reference m of exp2(logit - m) is the running maximum, which only has to stay within
     // 2^kLazyBits of the true one: a block whose logits do not exceed m by more than that keeps
     // m (p <= 2^kLazyBits, no cross-lane maximum, no rescale).  Otherwise -- the first blocks of
-    // a range and the occasional much larger logit -- the whole warp reduces the block maximum
+    // a range and the occasional larger logit -- the whole warp reduces the block maximum
     // over the token lanes and rescales its sums, as a plain online softmax does every block.
-    constexpr float kLazyBits = 4.0f;
+    // 2^1.5 stays below the V table scale (TQ_ALPHA4 = 3.2), so the fp16 operand p * vs / alpha
+    // is never larger than the row scale vs itself: no new overflow case for any fp16 input.
+    constexpr float kLazyBits = 1.5f;
+    static_assert(2.8285f < 3.19f, "2^kLazyBits must stay below TQ_ALPHA4");
     float mx0 = fmaxf(lg[0], lg[2]), mx1 = fmaxf(lg[1], lg[3]);
     if (__any_sync(0xffffffffu, (mx0 > m_run[0] + kLazyBits) | (mx1 > m_run[1] + kLazyBits))) {
 #pragma unroll
