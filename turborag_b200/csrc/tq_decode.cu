@@ -1029,12 +1029,9 @@ decode_paged16_kernel(DecodeParams p) {
     int stage = 0;  // stage holding iteration `it`
     for (int it = 0; it < n_iter; ++it) {
         const int fill = stage == 0 ? kStages - 1 : stage - 1;  // (it + kStages - 1) % kStages
-        // Block `it` has landed once all but the newest group are complete.  The barrier makes the
-        // other lanes' pieces visible and, being behind every lane's reads of the previous block,
-        // also frees that block's stage: its refill is issued right after it.
-        cp_async_wait<kStages - 2>();
-        __syncwarp();
         issue(it + kStages - 1, ring_addr + fill * kStageBytes);
+        cp_async_wait<kStages - 1>();
+        __syncwarp();  // scale pieces are copied by other lanes
         const uint8_t* stg = ring + stage * kStageBytes;
         const int tb = r.t_begin + 16 * (r.blk_lo + r.stream + it * kStreams);
         BlockRaw cur;
@@ -1060,6 +1057,7 @@ decode_paged16_kernel(DecodeParams p) {
             if (tb + g + 8 >= r.t_end) cur.ks1 = cur.vs1 = cur.re1 = 0.0f;
         }
         process_block<PROD, 0, true, false, kSignQ>(p, ctx, cur, tb, r.t_end, st);
+        __syncwarp();  // every lane is done reading this stage before it is refilled
         stage = stage == kStages - 1 ? 0 : stage + 1;
     }
     cp_async_wait<0>();
