@@ -540,7 +540,7 @@ def prefill_numbers(torch, tq, dev, gen, batch=8, nq=256, n=32768, hq=16, h=2, i
     if pk.exists():
         tensor_peak = float(json.loads(pk.read_text())["bf16_tflops"])
     return {"value": flops / ms / 1e9, "unit": "TFLOP/s", "ms": ms, "frac_of_tensor_peak": flops / ms / 1e9 / tensor_peak,
-            "shape": f"b{batch}_q{nq}_kv{n}_q{hq}kv{h}", "note": "tcgen05 + TMEM tensor tiles; TQ_PREFILL_MMA_SYNC=1 selects the mma.sync kernel"}
+            "shape": f"b{batch}_q{nq}_kv{n}_q{hq}kv{h}", "note": "tcgen05 + TMEM tensor tiles"}
 
 
 def side_workload(args):

@@ -17,7 +17,9 @@
  *   slot_mapping: int32 [num_tokens]; slot = physical_block*block_size + t.
  *   query/output: fp16 [num_queries, num_kv_heads, head_dim] — one query row
  *   per KV head (GQA group member g of kv-head h is row g).
- * Supported shapes: head_dim == 128, block_size >= 1, num_kv_heads 1..32.
+ * Supported shapes: head_dim == 128, block_size >= 1, any num_kv_heads >= 1 (attention serves
+ * layouts with more than 8 kv heads by one launch per group of 8 heads; tq_mse_prefill_paged and
+ * tq_decode_paged_static take 1..8 kv heads).
  */
 #ifndef TURBOQUANT_H
 #define TURBOQUANT_H
@@ -202,8 +204,8 @@ int tq_decode_paged(int scheme, const tq_half* query, const uint8_t* page_pool,
 
 /* Has no counterpart in the reference.  tq_decode_paged for callers that must not allocate
  * device memory: a serving engine that gave the whole GPU to its own memory pool when it
- * started, a latency-critical loop that cannot risk the synchronisation an allocation may
- * bring, code running under stream capture.  Same inputs, outputs and results as
+ * started, or a latency-critical loop that cannot risk the synchronisation an allocation may
+ * bring.  Same inputs, outputs and results as
  * tq_decode_paged(..., workspace = NULL) over the whole sequence, but the split-KV scratch is
  * a fixed array inside the library (TQ_DECODE_STATIC_SCRATCH_BYTES per GPU, held from the
  * moment the library is loaded on that GPU until the process ends) and the call performs no

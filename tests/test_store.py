@@ -1,6 +1,7 @@
 """Disk store (turborag_b200/store.py): file names and manifest as the reference writes them
 (tq_backend/cag_store.py:24-157), and the GPU load path."""
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -10,7 +11,8 @@ import pytest
 torch = pytest.importorskip("torch")
 
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE = Path("/root/reference")
+# a checkout of the reference project, when the machine has one (the host-side compatibility test)
+REFERENCE = Path(os.environ.get("TQ_REFERENCE_DIR", "/root/reference"))
 
 
 def test_names_and_manifest(tmp_path, lib_path):
@@ -231,3 +233,38 @@ def test_container_load_matches_per_layer_files(tmp_path, lib_path, scheme):
     path.write_bytes(raw)
     with pytest.raises(RuntimeError, match="checksum mismatch in layer 2"):
         st.load_container_hnd("doc", scheme, (h, d), verify=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse"])
+def test_load_paths_inside_a_side_stream(tmp_path, lib_path, scheme):
+    """The store's kernels run on torch's current stream: a load issued inside
+    ``with torch.cuda.stream(s)`` is ordered after the host-to-device copies and before work queued
+    on ``s`` afterwards, and gives the bits of the default-stream load.  A long-running kernel is
+    queued on ``s`` first so that a missing dependency would show."""
+    from turborag_b200.store import CAGStore
+    dev = torch.device("cuda:0")
+    st = CAGStore(tmp_path, lib_path)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    n, h, d, layers = 4099, 2, 128, 6
+    for l in range(layers):
+        st.pack_document("doc", l, torch.randn(n, h, d, device=dev, generator=g).half(),
+                         torch.randn(n, h, d, device=dev, generator=g).half(), scheme)
+    st.export_container("doc", layers, scheme, (h, d))
+    want, _ = st.load_layers_hnd("doc", layers, scheme, (h, d))
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(dev)
+    busy = torch.randn(4096, 4096, device=dev)
+    for loader in (lambda: st.load_layers_hnd("doc", layers, scheme, (h, d)),
+                   lambda: st.load_container_hnd("doc", scheme, (h, d))):
+        with torch.cuda.stream(side):
+            for _ in range(20):
+                busy = busy @ busy * 1e-3  # keeps the side stream busy while the loads are queued behind it
+            got, doc_len = loader()
+            sums = [(k.float().sum(), v.float().sum()) for _, k, v in got]  # consumers on the same stream
+        side.synchronize()
+        assert doc_len == n
+        for (l, k, v), (l2, k2, v2), (sk, sv) in zip(want, got, sums):
+            assert l == l2 and torch.equal(k, k2) and torch.equal(v, v2)
+            assert sk.item() == k.float().sum().item() and sv.item() == v.float().sum().item()

@@ -2,7 +2,7 @@
 
 It exists for hosts that may not allocate device memory on the decode path (a serving
 engine whose own pool owns the whole GPU, a loop that cannot risk an allocation's implicit
-synchronisation, code under stream capture): its split-KV scratch is a fixed array inside
+synchronisation): its split-KV scratch is a fixed array inside
 the library.  Checked here against the regular entry point on two calls in a row (the array
 is shared and keeps the previous call's bytes), and that a shape beyond the array is refused.
 This file is collected last so that every other test has already run if it fails."""
@@ -70,3 +70,29 @@ def test_static_scratch_rejects_oversized_shape(tq):
     pool = torch.zeros(lay.page_size_bytes, dtype=torch.uint8, device=dev)
     with pytest.raises(RuntimeError, match="built-in array holds"):
         tq.decode_paged_static("turbo_prod", q, pool, tables, lens, lay, cfg, max_kv_tokens=n)
+
+
+def test_static_scratch_leaves_device_memory_alone(tq, oracle):
+    """The device's free memory (driver view: every allocation of any pool in this process counts)
+    is the same after a series of static calls as before it, with the output tensor made
+    beforehand -- whereas the regular entry point without a workspace draws on the library's
+    stream-ordered pool, which shows as less free memory once that pool has grown."""
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(5)
+    cfg = tq.default_config()
+    cfg.num_kv_heads = 2
+    lay = tq.make_layout_for(cfg)
+    lens = [2500, 900]
+    pool, tables = _case(oracle, "turbo_prod", rng, lens, 2)
+    q = torch.from_numpy(rng.standard_normal((2, 16, 128)).astype(np.float16).view(np.int16)).to(dev).view(torch.float16)
+    out = torch.empty_like(q)
+    args = ("turbo_prod", q, torch.from_numpy(pool).to(dev), torch.from_numpy(tables).to(dev),
+            torch.tensor(lens, dtype=torch.int32, device=dev), lay, cfg)
+    tq.decode_paged_static(*args, output=out, max_kv_tokens=max(lens))  # first call: symbol address lookup
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(8):
+        tq.decode_paged_static(*args, output=out, max_kv_tokens=max(lens))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(dev)
+    assert free1 == free0

@@ -18,7 +18,7 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libturboquant.so"
-SOURCES = ["tq_capi.cpp", "tq_pack.cu", "tq_dequant.cu", "tq_decode.cu", "tq_prefill.cu",
+SOURCES = ["tq_capi.cpp", "tq_pack.cu", "tq_dequant.cu", "tq_decode.cu",
            "tq_prefill_tc.cu", "tq_peer.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

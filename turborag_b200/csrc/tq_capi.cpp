@@ -4,7 +4,6 @@
 // arguments -> -1, any failure in a launch helper -> -2 with the text kept in a
 // thread-local buffer returned by tq_last_error(), no C++ exception ever
 // crosses the boundary, no synchronisation.
-#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include <climits>
@@ -570,8 +569,7 @@ extern "C" int tq_mse_prefill_paged(const tq_half* query, const uint8_t* page_po
         if (batch < 0 || num_q_tokens < 0 || num_q_heads < 1 || table_stride < 0)
             throw std::runtime_error("mse_prefill_paged: negative size");
         if (cfg->num_kv_heads > 8) throw std::runtime_error("mse_prefill_paged: num_kv_heads must be 1..8");
-        static const bool legacy = std::getenv("TQ_PREFILL_MMA_SYNC") != nullptr;
-        (legacy ? tq::launch_prefill : tq::launch_prefill_tc)(
+        tq::launch_prefill_tc(
             query, page_pool, block_tables, table_stride, seq_lens, chunk_key, chunk_value, output,
             geom_mse(*layout, *cfg), cfg->head_dim, batch, num_q_tokens, num_q_heads,
             table_stride * cfg->block_size, static_cast<cudaStream_t>(stream));
@@ -614,7 +612,9 @@ extern "C" TQBlockTableHandle* tq_block_table_create(int num_pages, int block_si
 extern "C" void tq_block_table_destroy(TQBlockTableHandle* h) { delete h; }
 
 extern "C" int tq_block_table_free_pages(const TQBlockTableHandle* h) {
-    return h ? static_cast<int>(h->free_list.size()) : -1;
+    if (!h) return -1;
+    std::lock_guard<std::mutex> lock(const_cast<TQBlockTableHandle*>(h)->mu);
+    return static_cast<int>(h->free_list.size());
 }
 
 extern "C" int tq_block_table_append(TQBlockTableHandle* h, int seq_id, int append_tokens,
@@ -641,6 +641,7 @@ extern "C" int tq_block_table_append(TQBlockTableHandle* h, int seq_id, int appe
 
 extern "C" int tq_block_table_num_tokens(const TQBlockTableHandle* h, int seq_id) {
     if (!h) return -1;
+    std::lock_guard<std::mutex> lock(const_cast<TQBlockTableHandle*>(h)->mu);
     const auto it = h->seqs.find(seq_id);
     return it == h->seqs.end() ? 0 : it->second.num_tokens;
 }
@@ -648,6 +649,7 @@ extern "C" int tq_block_table_num_tokens(const TQBlockTableHandle* h, int seq_id
 extern "C" int tq_block_table_pages(const TQBlockTableHandle* h, int seq_id, int32_t* pages_out,
                                     int max_pages) {
     if (!h || (!pages_out && max_pages > 0)) return -1;
+    std::lock_guard<std::mutex> lock(const_cast<TQBlockTableHandle*>(h)->mu);
     const auto it = h->seqs.find(seq_id);
     if (it == h->seqs.end()) return 0;
     const int n = static_cast<int>(it->second.pages.size());

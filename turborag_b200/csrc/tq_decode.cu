@@ -98,6 +98,7 @@ struct DecodeParams {
     int streams;       // warps per kv head inside a group
     int bs_shift;      // log2(block_size) or -1
     int aligned16;     // every code row starts on a 16-byte boundary
+    int head0, heads;  // kv heads [head0, head0 + heads) are served by this launch (heads <= 8)
 };
 
 // ---- small PTX wrappers ------------------------------------------------------
@@ -328,7 +329,8 @@ struct BlockCtx {
     uint32_t lane_k, lane_v;  // this lane's replica offsets inside a table row
     uint8_t* group_smem;  // first per-warp region of this warp's group (merge records)
     int bar_id, bar_threads;  // barrier shared by the warps that work on one (sequence, split)
-    int lane, g, tig, h, H, nq, gq0;
+    int lane, g, tig, h, H, nq, gq0;  // h: kv head (global index), H: kv heads of the page layout
+    int hl, Hl;                       // head index inside this launch, heads of this launch
 };
 
 // ---- shared-memory operand tables (paged fast path) -----------------------------------
@@ -650,7 +652,9 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                                                 BlockCtx& ctx, CtaRange& r, uint4* qsign_group = nullptr) {
     const int lane = threadIdx.x & 31;
     const int H = p.geo.num_kv_heads;
-    const int h = warp % H, stream = warp / H;
+    const int Hl = p.heads;
+    const int hl = warp % Hl, stream = warp / Hl;
+    const int h = p.head0 + hl;
     const int g = lane >> 2, tig = lane & 3;
     const int qg = blockIdx.z;
     r.split = split;
@@ -693,7 +697,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
 #pragma unroll
             for (int e = 0; e < 4; ++e) x[e] *= sc;
         }
-        __half2* dst = reinterpret_cast<__half2*>(qsm + (h * 8 + col) * kHeadDim + 4 * lane);
+        __half2* dst = reinterpret_cast<__half2*>(qsm + (hl * 8 + col) * kHeadDim + 4 * lane);
         const __half2 hi0 = __floats2half2_rn(x[0], x[1]), hi1 = __floats2half2_rn(x[2], x[3]);
         dst[0] = hi0;
         dst[1] = hi1;
@@ -701,7 +705,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
             // the fp16 rounding of q' that the other schemes tolerate is 11 times larger against
             // unscaled logits: keep the remainder as a second fp16 fragment set (q' = hi + lo)
             const float2 h0 = __half22float2(hi0), h1 = __half22float2(hi1);
-            __half2* dlo = dst + (H * 8 * kHeadDim) / 2;
+            __half2* dlo = dst + (Hl * 8 * kHeadDim) / 2;
             dlo[0] = __floats2half2_rn(x[0] - h0.x, x[1] - h0.y);
             dlo[1] = __floats2half2_rn(x[2] - h1.x, x[3] - h1.y);
         }
@@ -709,7 +713,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     group_sync(bar_id, bar_threads);
 
     {
-        const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
+        const __half* qrow = qsm + (hl * 8 + g) * kHeadDim + 32 * tig;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             if (LUT) {
@@ -725,7 +729,7 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
                 ctx.qf[s][0] = *reinterpret_cast<const uint32_t*>(&b01);
                 ctx.qf[s][1] = *reinterpret_cast<const uint32_t*>(&b23);
                 if (QJL) {
-                    const __half* qlo = qrow + H * 8 * kHeadDim;
+                    const __half* qlo = qrow + Hl * 8 * kHeadDim;
                     const __half2 l01 = __halves2half2(qlo[base], qlo[base + 4]);
                     const __half2 l23 = __halves2half2(qlo[base + 1], qlo[base + 5]);
                     ctx.qlo[s][0] = *reinterpret_cast<const uint32_t*>(&l01);
@@ -738,19 +742,19 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     if (qsign_group) {
         // fragments in the (d, d+4) pairing for the residual-sign MMAs: word wi of the lane's 32 dims
         // -> (q[0],q[4]) (q[1],q[5]) | (q[2],q[6]) (q[3],q[7]); written once per kv head
-        const __half* qrow = qsm + (h * 8 + g) * kHeadDim + 32 * tig;
+        const __half* qrow = qsm + (hl * 8 + g) * kHeadDim + 32 * tig;
         if (stream == 0) {
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 const __half* q8 = qrow + 8 * wi;
                 const __half2 f0 = __halves2half2(q8[0], q8[4]), f1 = __halves2half2(q8[1], q8[5]);
                 const __half2 f2 = __halves2half2(q8[2], q8[6]), f3 = __halves2half2(q8[3], q8[7]);
-                qsign_group[(h * 4 + wi) * 32 + lane] =
+                qsign_group[(hl * 4 + wi) * 32 + lane] =
                     make_uint4(*reinterpret_cast<const uint32_t*>(&f0), *reinterpret_cast<const uint32_t*>(&f1),
                                *reinterpret_cast<const uint32_t*>(&f2), *reinterpret_cast<const uint32_t*>(&f3));
             }
         }
-        ctx.qsign = qsign_group + h * 4 * 32;
+        ctx.qsign = qsign_group + hl * 4 * 32;
     }
     // fp16(alpha * level) split into high-byte and low-byte pools, entries 0-3 | 4-7
     // (tests/test_abi.py recomputes them from the level tables)
@@ -770,6 +774,8 @@ __device__ __forceinline__ void decode_prologue(const DecodeParams& p, uint8_t* 
     ctx.tig = tig;
     ctx.h = h;
     ctx.H = H;
+    ctx.hl = hl;
+    ctx.Hl = Hl;
     ctx.nq = nq;
     ctx.gq0 = gq0;
 
@@ -819,7 +825,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int warp_
     group_sync(c.bar_id, c.bar_threads);
     if (r.stream > 0) return;
     for (int s = 1; s < p.streams; ++s) {
-        const float* q = reinterpret_cast<const float*>(smem_raw + (s * H + h) * warp_bytes);
+        const float* q = reinterpret_cast<const float*>(smem_raw + (s * c.Hl + c.hl) * warp_bytes);
         const float ms0 = q[32 * 32 + lane], ms1 = q[33 * 32 + lane];
         const float mn0 = fmaxf(m_run[0], ms0), mn1 = fmaxf(m_run[1], ms1);
         const float a0 = ex2(m_run[0] - mn0), a1 = ex2(m_run[1] - mn1);
@@ -1297,7 +1303,7 @@ void launch_merge_splits(const float* partials, int splits, void* output, int ro
 
 void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     const int H = a.geo.num_kv_heads;
-    if (H < 1 || H > kMaxHeads) throw std::runtime_error("decode: num_kv_heads must be 1..8");
+    if (H < 1) throw std::runtime_error("decode: num_kv_heads must be positive");
     if (a.num_q_heads % H != 0)
         throw std::runtime_error("decode: num_q_heads must be a multiple of num_kv_heads");
     if (a.batch <= 0 || a.num_q_heads <= 0) return;
@@ -1309,11 +1315,14 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
         throw std::runtime_error("decode: partials, logits and the peer exchange serve turbo_prod and turbo_mse only");
     const int G = a.num_q_heads / H;
     const int qgroups = (G + 7) / 8;
-    const int streams = (8 % H == 0) ? 8 / H : 1;
-    const int warps = H * streams;
+    // A CTA serves at most kMaxHeads kv heads; layouts with more heads are served by one launch per
+    // group of kMaxHeads heads (same grid, same splits, the partial records of all heads meet in one merge).
+    const int heads_per_launch = H <= kMaxHeads ? H : kMaxHeads;
+    const int streams = (H <= kMaxHeads && 8 % H == 0) ? 8 / H : 1;
+    const int warps = heads_per_launch * streams;
     // per-warp regions, then the query scratch (QJL: a second one for the fp16 remainders)
     const size_t smem = static_cast<size_t>(warps) * kWarpSmemBytes +
-                        (a.scheme == TQ_SCHEME_QJL ? 2 : 1) * H * 8 * kHeadDim * sizeof(__half);
+                        (a.scheme == TQ_SCHEME_QJL ? 2 : 1) * heads_per_launch * 8 * kHeadDim * sizeof(__half);
 
     DecodeParams p{};
     p.query = static_cast<const __half*>(a.query);
@@ -1332,6 +1341,8 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     p.kv_end = a.kv_end;
     p.streams = streams;
     p.batch = a.batch;
+    p.head0 = 0;
+    p.heads = heads_per_launch;
     {
         const int bs = a.geo.block_size;
         p.bs_shift = -1;
@@ -1348,8 +1359,12 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
         if (!prod) throw std::runtime_error("logits: turbo_prod only");
         int splits = decode_num_splits(a.batch * qgroups, a.max_kv_tokens, H, a.geo.block_size);
         p.splits = splits;
-        decode_kernel<true, 1><<<dim3(splits, a.batch, qgroups), warps * 32, smem, stream>>>(p);
-        check_launch("turbo_prod fused_attention_logits");
+        for (int h0 = 0; h0 < H; h0 += kMaxHeads) {
+            p.head0 = h0;
+            p.heads = H - h0 < kMaxHeads ? H - h0 : kMaxHeads;
+            decode_kernel<true, 1><<<dim3(splits, a.batch, qgroups), p.heads * streams * 32, smem, stream>>>(p);
+            check_launch("turbo_prod fused_attention_logits");
+        }
         return;
     }
 
@@ -1388,14 +1403,17 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
             else TQ_FAST_LAUNCH(false, 8);
         }
 #undef TQ_FAST_LAUNCH
-    } else if (prod) {
-        decode_kernel<true, 0><<<grid, warps * 32, smem, stream>>>(p);
-    } else if (qjl) {
-        decode_kernel<false, 0, true><<<grid, warps * 32, smem, stream>>>(p);
     } else {
-        decode_kernel<false, 0><<<grid, warps * 32, smem, stream>>>(p);
+        for (int h0 = 0; h0 < H; h0 += kMaxHeads) {
+            p.head0 = h0;
+            p.heads = H - h0 < kMaxHeads ? H - h0 : kMaxHeads;
+            const int threads = p.heads * streams * 32;
+            if (prod) decode_kernel<true, 0><<<grid, threads, smem, stream>>>(p);
+            else if (qjl) decode_kernel<false, 0, true><<<grid, threads, smem, stream>>>(p);
+            else decode_kernel<false, 0><<<grid, threads, smem, stream>>>(p);
+            check_launch(prod ? "turbo_prod decode" : qjl ? "qjl decode" : "turbo_mse decode");
+        }
     }
-    check_launch(prod ? "turbo_prod decode" : qjl ? "qjl decode" : "turbo_mse decode");
 
     // merge the splits of every (sequence, query head) row
     const int rows = a.batch * a.num_q_heads;
@@ -1414,9 +1432,8 @@ void launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 //
 // Some hosts of this library must not allocate device memory on the decode path: a serving
 // engine that has handed the whole GPU to its own pool at start-up (any later driver
-// allocation can fail or fragment it), a real-time loop that cannot afford the implicit
-// synchronisation an allocation may cause, or code that runs while a CUDA stream is being
-// captured.  tq_decode_paged_static serves them: same arithmetic as tq_decode_paged, but the
+// allocation can fail or fragment it), or a real-time loop that cannot afford the implicit
+// synchronisation an allocation may cause.  tq_decode_paged_static serves them: same arithmetic as tq_decode_paged, but the
 // split-KV partials go to the fixed array below instead of a caller buffer or the library's stream-ordered scratch pool.
 //
 // The array is part of the loaded module: every GPU that loads the library holds these

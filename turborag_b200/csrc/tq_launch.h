@@ -86,12 +86,10 @@ void launch_merge(const float* partials, int num_parts, void* output, float* par
 void launch_merge_splits(const float* partials, int splits, void* output, int rows, int num_q_heads,
                          int num_kv_heads, int head_dim, cudaStream_t stream);
 
-void launch_prefill(const void* query, const uint8_t* pool, const int32_t* block_tables,
-                    int table_stride, const int32_t* seq_lens, const void* chunk_key,
-                    const void* chunk_value, void* output, const PageGeom& geo, int head_dim,
-                    int batch, int nq, int hq, int max_prefix_tokens, cudaStream_t stream);
-// Same contract on the tcgen05 tensor cores; prefill_tc_status() returns the device status word
-// of that kernel (0 = no bounded wait ever ran out; synchronises the device).
+// Chunk prefill over a turbo_mse prefix on the tcgen05 tensor cores: `nq` query tokens per sequence
+// attend to the paged prefix and, causally, to their own fp16 chunk (chunk_key / chunk_value may be
+// null: prefix only).  prefill_tc_status() returns the device status word of that kernel (0 = no
+// bounded wait ever ran out; synchronises the device).
 void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* block_tables,
                        int table_stride, const int32_t* seq_lens, const void* chunk_key,
                        const void* chunk_value, void* output, const PageGeom& geo, int head_dim,

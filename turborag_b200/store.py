@@ -191,7 +191,7 @@ class CAGStore:
             layout = self._layout(scheme, cfg)
             pool = torch.zeros(self._pool_bytes(scheme, n, cfg), dtype=torch.uint8, device=key.device)
             {"turbo_prod": self.tq.pack, "turbo_mse": self.tq.mse_pack, "qjl": self.tq.qjl_pack}[scheme](
-                key.contiguous(), value.contiguous(), slots, pool, layout, cfg)
+                key.contiguous(), value.contiguous(), slots, pool, layout, cfg, stream=self._stream(key.device))
             host = torch.empty(pool.numel(), dtype=torch.uint8, pin_memory=True)
             host.copy_(pool, non_blocking=True)
             torch.cuda.current_stream(key.device).synchronize()
@@ -202,6 +202,28 @@ class CAGStore:
         return pool_p.stat().st_size
 
     # ---- online: load -------------------------------------------------------------------------
+    @staticmethod
+    def _stream(device) -> int:
+        """Handle of torch's current stream on ``device``: every library call of the store runs on it,
+        so the kernels are ordered with the caller's work inside ``with torch.cuda.stream(s)`` too."""
+        return torch.cuda.current_stream(device).cuda_stream
+
+    def _copy_to_device(self, host: torch.Tensor, nbytes: int, device: torch.device):
+        """Pinned buffer -> fresh device tensor on the copy stream; returns (pool, end-of-copy event).
+        The copy stream first waits for the caller's stream: the block the caching allocator hands
+        out may still be in use by work queued there (a previous layer's dequant).  record_stream
+        keeps the allocator from recycling the pool while the copy is in flight."""
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device)
+        pool = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self._copy_stream.wait_stream(torch.cuda.current_stream(device))
+        done = torch.cuda.Event()
+        with torch.cuda.stream(self._copy_stream):
+            pool.copy_(host[:nbytes], non_blocking=True)
+            done.record()
+        pool.record_stream(self._copy_stream)
+        return pool, done
+
     def _reader_pool(self):
         if self._readers is None:
             from concurrent.futures import ThreadPoolExecutor
@@ -228,14 +250,7 @@ class CAGStore:
         if got != nbytes:
             raise RuntimeError(f"{self._pool_path(doc_id, layer, scheme)}: {got} bytes, expected {nbytes} "
                                f"(wrong head_shape, or a stale store)")
-        if self._copy_stream is None:
-            self._copy_stream = torch.cuda.Stream(device)
-        pool = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        done = torch.cuda.Event()
-        with torch.cuda.stream(self._copy_stream):
-            pool.copy_(host[:nbytes], non_blocking=True)
-            done.record()
-        return pool, done
+        return self._copy_to_device(host, nbytes, device)
 
     def load_document(self, doc_id: str, layer: int, scheme: Scheme = "turbo_prod",
                       head_shape: tuple[int, int] = (2, 64)) -> tuple[torch.Tensor, torch.Tensor, int]:
@@ -270,7 +285,7 @@ class CAGStore:
         out_k = torch.empty(n, h, d, device=slots.device, dtype=torch.float16)
         out_v = torch.empty_like(out_k)
         {"turbo_prod": self.tq.dequant, "turbo_mse": self.tq.mse_dequant, "qjl": self.tq.qjl_dequant}[scheme](
-            pool, slots, out_k, out_v, self._layout(scheme, cfg), cfg)
+            pool, slots, out_k, out_v, self._layout(scheme, cfg), cfg, stream=self._stream(slots.device))
         return out_k, out_v
 
     def load_layers_hnd(self, doc_id: str, num_layers: int, scheme: Scheme,
@@ -326,7 +341,7 @@ class CAGStore:
             torch.cuda.current_stream(dev).wait_event(done)
             k = torch.empty(1, h, n, d, device=dev, dtype=torch.float16)
             v = torch.empty_like(k)
-            self.tq.dequant_hnd(scheme, pool, slots, k, v, layout, cfg)
+            self.tq.dequant_hnd(scheme, pool, slots, k, v, layout, cfg, stream=self._stream(dev))
             out.append((l, k, v))
             doc_len = doc_len or n
         for ev in copies_in_flight:
@@ -451,11 +466,7 @@ class CAGStore:
             try:
                 for i, l in enumerate(hd["layers"]):
                     reads.pop(i).result()
-                    pool = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-                    done = torch.cuda.Event()
-                    with torch.cuda.stream(self._copy_stream):
-                        pool.copy_(hosts[i % ring][:nbytes], non_blocking=True)
-                        done.record()
+                    pool, done = self._copy_to_device(hosts[i % ring], nbytes, dev)
                     copied[i % ring] = done
                     # the buffer of the previous layer is free once its copy has finished: hand it to
                     # the reader of the layer one ring ahead of it
@@ -506,7 +517,8 @@ class CAGStore:
             torch.cuda.current_stream(dev).wait_event(done)
             k = torch.empty(1, h, hd["num_tokens"], d, device=dev, dtype=torch.float16)
             v = torch.empty_like(k)
-            self.tq.dequant_hnd(scheme, pool, state["slots"], k, v, state["layout"], state["cfg"])
+            self.tq.dequant_hnd(scheme, pool, state["slots"], k, v, state["layout"], state["cfg"],
+                                stream=self._stream(dev))
             out.append((l, k, v))
         n = self._stream_container(doc_id, scheme, head_shape, verify, consume)
         return out, n
@@ -553,7 +565,8 @@ class CAGStore:
         output = torch.empty_like(query)
         fn = {"turbo_prod": self.tq.fused_attn_output, "turbo_mse": self.tq.mse_fused_attn_output,
               "qjl": self.tq.qjl_fused_attn_output}[scheme]
-        fn(query.contiguous(), pool, slots, output, self._layout(scheme, cfg), cfg, query.shape[0], N)
+        fn(query.contiguous(), pool, slots, output, self._layout(scheme, cfg), cfg, query.shape[0], N,
+           stream=self._stream(query.device))
         return output
 
     def decode_documents(self, query: torch.Tensor, pools: list[torch.Tensor], lengths: list[int],
@@ -577,4 +590,4 @@ class CAGStore:
         dev = query.device
         return self.tq.decode_paged(scheme, query.contiguous(), pool, tables.to(dev),
                                     torch.tensor(lengths, dtype=torch.int32, device=dev), layout, cfg,
-                                    max_kv_tokens=max(lengths))
+                                    max_kv_tokens=max(lengths), stream=self._stream(dev))

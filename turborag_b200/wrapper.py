@@ -327,7 +327,8 @@ class TurboQuantWrapper:
     def decode_paged_static(self, scheme: str, query, page_pool, block_tables, seq_lens, layout,
                             cfg, output=None, max_kv_tokens: int | None = None, stream: int = 0):
         """``decode_paged`` for hosts that cannot allocate device memory while decoding (an
-        engine whose own pool owns the GPU, a capture in progress): the split-KV scratch is a
+        engine whose own pool owns the GPU, a loop that cannot risk an allocation's implicit
+        synchronisation): the split-KV scratch is a
         fixed 8 MiB array inside the library, nothing is allocated or freed.  Shapes that need
         more scratch raise; calls that may overlap on one GPU must be ordered by the caller."""
         _cuda(query, page_pool, block_tables, seq_lens, output)
