@@ -264,7 +264,10 @@ int tq_mse_prefill_status(void);
  *   tq_peer_merge: waits (at most 2 s) until every rank's flag in my_buffer shows `exchange`, then
  *     merges the world records per row (log-sum-exp), normalises, applies the inverse rotation and
  *     writes fp16 output[rows][128]; rows = sequences * num_q_heads, rows ordered (sequence, q head).
- * tq_peer_status(): 0, or 1 if a wait ever ran out on the current device (synchronises).
+ * tq_peer_status(): 0, or 1 if a wait ever ran out on the current device (synchronises);
+ * tq_peer_clear_status() sets it back to 0.  tq_peer_set_wait_ns(ns) changes the bound of the waits of
+ * later tq_peer_merge calls of this process (0 = back to the default 2 s); a wait that runs out makes
+ * the kernel give up on the missing records and finish, the context stays usable.
  * tq_decode_paged_publish = tq_decode_paged restricted to [kv_begin, kv_end) whose split merge
  * writes the records straight into the peers' buffers (decode + publish in two launches). */
 size_t tq_peer_buffer_bytes(int world, int rows_cap);
@@ -279,6 +282,8 @@ int tq_peer_publish(const float* local_partials, void* const* peer_buffers, int 
 int tq_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange,
                   tq_half* output, int num_q_heads, int num_kv_heads, int head_dim, tq_stream_t stream);
 int tq_peer_status(void);
+int tq_peer_clear_status(void);
+int tq_peer_set_wait_ns(unsigned long long ns);
 
 /* Host-side page allocator and block table (LIFO free list and the slot
  * formula of src/tq_allocator.cpp:5-31, src/tq_block_table.cpp:7-39; the pool

@@ -259,19 +259,22 @@ def attention_ref_single_head(q, k_all, v_all):
     return out
 
 
-def mse_prefill(query, pool, slots, chunk_k, chunk_v, cfg: Config):
+def mse_prefill(query, pool, slots, chunk_k, chunk_v, cfg: Config, rows=None):
     """query [nq, Hq, D]; prefix = turbo_mse pool via slots; optional causal
-    fp16 chunk [nq, H, D]. Returns fp32 [nq, Hq, D]."""
+    fp16 chunk [nq, H, D]. Returns fp32 [nq, Hq, D], or [len(rows), Hq, D] for the listed
+    query rows only (a row's index inside the chunk decides how much of the chunk it sees)."""
     q = _u16(query)
     slots = np.ascontiguousarray(slots, dtype=np.int32)
     nq, hq, d = q.shape
     lay = mse_layout(cfg)
-    out = np.zeros((nq, hq, d), np.float32)
     ck = None if chunk_k is None else _u16(chunk_k)
     cv = None if chunk_v is None else _u16(chunk_v)
-    lib().orc_mse_prefill(_p(q), _p(pool), _p(slots), C.c_int(slots.shape[0]), _p(ck),
-                          _p(cv), C.c_int(nq), C.c_int(hq), _p(out), C.byref(lay),
-                          C.byref(cfg))
+    rows_a = None if rows is None else np.ascontiguousarray(rows, dtype=np.int32)
+    nrows = nq if rows_a is None else int(rows_a.shape[0])
+    out = np.zeros((nrows, hq, d), np.float32)
+    lib().orc_mse_prefill_rows(_p(q), _p(pool), _p(slots), C.c_int(slots.shape[0]), _p(ck),
+                               _p(cv), C.c_int(nq), C.c_int(hq), _p(rows_a), C.c_int(nrows),
+                               _p(out), C.byref(lay), C.byref(cfg))
     return out
 
 

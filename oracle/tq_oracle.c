@@ -635,10 +635,11 @@ int orc_attention_ref_single_head(const uint16_t* q, const uint16_t* k_all,
  * the dequant kernel forms before its inverse rotation).  Chunk: fp16 K/V,
  * rotated with the same transform so one dot product serves both; query row
  * i sees the whole prefix and chunk rows 0..i.  Two-pass softmax in fp32. */
-void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
-                     const int32_t* slots, int nkv, const uint16_t* chunk_k,
-                     const uint16_t* chunk_v, int nq, int hq, float* out,
-                     const OrcMseLayout* lay, const OrcConfig* cfg) {
+void orc_mse_prefill_rows(const uint16_t* query, const uint8_t* pool,
+                          const int32_t* slots, int nkv, const uint16_t* chunk_k,
+                          const uint16_t* chunk_v, int nq, int hq, const int32_t* rows,
+                          int nrows, float* out, const OrcMseLayout* lay,
+                          const OrcConfig* cfg) {
     const int d = cfg->head_dim, H = cfg->num_kv_heads, grp = hq / H;
     const float c = inv_sqrt_d(d);
     for (int h = 0; h < H; ++h) {
@@ -658,8 +659,9 @@ void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
                            vr + (size_t)(nkv + t) * d);
             }
 #pragma omp parallel for collapse(2) schedule(static) num_threads(nthreads())
-        for (int i = 0; i < nq; ++i)
+        for (int r = 0; r < nrows; ++r)
             for (int g = 0; g < grp; ++g) {
+                int i = rows ? rows[r] : r;
                 int j = h * grp + g;
                 float qrot[128], acc[128];
                 rotate_fwd(query + ((size_t)i * hq + j) * d, h, d, qrot);
@@ -686,13 +688,22 @@ void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
                 for (int e = 0; e < d; ++e) acc[e] *= inv;
                 orc_fwht128(acc, d);
                 for (int e = 0; e < d; ++e)
-                    out[((size_t)i * hq + j) * d + e] =
+                    out[((size_t)r * hq + j) * d + e] =
                         acc[e] * c * orc_sign_flip(e, h);
                 free(sc);
             }
         free(kr);
         free(vr);
     }
+}
+
+/* All query rows of the chunk. */
+void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
+                     const int32_t* slots, int nkv, const uint16_t* chunk_k,
+                     const uint16_t* chunk_v, int nq, int hq, float* out,
+                     const OrcMseLayout* lay, const OrcConfig* cfg) {
+    orc_mse_prefill_rows(query, pool, slots, nkv, chunk_k, chunk_v, nq, hq, NULL, nq, out,
+                         lay, cfg);
 }
 
 /* ------------------------------------------------------------------------- */

@@ -125,6 +125,13 @@ int orc_attention_ref_single_head(const uint16_t* q, const uint16_t* k_all,
  * chunk (extension; arithmetic = restated dequant + dense fp32 softmax).
  * query [nq, hq, d] fp16, chunk_k/chunk_v [nq, h, d] fp16 (may be NULL),
  * out [nq, hq, d] fp32. Query head j uses kv head j / (hq / h). */
+/* The same for the listed query rows only (rows[r] = index of the row inside the chunk, which
+ * decides how much of the chunk it sees); out is [nrows, hq, head_dim].  rows == NULL: rows 0..nrows-1. */
+void orc_mse_prefill_rows(const uint16_t* query, const uint8_t* pool,
+                          const int32_t* slots, int nkv, const uint16_t* chunk_k,
+                          const uint16_t* chunk_v, int nq, int hq, const int32_t* rows,
+                          int nrows, float* out, const OrcMseLayout* lay,
+                          const OrcConfig* cfg);
 void orc_mse_prefill(const uint16_t* query, const uint8_t* pool,
                      const int32_t* slots, int nkv, const uint16_t* chunk_k,
                      const uint16_t* chunk_v, int nq, int hq, float* out,

@@ -28,12 +28,14 @@ def _worker(rank, world, port, q):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    res = {}
     try:
         tq = turborag_b200.TurboQuantWrapper()
         rng = np.random.default_rng(77)  # identical data on every rank
         lens, hq, h = [3000, 1234], 28, 4
-        res = {}
         xchg = PeerExchange(tq, len(lens) * hq, dev)
         res["mapping"] = xchg.how
         for scheme in ("turbo_prod", "turbo_mse"):
@@ -69,8 +71,14 @@ def _worker(rank, world, port, q):
                                      torch.tensor(lens, dtype=torch.int32, device=dev), lay, cfg,
                                      max_kv_tokens=max(lens), output=out2)
                 torch.cuda.synchronize()
-                assert torch.equal(out2, out), f"peer exchange differs from the all-gather path (call {rep})"
+                # recorded, not asserted: a rank that raised here would leave the others inside the
+                # next collective
+                if not torch.equal(out2, out):
+                    res.setdefault("peer_mismatch", []).append((scheme, rep))
         res["peer_status"] = tq.peer_status()
+    except Exception as e:  # noqa: BLE001 - reported through the queue, every rank still joins the gather
+        res["error"] = repr(e)
+    try:
         gathered = [None] * world
         dist.all_gather_object(gathered, res)
         if rank == 0:
@@ -89,11 +97,18 @@ def test_kv_split_across_gpus():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=300)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        res = q.get(timeout=300)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:  # no rank is left spinning in a collective on the shared GPUs
+            if p.is_alive():
+                p.terminate()
+            p.join(timeout=30)
     print(res)
     for r in res:
+        assert "error" not in r and "peer_mismatch" not in r, res
         assert r["turbo_prod"] < 2e-3 and r["turbo_mse"] < 2e-3, res
         assert r["peer_status"] == 0, res

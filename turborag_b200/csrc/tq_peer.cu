@@ -16,9 +16,9 @@
 // Double buffering by exchange parity is enough: rank r can only publish exchange e + 2 after
 // it merged e + 1, which needed q's records of e + 1, which q sent after it had finished
 // reading the buffers of e.
-// The merge kernel's wait for the flags is bounded by wall-clock time (kWaitNs); when it runs
-// out the kernel records a status code, skips the wait and finishes (results of that call are
-// then undefined, the context stays usable).
+// The merge kernel's wait for the flags is bounded by wall-clock time (2 s unless
+// tq_peer_set_wait_ns chose another bound); when it runs out the kernel records a status code,
+// skips the wait and finishes (results of that call are then undefined, the context stays usable).
 #include "tq_common.cuh"
 #include "tq_launch.h"
 
@@ -26,7 +26,9 @@ namespace tq {
 namespace {
 
 constexpr int kMaxPeers = 8;
-constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // 2 s
+// bound of the flag wait, handed to every merge launch as an argument (tq_peer_set_wait_ns)
+unsigned long long g_wait_ns = kDefaultWaitNs;
 
 struct PeerPtrs {
     float* records[kMaxPeers];
@@ -82,7 +84,7 @@ publish_kernel(const float* __restrict__ local, PeerPtrs peers, unsigned int* ti
 __global__ void __launch_bounds__(128)
 peer_merge_kernel(const float* __restrict__ records, const unsigned int* __restrict__ flags, int world,
                   int rows, int rows_cap, unsigned int exchange, __half* __restrict__ output,
-                  int num_q_heads, int num_kv_heads, int head_dim) {
+                  int num_q_heads, int num_kv_heads, int head_dim, unsigned long long wait_ns) {
     __shared__ int timed_out;
     if (threadIdx.x == 0) {
         int bad = 0;
@@ -90,7 +92,7 @@ peer_merge_kernel(const float* __restrict__ records, const unsigned int* __restr
         for (int q = 0; q < world && !bad; ++q) {
             const unsigned int* f = flags + (exchange & 1u) * world + q;
             while (ld_acquire_sys(f) != exchange) {
-                if (global_ns() - t0 > kWaitNs) {
+                if (global_ns() - t0 > wait_ns) {
                     bad = 1;
                     break;
                 }
@@ -200,7 +202,7 @@ extern "C" int tq_peer_merge(const void* my_buffer, int world, int rows, int row
             reinterpret_cast<const unsigned int*>(static_cast<const unsigned char*>(my_buffer) + rec);
         tq::peer_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
             records, flags, world, rows, rows_cap, exchange, reinterpret_cast<__half*>(output), num_q_heads,
-            num_kv_heads, head_dim);
+            num_kv_heads, head_dim, tq::g_wait_ns);
         tq::check_launch("peer merge");
         return 0;
     } catch (const std::exception& e) {
@@ -213,4 +215,14 @@ extern "C" int tq_peer_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tq::g_peer_status, sizeof v) != cudaSuccess) return -2;
     return v;
+}
+
+extern "C" int tq_peer_set_wait_ns(unsigned long long ns) {
+    tq::g_wait_ns = ns ? ns : tq::kDefaultWaitNs;
+    return 0;
+}
+
+extern "C" int tq_peer_clear_status(void) {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(tq::g_peer_status, &zero, sizeof zero) == cudaSuccess ? 0 : -2;
 }

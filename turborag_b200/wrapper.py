@@ -95,6 +95,8 @@ SIGNATURES = {
     "tq_peer_publish": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, _P]),
     "tq_peer_merge": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_uint, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tq_peer_status": (C.c_int, []),
+    "tq_peer_clear_status": (C.c_int, []),
+    "tq_peer_set_wait_ns": (C.c_int, [C.c_ulonglong]),
     "tq_block_table_create": (_P, [C.c_int, C.c_int]),
     "tq_block_table_destroy": (None, [_P]),
     "tq_block_table_free_pages": (C.c_int, [_P]),
@@ -403,6 +405,14 @@ class TurboQuantWrapper:
 
     def peer_status(self) -> int:
         return int(self._lib.tq_peer_status())
+
+    def peer_clear_status(self) -> None:
+        if self._lib.tq_peer_clear_status() != 0:
+            raise RuntimeError("tq_peer_clear_status failed")
+
+    def peer_set_wait_ns(self, ns: int) -> None:
+        """Bound of the flag wait in later ``peer_merge`` calls (0 = the default 2 s)."""
+        self._lib.tq_peer_set_wait_ns(int(ns))
 
     def mse_prefill_status(self) -> int:
         """0 when every bounded wait inside the prefill kernel was satisfied (synchronises)."""
