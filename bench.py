@@ -23,9 +23,21 @@ The JSON line carries
   roofline       decode kernel vs the measured HBM copy bandwidth (MEASURED_PEAKS.json);
   cpu_baseline   the CPU oracle (a port of the reference's kernels; the reference has no CPU
                  implementation of this path) on the box's host cores, bounded sample;
-  secondary      quantize-pack and dequant GB/s on the offline-store shape.
-With N > 1 (torchrun) every rank runs the whole workload on its own sequences (weak
+  secondary      quantize-pack and dequant GB/s on the offline-store shape (with the CPU oracle's
+                 quantiser and the reference's attention_ref_single_head timed beside them), chunk
+                 prefill TFLOP/s, and three sharded workloads measured at every N:
+                   decode_strong    the same 32 sequences dealt over the ranks (32/N each);
+                   longctx_kvsplit  28 layers, 28 q / 4 kv heads, 8 x 131072 tokens, every sequence's
+                                    KV range cut over the ranks, (acc, m, l) partials exchanged per
+                                    layer by peer stores and by an NCCL all-gather, LSE merge;
+                   store_sharded    36 layers x 64 documents x 8192 tokens dealt by (layer, document)
+                                    unit: pack (both schemes) and dequant into [head, token, dim].
+With N > 1 (torchrun) the headline runs the whole workload on every rank's own sequences (weak
 scaling, no data-path collective).
+
+--impl reference: the reference's own CUDA kernels (its only implementation of this path), driven
+through its own ctypes wrapper, when oracle/_ref holds them (make -C oracle ref); otherwise the CPU
+oracle port on the host cores.
 """
 from __future__ import annotations
 
@@ -157,9 +169,112 @@ def cpu_decode_sample(num_seqs, kv_tokens, hq, h, seed=0):
     return run, nbytes
 
 
+REF_DIR = ROOT / "oracle" / "_ref"
+
+
+def reference_gpu_arm(args):
+    """The reference's kernels, unmodified, through the reference's own ctypes wrapper (both built
+    from the reference checkout into oracle/_ref): tq_launch_turbo_prod_pack_kv builds the pages,
+    tq_launch_turbo_prod_fused_attention_output reads them, one call per sequence with the 8 query
+    rows per kv head of GQA 8:1 (it has no batched entry point).  A step = a bounded sample of the
+    workload's sequences for one layer.  Returns False when the reference build or a GPU is missing."""
+    if not ((REF_DIR / "libturboquant_ref.so").exists() and (REF_DIR / "tq_backend" / "turboquant_wrapper.pyc").exists()):
+        return False
+    import torch
+    if not torch.cuda.is_available():
+        return False
+    sys.path.insert(0, str(REF_DIR))
+    try:
+        from tq_backend.turboquant_wrapper import TurboQuantWrapper as RefWrapper
+    finally:
+        sys.path.remove(str(REF_DIR))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ref = RefWrapper(str(REF_DIR / "libturboquant_ref.so"))
+    N, HQ, H = args.kv_tokens, args.q_heads, args.kv_heads
+    G = HQ // H
+    num_seqs = max(1, min(args.batch, 2))
+    cfg = ref.default_config()
+    cfg.num_kv_heads, cfg.head_dim = H, 128
+    lay = ref.make_layout_for(cfg)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    pages = N // 16
+    t = torch.arange(N, device=dev)
+    pools, slots_l, qs = [], [], []
+    for b in range(num_seqs):
+        table = torch.randperm(pages, device=dev, generator=gen).to(torch.int32)
+        slots = (table[t // 16].to(torch.int64) * 16 + t % 16).to(torch.int32)
+        k, v = synth_kv(torch, N, H, dev, gen)
+        pool = torch.zeros(pages * lay.page_size_bytes, dtype=torch.uint8, device=dev)
+        ref.pack(k, v, slots, pool, lay, cfg)
+        pools.append(pool)
+        slots_l.append(slots)
+        # reference layout: row g of kv head h = query head h*G + g
+        qs.append(torch.randn(G, H, 128, device=dev, generator=gen).to(torch.float16))
+    outs = [torch.zeros_like(q) for q in qs]
+    host_pools = [p_.cpu().pin_memory() for p_ in pools]
+    out_host = torch.zeros(num_seqs, G, H, 128, dtype=torch.float16).pin_memory()
+    torch.cuda.synchronize()
+
+    def step():
+        for b in range(num_seqs):
+            ref.fused_attn_output(qs[b], pools[b], slots_l[b], outs[b], lay, cfg, G, N)
+
+    def step_e2e():
+        for b in range(num_seqs):
+            pools[b].copy_(host_pools[b], non_blocking=True)
+            ref.fused_attn_output(qs[b], pools[b], slots_l[b], outs[b], lay, cfg, G, N)
+            out_host[b].copy_(outs[b], non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    step_e2e()
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(args.steps, 5))
+    for _ in range(e2e_steps):
+        step_e2e()
+    t_e2e = (time.perf_counter() - t0) / e2e_steps
+    # slot mappings are per token in the reference API: 4 B per token instead of 4 B per page
+    nbytes = num_seqs * (N * H * 134 + N * 4)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    sample = (f"{num_seqs} of {args.batch} sequences x {N} tokens x 1 of {args.layers} layers per step, one "
+              f"tq_launch_turbo_prod_fused_attention_output call per sequence ({G} query rows x {H} kv heads)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": 0, "kind": "reference", "sample": sample,
+                         "device": "the same B200: the reference implements this path only as CUDA kernels "
+                                   "(compiled unmodified for sm_100), it has no CPU implementation"},
+        "e2e": {"value": nbytes / t_e2e / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": sum(p_.numel() for p_ in host_pools),
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": t_e2e * 1e3,
+                "note": "pages copied from pinned host memory before every call, outputs copied back"},
+        "gpu_launches": args.steps * num_seqs, "clocks": clocks,
+    }))
+    return True
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if reference_gpu_arm(args):
         return
     cores = host_threads()
     num_seqs = max(1, min(args.batch, 8))
@@ -195,26 +310,15 @@ def workload_name(args):
 # long-context decode with the KV sequence split across ranks (one exchange step per layer)
 # -------------------------------------------------------------------------------------
 
-def longctx(args):
-    """Qwen2.5-7B-shaped decode: 28 layers, 28 q / 4 kv heads, batch 8 x 131072 cached tokens in
-    turbo_prod pages.  Every rank holds the pages of its contiguous, page-aligned token range of
-    every sequence; per layer: local split-KV decode -> (acc, m, l) partials, one NCCL all-gather,
-    local log-sum-exp merge.  Strong scaling: the total work is fixed as ranks are added."""
-    import torch
-    import torch.distributed as dist
-
-    import turborag_b200
+def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges, steps, warmup):
+    """One measurement of the long-context decode with every sequence's KV range cut over the
+    ranks (strong scaling: the total work is fixed).  Every rank holds the pages of its contiguous,
+    page-aligned token range of every sequence; per layer: local split-KV decode -> (acc, m, l)
+    partials, exchange (peer stores over NVLink, or one NCCL all-gather), local log-sum-exp merge.
+    Returns {exchange: dict} for every name in `exchanges` ("peer", "nccl"; same on every rank):
+    whole-job GB/s, microseconds per layer, and the time of the local decode part alone (the same
+    launches without the exchange) for the share spent outside it."""
     from turborag_b200.parallel import gather_partials, kv_token_range
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    tq = turborag_b200.TurboQuantWrapper()
-    B, N, L, HQ, H = args.batch, args.kv_tokens, args.layers, args.q_heads, args.kv_heads
     cfg = tq.default_config()
     cfg.num_kv_heads = H
     lay = tq.make_layout_for(cfg)
@@ -241,12 +345,7 @@ def longctx(args):
     ws = torch.empty(max(tq.decode_workspace_bytes(B, HQ, N, cfg), 16), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
 
-    # partials travel by peer stores over NVLink (PeerExchange) unless --exchange nccl asks for the
-    # all-gather path
     xchg = None
-    if world > 1 and args.exchange == "peer":
-        from turborag_b200.parallel import PeerExchange
-        xchg = PeerExchange(tq, B * HQ, dev)
 
     def step():
         for l in range(L):
@@ -264,47 +363,94 @@ def longctx(args):
             allp = gather_partials(part) if world > 1 else part.view(1, B * HQ, 130)
             tq.merge_partials(allp, out[l].view(B * HQ, 128), HQ, H, stream=stream)
 
+    def step_local_only():
+        # the decode part of a layer alone: same kernels, partials stay on this GPU
+        for l in range(L):
+            tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
+                            partials_out=part.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo, kv_end=hi,
+                            workspace=ws, stream=stream)
+
     def sync_all():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    sync_all()
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    ms_local = timed(step_local_only)
+    total_bytes = L * B * (N * H * 134 + (N // 16) * 4)  # whole job, all ranks together
+    res = {}
+    for exchange in exchanges:
+        if world > 1 and exchange == "peer":
+            from turborag_b200.parallel import PeerExchange
+            xchg = PeerExchange(tq, B * HQ, dev)
+        else:
+            xchg = None
+        ms_per_step = timed(step)
+        status = tq.peer_status() if xchg is not None else 0
+        res[exchange] = {
+            "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_per_step,
+            "us_per_layer": ms_per_step * 1e3 / L, "us_per_layer_decode_only": ms_local * 1e3 / L,
+            "share_outside_decode": max(0.0, 1.0 - ms_local / ms_per_step),
+            "exchange": ("none (one rank)" if world == 1 else
+                         f"peer stores over NVLink ({xchg.how})" if xchg is not None else "one NCCL all-gather"),
+            "partials_bytes_per_rank_per_layer": B * HQ * 130 * 4, "peer_wait_status": status,
+            "scaling": "strong", "shape": f"b{B}_kv{N}_L{L}_q{HQ}kv{H}"}
+        if world == 1:
+            break  # one rank: nothing is exchanged, one measurement serves both names
+    return res
+
+
+def longctx(args):
+    """--workload longctx: the KV-split measurement as the headline of its own JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    import turborag_b200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tq = turborag_b200.TurboQuantWrapper()
+    B, N, L, HQ, H = args.batch, args.kv_tokens, args.layers, args.q_heads, args.kv_heads
     sampler = ClockSampler(local)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    sync_all()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    r = longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, (args.exchange,), args.steps, args.warmup)
+    r = next(iter(r.values()))
     clocks = sampler.stop()
-    ms_per_step = float(t.item()) / args.steps
-    total_bytes = L * B * (N * H * 134 + (N // 16) * 4)  # whole job, all ranks together
-    value = total_bytes / (ms_per_step * 1e-3) / 1e9
     peak, peak_kind = peaks()
-    per_rank = total_bytes / world / (ms_per_step * 1e-3) / 1e9
+    per_rank = r["value"] / world
     if rank == 0:
         print(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": workload_name(args), "global_batch": B, "kv_tokens": N, "layers": L,
                        "parallelism": (f"kv sequence split over {world} rank(s), {B * HQ * 130 * 4} B of partials per "
-                                       f"rank per layer exchanged by " +
-                                       (f"peer stores over NVLink ({xchg.how})" if xchg is not None
-                                        else "one NCCL all-gather") + ", local LSE merge"),
+                                       f"rank per layer exchanged by {r['exchange']}, local LSE merge"),
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": per_rank, "peak": peak, "unit": "GB/s",
                          "frac": per_rank / peak, "traffic": None, "peak_kind": peak_kind,
                          "kernel": "decode_paged16_kernel<turbo_prod> + partial exchange + merge, per rank"},
-            "gpu_launches": args.steps * L * 3, "clocks": clocks,
+            "detail": r, "gpu_launches": args.steps * L * 3, "clocks": clocks,
         }))
     if world > 1:
         dist.barrier()
@@ -459,8 +605,14 @@ def ours(args):
         out_host.copy_(out_dev, non_blocking=True)
         main.synchronize()
 
+    step_resident()
+    torch.cuda.synchronize()
+    layer0_resident = out_dev[0].clone()
     cold_steps = max(1, min(args.steps, 3))
     t_cold = wall(step_e2e_cold, cold_steps, 1)
+    # the cold loop sends one layer's pages (layer 0's) for every layer: its layer-0 output must be the
+    # resident run's, bit for bit
+    e2e_same = bool(torch.equal(out_host[0].to(dev), layer0_resident))
     h2d_cold = h2d_res + L * layer_bytes
 
     line = {
@@ -473,12 +625,16 @@ def ours(args):
                    "pct_of_measured_hbm": 100.0 * achieved / peak},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic,
+                     "traffic_source": "constant: one ncu capture of this kernel at half the batch, scaled by "
+                                       "the pages a launch reads (profiles/decode_turbo_prod_b16_kv32768.md); "
+                                       "not measured in this run",
                      "peak_kind": peak_kind, "kernel": "decode_paged16_kernel<turbo_prod,2>",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
                      "launch_ms": launch_ms,
                      "note": "launch_ms = timed region / decode launches; includes the merge kernel and launch gaps"},
         "e2e": {"value": world * bytes_per_step / t_cold / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": h2d_cold, "d2h_bytes_per_step": d2h, "ms_per_step": t_cold * 1e3,
+                "layer0_output_equals_resident_run": e2e_same,
                 "note": "compressed pages start in pinned host memory and are copied H2D per layer "
                         "inside the timed region (double-buffered against the decode kernel)"},
         "e2e_resident": {"value": world * bytes_per_step / t_res / 1e9, "unit": UNIT,
@@ -489,16 +645,51 @@ def ours(args):
         "tokens_per_s": world * B / (ms_per_step * 1e-3),
     }
 
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(
+            torch, tq, args, pools, tables, q_dev, out_dev, lay)
+    if not args.skip_secondary:
+        sec = {}
+        # ---- the same B sequences dealt over the ranks (strong scaling, no collective) ----------
+        if B % world == 0:
+            b_loc = B // world
+
+            def step_strong():
+                for l in range(L):
+                    tq.decode_paged("turbo_prod", q_dev[l][:b_loc], pools[l], tables[l][:b_loc], lens[:b_loc],
+                                    lay, cfg, output=out_dev[l][:b_loc], max_kv_tokens=N, workspace=ws,
+                                    stream=stream)
+            for _ in range(args.warmup):
+                step_strong()
+            sync_all()
+            e0.record()
+            for _ in range(args.steps):
+                step_strong()
+            e1.record()
+            sync_all()
+            ms_strong = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+            sec["decode_strong"] = {
+                "value": bytes_per_step / (ms_strong * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_strong,
+                "scaling": "strong", "sequences_total": B, "sequences_per_rank": b_loc,
+                "note": "config 3 with its 32 sequences in total: 32/N per rank, no collective"}
+        pools = staging = host_pool = tables_in = None  # free 10+ GB before the other workloads
+        torch.cuda.empty_cache()
+        if rank == 0:
+            sec.update(store_numbers(torch, tq, dev, gen, peak, cpu=(world == 1 and not args.skip_cpu)))
+        sec["store_sharded"] = store_sharded(torch, dist, tq, dev, rank, world, peak)
+        torch.cuda.empty_cache()
+        lc = longctx_measure(torch, dist, tq, dev, rank, world, 8, 131072, 28, 28, 4, ("peer", "nccl"),
+                             steps=max(2, min(args.steps, 5)), warmup=3)
+        sec["longctx_kvsplit"] = lc.get("peer") if world > 1 else next(iter(lc.values()))
+        if world > 1:
+            sec["longctx_kvsplit_nccl"] = lc.get("nccl")
+        torch.cuda.empty_cache()
+        if rank == 0 and world == 1:
+            sec["prefill_turbo_mse"] = prefill_numbers(torch, tq, dev, gen)
+            if not args.skip_cpu:
+                sec["cpu_attention_ref_single_head"] = cpu_attention_ref_numbers()
+        line["secondary"] = sec
     if rank == 0:
-        if world == 1 and not args.skip_cpu:
-            line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(
-                torch, tq, args, pools, tables, q_dev, out_dev, lay)
-        if not args.skip_secondary:
-            line["secondary"] = store_numbers(torch, tq, dev, gen, peak)
-            if world == 1:
-                pools = staging = host_pool = None  # free 10+ GB before the prefill case
-                torch.cuda.empty_cache()
-                line["secondary"]["prefill_turbo_mse"] = prefill_numbers(torch, tq, dev, gen)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -706,7 +897,134 @@ def load_numbers(torch, dev, gen, tokens, layers):
             "pool_bytes": pool_bytes, "note": "wall clock, best of 5, files in the page cache"}
 
 
-def store_numbers(torch, tq, dev, gen, peak):
+def store_sharded(torch, dist, tq, dev, rank, world, peak, layers=36, docs=64, tokens=8192, H=2, passes=3):
+    """Offline store build at its stated size: 36 layers x 64 documents x 8192 tokens, 2 kv heads.
+    The 2304 (layer, document) units are dealt to the ranks by parallel.shard_range (contiguous,
+    layer-major, no communication); a rank packs (turbo_prod and turbo_mse) and dequantises (both,
+    into fp16 [layer, head, token, dim]) the documents of a layer that fell to it with one launch per
+    kernel -- their pages are contiguous in the layer's pool, so a document's slice of it is byte
+    for byte the pool a per-document call writes.  GB/s of algorithmic bytes over the max-over-ranks
+    time of a pass.  Inputs: one set of 64 synthetic documents reused for every layer (268 MB per
+    tensor, larger than L2); outputs and pools are distinct memory for every unit."""
+    from turborag_b200.parallel import shard_range
+    cfg = tq.default_config()
+    cfg.num_kv_heads = H
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242)
+    k_all, v_all = synth_kv(torch, docs * tokens, H, dev, gen)
+    slots = torch.arange(docs * tokens, dtype=torch.int32, device=dev)
+    units = shard_range(layers * docs, rank, world)
+    runs = []  # (layer, first document, one past the last document) of this rank
+    for u in units:
+        l, d = divmod(u, docs)
+        if runs and runs[-1][0] == l and runs[-1][2] == d:
+            runs[-1][2] = d + 1
+        else:
+            runs.append([l, d, d + 1])
+    lays = {s: tq.layout_for_scheme(s, cfg) for s in ("turbo_prod", "turbo_mse")}
+    pools = {s: [torch.zeros((hi - lo) * (tokens // 16) * lays[s].page_size_bytes, dtype=torch.uint8, device=dev)
+                 for _, lo, hi in runs] for s in lays}
+    outs = [(torch.empty(H, (hi - lo) * tokens, 128, dtype=torch.float16, device=dev),
+             torch.empty(H, (hi - lo) * tokens, 128, dtype=torch.float16, device=dev)) for _, lo, hi in runs]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def one_pass():
+        for i, (_, lo, hi) in enumerate(runs):
+            n = (hi - lo) * tokens
+            k, v = k_all[lo * tokens:hi * tokens], v_all[lo * tokens:hi * tokens]
+            tq.pack(k, v, slots[:n], pools["turbo_prod"][i], lays["turbo_prod"], cfg, stream=stream)
+            tq.mse_pack(k, v, slots[:n], pools["turbo_mse"][i], lays["turbo_mse"], cfg, stream=stream)
+            for s in ("turbo_prod", "turbo_mse"):
+                tq.dequant_hnd(s, pools[s][i], slots[:n], outs[i][0], outs[i][1], lays[s], cfg, stream=stream)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    one_pass()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(passes):
+        one_pass()
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1) / passes], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    per_token = sum(2 * (2 * H * 128 * 2 + 4 + H * w) for w in (134, 132))  # pack + dequant, both schemes
+    total = layers * docs * tokens * per_token
+    gbs = total / (ms * 1e-3) / 1e9
+    return {"value": gbs, "unit": "GB/s", "ms_per_pass": ms, "scaling": "strong", "units": layers * docs,
+            "units_per_rank": len(units), "launches_per_rank_per_pass": 4 * len(runs),
+            "frac_of_hbm_peak_per_gpu": gbs / world / peak,
+            "shape": f"L{layers}_docs{docs}_x{tokens}_kv{H}", "ops": "pack turbo_prod + pack turbo_mse + dequant both into [head, token, dim]"}
+
+
+def cpu_pack_numbers(tokens=8192, H=2):
+    """The CPU oracle's quantiser (the port of the reference's pack kernels) on one store unit of
+    8192 tokens, on one thread and on all host cores (OpenMP over token-heads)."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    k = rng.standard_normal((tokens, H, 128)).astype(np.float32)
+    k[:, :, list(OUTLIERS)] *= 8
+    k = k.astype(np.float16)
+    v = rng.standard_normal((tokens, H, 128)).astype(np.float16)
+    slots = np.arange(tokens, dtype=np.int32)
+    cfg = O.make_config(H)
+    cores = host_threads()
+    res = {}
+    for scheme, w in (("turbo_prod", 134), ("turbo_mse", 132)):
+        nbytes = tokens * (2 * H * 128 * 2 + 4 + H * w)
+        for label, threads in (("all_cores", cores), ("one_thread", 1)):
+            O.set_threads(threads)
+            O.pack(scheme, k, v, slots, cfg)
+            reps, t0 = 0, time.perf_counter()
+            while reps < 3 or time.perf_counter() - t0 < 1.0:
+                O.pack(scheme, k, v, slots, cfg)
+                reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            res[f"{scheme}_{label}"] = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads}
+    O.set_threads(cores)
+    res["kind"] = "port"
+    res["sample"] = f"one (layer, document) unit: {tokens} tokens x {H} kv heads"
+    return res
+
+
+def cpu_attention_ref_numbers(n=32768, d=128, pairs=32):
+    """attention_ref_single_head (the reference's one CPU routine on this path: fp32 dense attention
+    of one query over one head's fp16 K/V), its own compiled code when oracle/_ref holds it (else the
+    oracle's restatement): one call on one thread, and `pairs` (sequence, head) calls spread over the
+    host cores by a thread pool.  Bytes = the fp16 K and V it reads (4 x 128 B per token)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from oracle import oracle as O
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal(d).astype(np.float16)
+    k = rng.standard_normal((n, d)).astype(np.float16)
+    v = rng.standard_normal((n, d)).astype(np.float16)
+    own = O.ref_host() is not None
+    fn = O.ref_attention_single_head if own else O.attention_ref_single_head
+    fn(q, k, v)
+    t0 = time.perf_counter()
+    fn(q, k, v)
+    one = time.perf_counter() - t0
+    cores = host_threads()
+    with ThreadPoolExecutor(max_workers=cores) as ex:
+        t0 = time.perf_counter()
+        list(ex.map(lambda _: fn(q, k, v), range(pairs)))
+        many = time.perf_counter() - t0
+    nbytes = n * d * 2 * 2
+    return {"one_thread": {"value": nbytes / one / 1e9, "unit": "GB/s of fp16 K/V", "cores": 1, "ms_per_head": one * 1e3},
+            "all_cores": {"value": pairs * nbytes / many / 1e9, "unit": "GB/s of fp16 K/V", "cores": min(cores, pairs)},
+            "kind": "reference" if own else "port",
+            "sample": f"{pairs} (sequence, head) pairs x {n} tokens x {d} dims, one query row each"}
+
+
+def store_numbers(torch, tq, dev, gen, peak, cpu=False):
     """quantize-pack and dequant GB/s on the offline-store shape: 16 documents x 8192 tokens of
     one layer (2 kv heads), permuted pages; inputs 2 x 67 MB, larger than L2."""
     H, n = 2, 16 * 8192
@@ -738,6 +1056,8 @@ def store_numbers(torch, tq, dev, gen, peak):
             gbs = by / (e0.elapsed_time(e1) / 10 * 1e-3) / 1e9
             res[f"{name}_{scheme}"] = {"value": gbs, "unit": "GB/s", "frac_of_hbm_peak": gbs / peak,
                                        "bytes_per_token": by // n}
+    if cpu:
+        res["cpu_baseline_pack"] = cpu_pack_numbers()
     return res
 
 
