@@ -178,16 +178,13 @@ def reference_gpu_arm(args):
     tq_launch_turbo_prod_fused_attention_output reads them, one call per sequence with the 8 query
     rows per kv head of GQA 8:1 (it has no batched entry point).  A step = a bounded sample of the
     workload's sequences for one layer.  Returns False when the reference build or a GPU is missing."""
-    if not ((REF_DIR / "libturboquant_ref.so").exists() and (REF_DIR / "tq_backend" / "turboquant_wrapper.pyc").exists()):
+    from oracle import ref_client
+    if not ((REF_DIR / "libturboquant_ref.so").exists() and ref_client.available()):
         return False
     import torch
     if not torch.cuda.is_available():
         return False
-    sys.path.insert(0, str(REF_DIR))
-    try:
-        from tq_backend.turboquant_wrapper import TurboQuantWrapper as RefWrapper
-    finally:
-        sys.path.remove(str(REF_DIR))
+    RefWrapper = ref_client.load()[0].TurboQuantWrapper
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

@@ -2,34 +2,26 @@
 
 `make -C oracle ref` byte-compiles the reference's ctypes wrapper and disk store
 (tq_backend/turboquant_wrapper.py, tq_backend/cag_store.py) into oracle/_ref/tq_backend/; here they
-are imported from there, given this library as `lib_path`, and taken through the checks of the
+are loaded from there (oracle/ref_client.py), given this library as `lib_path`, and taken through the checks of the
 reference's own GPU round-trip test (tests/test_cag.py:218-252: pack a document, load and
 dequantise it, shapes, dtypes, relative MSE below 0.35 / 0.25, manifest entry).  The files they
 wrote are then read by this package's store, and the other way round: same bytes, same tensors."""
 import json
-import sys
-from pathlib import Path
 
 import pytest
 import torch
 
-ROOT = Path(__file__).resolve().parent.parent
-REF_CLIENT = ROOT / "oracle" / "_ref"
+from oracle import ref_client
 
 pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(not (REF_CLIENT / "tq_backend" / "cag_store.pyc").exists(),
+              pytest.mark.skipif(not ref_client.available(),
                                  reason="oracle/_ref/tq_backend was not built (make -C oracle ref)")]
 
 ROUNDTRIP_TOL = {"turbo_prod": 0.35, "turbo_mse": 0.25}  # tests/test_cag.py:212-215
 
 
 def reference_store_class():
-    sys.path.insert(0, str(REF_CLIENT))
-    try:
-        from tq_backend.cag_store import CAGStore
-    finally:
-        sys.path.remove(str(REF_CLIENT))
-    return CAGStore
+    return ref_client.load()[1].CAGStore
 
 
 @pytest.mark.parametrize("scheme", ["turbo_prod", "turbo_mse"])

@@ -21,8 +21,10 @@
 //              synchronisation); every code byte becomes two fp16 operands with one shared-memory
 //              table lookup; K and V tiles are stored in the 128-byte-swizzled canonical operand
 //              layout (three stages); chunk tiles (fp16, rotated by a pre-pass) are copied instead.
-//   warp 12    one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128: 8 instructions, A and
-//              B K-major) into one of two TMEM buffers, and O += P V (M 128, N 128, K 64: 4
+//   warp 12    one thread issues tcgen05.mma: S = Q K^T (M 128, N 64, K 128, A = Q from TMEM, K-major
+//              B; 16 instructions: the rotated query rows live in tensor memory as two fp16 parts,
+//              q' = hi + lo, so S carries no fp16 rounding of q' and the tensor core never reads Q
+//              from shared memory) into one of two TMEM buffers, and O += P V (M 128, N 128, K 64: 4
 //              instructions, A = P from TMEM, V as MN-major B operand) into TMEM; tcgen05.commit arrives on
 //              mbarriers.  It issues whichever product has its operands ready, S up to two tiles
 //              ahead, so the tensor pipe works on the next scores during the current softmax.
@@ -51,9 +53,8 @@ constexpr float kRescaleLag = 8.0f;  // log2 units a row maximum may run ahead o
 
 // shared-memory map (bytes); every operand tile starts on a 1024-byte boundary
 constexpr int kOffLut = 0;                      // 256 rows x 32 replicas x half2 (128 B per row)
-constexpr int kOffQ = 32768;                    // [2 dim chunks][128 rows][128 B]
 constexpr int kKvStages = 3;
-constexpr int kOffKV = 65536;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
+constexpr int kOffKV = 32768;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
 constexpr int kOffScale = kOffKV + kKvStages * 32768;  // per K/V stage: kscale[64], vscale[64] (fp32)
 constexpr int kOffBar = kOffScale + 2048;       // mbarriers, TMEM base
 constexpr int kRawStages = 3;
@@ -205,8 +206,8 @@ __device__ int g_prefill_tc_status = 0;
 
 // ---- pre-pass: R(x) * scale for fp16 rows of 128, natural dim order --------------------------
 __global__ void __launch_bounds__(128)
-rotate_rows_tc_kernel(const __half* __restrict__ src, __half* __restrict__ dst, long long rows,
-                      int heads_mod, int group, float scale, int head_dim) {
+rotate_rows_tc_kernel(const __half* __restrict__ src, __half* __restrict__ dst, __half* __restrict__ dst_lo,
+                      long long rows, int heads_mod, int group, float scale, int head_dim) {
     const int lane = threadIdx.x & 31;
     const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -228,12 +229,21 @@ rotate_rows_tc_kernel(const __half* __restrict__ src, __half* __restrict__ dst, 
     const float c = inv_sqrt_dim(head_dim);
     const float sc = ((h & 1) ? -c : c) * scale;
     __half2* out = reinterpret_cast<__half2*>(dst + row * kHeadDim + 4 * lane);
-    out[0] = __floats2half2_rn(x[0] * sc, x[1] * sc);
-    out[1] = __floats2half2_rn(x[2] * sc, x[3] * sc);
+    const __half2 h0 = __floats2half2_rn(x[0] * sc, x[1] * sc), h1 = __floats2half2_rn(x[2] * sc, x[3] * sc);
+    out[0] = h0;
+    out[1] = h1;
+    if (dst_lo) {
+        // what the fp16 rounding dropped, as a second fp16 row: value = hi + lo to ~22 bits
+        const float2 f0h = __half22float2(h0), f1h = __half22float2(h1);
+        __half2* lo = reinterpret_cast<__half2*>(dst_lo + row * kHeadDim + 4 * lane);
+        lo[0] = __floats2half2_rn(x[0] * sc - f0h.x, x[1] * sc - f0h.y);
+        lo[1] = __floats2half2_rn(x[2] * sc - f1h.x, x[3] * sc - f1h.y);
+    }
 }
 
 struct PrefillTcParams {
-    const __half* q_rot;      // [B, Nq, Hq, 128] rotated, scaled
+    const __half* q_rot;      // [B, Nq, Hq, 128] rotated, scaled: fp16 part
+    const __half* q_rot_lo;   // the same rows: remainder of the fp16 rounding
     const __half* ck_rot;     // [B, Nq, H, 128] or nullptr
     const __half* cv_rot;
     const uint8_t* pool;
@@ -278,13 +288,6 @@ prefill_tc_kernel(PrefillTcParams p) {
         const uint32_t e = level4_half_bits(n0) | (level4_half_bits(n1) << 16);
         *reinterpret_cast<uint4*>(smem + kOffLut + row * 128 + (i & 7) * 16) = make_uint4(e, e, e, e);
     }
-    for (int i = tid; i < kRowsCta * 16; i += kThreadsTc) {
-        const int r = i >> 4, u = i & 15;
-        const int rg = min(mt * kRowsCta + r, rows_total - 1);
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
-            p.q_rot + ((static_cast<long long>(b) * p.nq + rg / G) * p.hq + h * G + rg % G) * kHeadDim) + u);
-        *reinterpret_cast<uint4*>(smem + kOffQ + (u >> 3) * 16384 + sw128(r, u & 7)) = v;
-    }
     fence_async_smem();
     if (tid == 0) {
         for (int k = 0; k < kKvStages; ++k) {
@@ -310,7 +313,35 @@ prefill_tc_kernel(PrefillTcParams p) {
     const uint32_t tmem = *tmem_slot;          // columns 0-63 / 64-127: S buffers, 128-255: O
     const uint32_t tmem_o = tmem + 128;
     const uint32_t tmem_p = tmem + 256;        // columns 256-287 / 288-319: P buffers (fp16 pairs)
+    const uint32_t tmem_q = tmem + 320;        // columns 320-383: Q hi, 384-447: Q lo (fp16 pairs along dims)
     int fail = 0;
+
+    // ---- the CTA's 128 query rows go to tensor memory once: lane = row, 32-bit column c = dims 2c, 2c+1.
+    // Warps 0-3 write the fp16 part of their 32 rows, warps 8-11 the remainder part of the same rows.
+    if (warp < 4 || (warp >= 8 && warp < 12)) {
+        const int r = (warp & 3) * 32 + lane;
+        const int rg = min(mt * kRowsCta + r, rows_total - 1);
+        const __half* src = (warp < 4 ? p.q_rot : p.q_rot_lo) +
+                            ((static_cast<long long>(b) * p.nq + rg / G) * p.hq + h * G + rg % G) * kHeadDim;
+        const uint32_t dst = tmem_q + (warp < 4 ? 0u : 64u) + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(src + 2 * c0) + u);
+                v[4 * u] = __uint_as_float(w.x);
+                v[4 * u + 1] = __uint_as_float(w.y);
+                v[4 * u + 2] = __uint_as_float(w.z);
+                v[4 * u + 3] = __uint_as_float(w.w);
+            }
+            tmem_st32(dst + c0, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     if ((warp >= 4 && warp < 8) || warp >= 13) {
         // =========================== unpack warps ===========================
@@ -448,7 +479,6 @@ prefill_tc_kernel(PrefillTcParams p) {
         if (lane == 0) {
             // Two counters: S tiles issued, P V tiles issued.  Whichever operand set is ready first
             // is issued first; S may run at most two tiles ahead of P V (two S buffers).
-            const uint32_t q_addr = sbase + kOffQ;
             int next_s = 0, next_pv = 0, idle = 0;
             while (next_pv < n_tiles) {
                 bool progress = false;
@@ -457,10 +487,10 @@ prefill_tc_kernel(PrefillTcParams p) {
                     tc_fence_after();
                     const uint32_t k_addr = sbase + kOffKV + (next_s % kKvStages) * 32768;
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        mma_f16_ss(tmem + 64 * (next_s & 1),
-                                   make_desc(q_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                                   make_desc(k_addr + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS, ks > 0);
+                    for (int ks = 0; ks < 16; ++ks)  // k-steps 0-7: Q hi, 8-15: Q lo against the same K tile
+                        mma_f16_ts(tmem + 64 * (next_s & 1), tmem_q + 8 * ks,
+                                   make_desc(k_addr + ((ks & 7) >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS,
+                                   ks > 0 ? 1u : 0u);
                     mma_commit(bar_s_full + 8 * (next_s & 1));
                     ++next_s;
                     progress = true;
@@ -673,29 +703,32 @@ void launch_prefill_tc(const void* query, const uint8_t* pool, const int32_t* bl
     const size_t part_bytes = static_cast<size_t>(q_rows) * splits * TQ_PARTIAL_STRIDE * sizeof(float);
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     uint8_t* ws = nullptr;
-    ws = static_cast<decltype(ws)>(scratch_alloc(up(q_bytes) + 2 * up(kv_bytes) + part_bytes, stream,
+    ws = static_cast<decltype(ws)>(scratch_alloc(2 * up(q_bytes) + 2 * up(kv_bytes) + part_bytes, stream,
                                                  "scratch_alloc(prefill workspace)"));
     __half* q_rot = reinterpret_cast<__half*>(ws);
-    __half* ck_rot = reinterpret_cast<__half*>(ws + up(q_bytes));
-    __half* cv_rot = reinterpret_cast<__half*>(ws + up(q_bytes) + up(kv_bytes));
-    float* partials = reinterpret_cast<float*>(ws + up(q_bytes) + 2 * up(kv_bytes));
+    __half* q_rot_lo = reinterpret_cast<__half*>(ws + up(q_bytes));
+    __half* ck_rot = reinterpret_cast<__half*>(ws + 2 * up(q_bytes));
+    __half* cv_rot = reinterpret_cast<__half*>(ws + 2 * up(q_bytes) + up(kv_bytes));
+    float* partials = reinterpret_cast<float*>(ws + 2 * up(q_bytes) + 2 * up(kv_bytes));
 
     const uint32_t alpha_bits = 0x404c9252u;
     float alpha;
     std::memcpy(&alpha, &alpha_bits, sizeof alpha);
     // q' = R(q) / sqrt(D) * log2(e) / alpha: the rotation's own 1/sqrt(D) is applied in the kernel
     rotate_rows_tc_kernel<<<static_cast<unsigned>((q_rows + 3) / 4), 128, 0, stream>>>(
-        static_cast<const __half*>(query), q_rot, q_rows, hq, G, kLog2eT / alpha * 0.08838834764831845f, head_dim);
+        static_cast<const __half*>(query), q_rot, q_rot_lo, q_rows, hq, G, kLog2eT / alpha * 0.08838834764831845f,
+        head_dim);
     check_launch("prefill rotate q");
     if (chunk_key) {
         rotate_rows_tc_kernel<<<static_cast<unsigned>((kv_rows + 3) / 4), 128, 0, stream>>>(
-            static_cast<const __half*>(chunk_key), ck_rot, kv_rows, H, 1, alpha, head_dim);
+            static_cast<const __half*>(chunk_key), ck_rot, nullptr, kv_rows, H, 1, alpha, head_dim);
         rotate_rows_tc_kernel<<<static_cast<unsigned>((kv_rows + 3) / 4), 128, 0, stream>>>(
-            static_cast<const __half*>(chunk_value), cv_rot, kv_rows, H, 1, alpha, head_dim);
+            static_cast<const __half*>(chunk_value), cv_rot, nullptr, kv_rows, H, 1, alpha, head_dim);
         check_launch("prefill rotate chunk");
     }
     PrefillTcParams p{};
     p.q_rot = q_rot;
+    p.q_rot_lo = q_rot_lo;
     p.ck_rot = chunk_key ? ck_rot : nullptr;
     p.cv_rot = chunk_key ? cv_rot : nullptr;
     p.pool = pool;
