@@ -81,24 +81,35 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
     const long long warps_total = static_cast<long long>(gridDim.x) * kDqWarps;
     constexpr bool al = ALIGNED8;
 
-    // Packed inputs of one row group for this lane; the next group's are fetched before the
-    // current one is expanded so that the dependent slot -> page -> code loads stay hidden.
+    // Packed inputs of one row group for this lane, software-pipelined two deep so that neither
+    // link of the dependent chain slot -> page -> codes is waited for: iteration i loads the slot of
+    // group i + 2, issues the page loads of group i + 1 (whose slot arrived during iteration i - 1)
+    // and expands group i.  Scales stay raw fp16 bits until they are used: a conversion placed next to
+    // its load would wait for the load inside the prefetch.
     struct Raw {
         uint2 kc, vc;
-        float ks, vs, re;
+        unsigned short ks, vs, re;
         long long out_row;
         int h;
         bool valid;
     };
-    auto fetch = [&](long long g, Raw& r) {
+    struct Slot {
+        long long row, tok;
+        int slot;
+        bool valid;
+    };
+    auto fetch_slot = [&](long long g, Slot& sl) {
         const long long row_raw = g * 4 + rr;
-        r.valid = row_raw < num_rows;
-        const long long row = r.valid ? row_raw : num_rows - 1;
-        const long long tok = index_div(row, div_heads);
-        r.h = static_cast<int>(row - tok * H);
-        const int slot = __ldg(slot_mapping + tok);
-        const int blk = index_div(slot, div_block);
-        const int tib = slot - blk * geo.block_size;
+        sl.valid = row_raw < num_rows;
+        sl.row = sl.valid ? row_raw : num_rows - 1;
+        sl.tok = index_div(sl.row, div_heads);
+        sl.slot = __ldg(slot_mapping + sl.tok);
+    };
+    auto fetch = [&](const Slot& sl, Raw& r) {
+        r.valid = sl.valid;
+        r.h = static_cast<int>(sl.row - sl.tok * H);
+        const int blk = index_div(sl.slot, div_block);
+        const int tib = sl.slot - blk * geo.block_size;
         const uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
         const unsigned int th = static_cast<unsigned int>(tib * H + r.h);
         if (QJL)  // 16 sign bits: dims 16l .. 16l+15
@@ -106,20 +117,32 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         else
             r.kc = load_codes(page + geo.k_codes + th * 64 + 8 * l, al);
         r.vc = load_codes(page + geo.v_codes + th * 64 + 8 * l, al);
-        r.ks = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.k_scales + th * 2)));
-        r.vs = __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.v_scales + th * 2)));
-        r.re = PROD ? __half2float(__ldg(reinterpret_cast<const __half*>(page + geo.k_res + th * 2))) : 0.0f;
-        r.out_row = hnd ? (static_cast<long long>(r.h) * num_tokens + tok) : row;
+        r.ks = __ldg(reinterpret_cast<const unsigned short*>(page + geo.k_scales + th * 2));
+        r.vs = __ldg(reinterpret_cast<const unsigned short*>(page + geo.v_scales + th * 2));
+        r.re = PROD ? __ldg(reinterpret_cast<const unsigned short*>(page + geo.k_res + th * 2)) : static_cast<unsigned short>(0);
+        r.out_row = hnd ? (static_cast<long long>(r.h) * num_tokens + sl.tok) : sl.row;
     };
+    auto widen = [](unsigned short bits) { return __half2float(__ushort_as_half(bits)); };
 
     long long g = static_cast<long long>(blockIdx.x) * kDqWarps + warp;
-    Raw cur;
-    if (g < groups) fetch(g, cur);
+    Raw cur{}, nxt{};
+    Slot s1{}, s2{};
+    if (g < groups) {
+        fetch_slot(g, s1);
+        fetch(s1, cur);
+    }
+    if (g + warps_total < groups) {
+        fetch_slot(g + warps_total, s1);
+        fetch(s1, nxt);
+    }
+    if (g + 2 * warps_total < groups) fetch_slot(g + 2 * warps_total, s2);
     for (; g < groups; g += warps_total) {
-        Raw nxt = cur;
-        if (g + warps_total < groups) fetch(g + warps_total, nxt);
+        // group i + 2: its slot was loaded an iteration ago, its page loads start now; group i + 3: slot
+        Raw nn = nxt;
+        if (g + 2 * warps_total < groups) fetch(s2, nn);
+        if (g + 3 * warps_total < groups) fetch_slot(g + 3 * warps_total, s2);
 
-        const float re = cur.re;
+        const float re = widen(cur.re), ks = widen(cur.ks), vs = widen(cur.vs);
         const int h = QJL ? 0 : cur.h;  // the QJL rotation has no head term (tq_qjl_kernels.cu:18-21)
         float2 x[8];
         auto level_k = [&](uint32_t nib) {
@@ -128,12 +151,12 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         };
         // K: rotated-domain values (tq_turbo_prod_kernels.cu:315-330 /
         // tq_turbo_mse_kernels.cu:150-156)
-        const float2 ks2 = make_float2(cur.ks, cur.ks), vs2 = make_float2(cur.vs, cur.vs);
+        const float2 ks2 = make_float2(ks, ks), vs2 = make_float2(vs, vs);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             if (QJL) {  // (bit ? +1 : -1) * ks   (tq_qjl_kernels.cu:235)
-                x[k] = make_float2((cur.kc.x >> (2 * k)) & 1u ? cur.ks : -cur.ks,
-                                   (cur.kc.x >> (2 * k + 1)) & 1u ? cur.ks : -cur.ks);
+                x[k] = make_float2((cur.kc.x >> (2 * k)) & 1u ? ks : -ks,
+                                   (cur.kc.x >> (2 * k + 1)) & 1u ? ks : -ks);
             } else {
                 const uint32_t b8 = ((k < 4 ? cur.kc.x : cur.kc.y) >> (8 * (k & 3))) & 0xFFu;
                 x[k] = mul2(make_float2(level_k(b8 & 0xFu), level_k(b8 >> 4)), ks2);
@@ -148,6 +171,7 @@ dequant_kv_kernel(const uint8_t* __restrict__ page_pool, const int32_t* __restri
         }
         inverse_and_store(x, buf, lane, c, h, out_value + cur.out_row * kHeadDim, cur.valid);
         cur = nxt;
+        nxt = nn;
     }
 }
 
