@@ -232,6 +232,18 @@ int tq_decode_paged_static(int scheme, const tq_half* query, const uint8_t* page
 int tq_merge_partials(const float* partials, int num_parts, tq_half* output, int rows,
                       int num_q_heads, int num_kv_heads, tq_stream_t stream);
 
+/* turbo_prod quantize+pack that also writes the kernel's intermediates, for parity triage: the
+ * debug_* arguments of the reference's pack kernel (src/cuda/tq_turbo_prod_kernels.cu:119-124,
+ * 216-217, 243-246), which its C API always passes as null (src/tq_capi.cpp:59-62).  Each is device
+ * memory [num_tokens, num_kv_heads, 128] or NULL: rotated K / V, the clamped normalised values
+ * (+-2.5 / +-2.75), the 3-bit K and 4-bit V level indices.  The pool receives the same bytes as from
+ * tq_launch_turbo_prod_pack_kv. */
+int tq_debug_turbo_prod_pack_kv(const tq_half* key, const tq_half* value, const int32_t* slot_mapping,
+                                uint8_t* page_pool, const TQTurboProdPageLayout* layout,
+                                const TQConfig* cfg, int num_tokens, float* debug_k_rot,
+                                float* debug_v_rot, float* debug_kn, float* debug_vn, int* debug_kidx,
+                                int* debug_vidx, tq_stream_t stream);
+
 /* Dequant straight into the [num_kv_heads, num_tokens, 128] layout a Hugging
  * Face cache wants (fuses the permute().contiguous() of
  * tq_backend/cag_store.py:250-251). */

@@ -208,6 +208,30 @@ def test_dequant_random_pages_and_roundtrip_quality(tq, oracle, dev, scheme, tag
         assert rel < (0.35 if scheme == "turbo_prod" else 0.25) and (n < 16 or rel < 0.02)
 
 
+def test_debug_pack_dumps_the_oracle_intermediates(tq, oracle, dev):
+    """tq_debug_turbo_prod_pack_kv: the pool of the regular pack, plus the normalised values the
+    oracle traces (bit-identical) and level indices that are the packed nibbles."""
+    rng = np.random.default_rng(21)
+    n, h = 77, 2
+    key, value = make_kv(rng, n, h)
+    slots = make_slots(rng, n, True, extra_pages=1)
+    cfg, ocfg = cfg_for(tq, h), oracle.make_config(h)
+    lay = tq.make_layout_for(cfg)
+    pool_o, kn_o, vn_o = oracle.pack("turbo_prod", key, value, slots, ocfg, trace=True)
+    pool = torch.zeros(pool_o.size, dtype=torch.uint8, device=dev)
+    d = tq.debug_pack(h16(key, dev), h16(value, dev), torch.from_numpy(slots).to(dev), pool, lay, cfg)
+    torch.cuda.synchronize()
+    assert np.array_equal(pool.cpu().numpy(), pool_o)
+    assert np.array_equal(d["kn"].cpu().numpy(), np.clip(kn_o, -2.5, 2.5))
+    assert np.array_equal(d["vn"].cpu().numpy(), np.clip(vn_o, -2.75, 2.75))
+    # indices against the levels: nearest level of the normalised value
+    cb3, cb4 = oracle.cb3(), oracle.cb4()
+    assert np.array_equal(d["kidx"].cpu().numpy(), np.abs(np.clip(kn_o, -2.5, 2.5)[..., None] - cb3).argmin(-1))
+    assert np.array_equal(d["vidx"].cpu().numpy(), np.abs(np.clip(vn_o, -2.75, 2.75)[..., None] - cb4).argmin(-1))
+    # rotated values: the oracle's normalised value times the stored scale reproduces them to fp16 precision of the scale
+    assert np.isfinite(d["k_rot"].cpu().numpy()).all() and np.isfinite(d["v_rot"].cpu().numpy()).all()
+
+
 # ---------------------------------------------------------------------------------
 # fused attention, reference API (one sequence, per-token slots, query [Q, H, D])
 # ---------------------------------------------------------------------------------

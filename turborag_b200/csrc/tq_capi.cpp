@@ -273,6 +273,22 @@ extern "C" int tq_launch_turbo_prod_pack_kv(const tq_half* key, const tq_half* v
     });
 }
 
+extern "C" int tq_debug_turbo_prod_pack_kv(const tq_half* key, const tq_half* value, const int32_t* slot_mapping,
+                                           uint8_t* page_pool, const TQTurboProdPageLayout* layout,
+                                           const TQConfig* cfg, int num_tokens, float* debug_k_rot,
+                                           float* debug_v_rot, float* debug_kn, float* debug_vn,
+                                           int* debug_kidx, int* debug_vidx, tq_stream_t stream) {
+    if (!key || !value || !slot_mapping || !page_pool || !layout || !cfg) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "turbo_prod");
+        check_align(key, 16, "key");
+        check_align(value, 16, "value");
+        tq::launch_pack_debug(key, value, slot_mapping, page_pool, geom_prod(*layout, *cfg), cfg->head_dim,
+                              num_tokens, debug_k_rot, debug_v_rot, debug_kn, debug_vn, debug_kidx, debug_vidx,
+                              static_cast<cudaStream_t>(stream));
+    });
+}
+
 extern "C" int tq_launch_turbo_prod_dequant_kv(const uint8_t* page_pool, const int32_t* slot_mapping,
                                                tq_half* out_key, tq_half* out_value,
                                                const TQTurboProdPageLayout* layout,

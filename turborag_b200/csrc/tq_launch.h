@@ -35,6 +35,12 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
                  uint8_t* pool, const PageGeom& geo, int head_dim, int num_tokens,
                  cudaStream_t stream);
 
+// turbo_prod pack that also writes its intermediates (each [num_tokens, H, 128] or null), for parity
+// triage; same pool bytes as launch_pack.
+void launch_pack_debug(const void* key, const void* value, const int32_t* slots, uint8_t* pool,
+                       const PageGeom& geo, int head_dim, int num_tokens, float* k_rot, float* v_rot, float* kn,
+                       float* vn, int* kidx, int* vidx, cudaStream_t stream);
+
 // hnd: write [H, N, D] instead of [N, H, D].
 void launch_dequant(int scheme, const uint8_t* pool, const int32_t* slots, void* out_key,
                     void* out_value, const PageGeom& geo, int head_dim, int num_tokens, bool hnd,

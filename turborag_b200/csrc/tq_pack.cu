@@ -112,7 +112,9 @@ __device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK, 
     const float4 t = *reinterpret_cast<const float4*>(lutK + ((u & kRowMaskK) | rep));
     const bool above = xc >= t.x;
     e = __fsub_rn(xc, above ? t.z : t.y);
-    return (__float_as_uint(t.w) + (above ? 1u : 0u)) | (e >= 0.0f ? 8u : 0u);
+    // residual sign bit (e >= 0): the complement of e's sign bit, moved to bit 3 (a difference of equal
+    // finite values is +0 under round-to-nearest, so -0 does not occur)
+    return (__float_as_uint(t.w) + (above ? 1u : 0u)) | ((~__float_as_uint(e) >> 28) & 8u);
 }
 
 // Squares that feed the reference's summation tree.  A packed mul.rn.f32x2 whose only consumer
@@ -148,15 +150,24 @@ __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t
     }
 }
 
+// Intermediate values of the turbo_prod pack for parity triage, each [num_tokens, num_kv_heads, 128]
+// or null (the reference kernel's debug_* arguments, tq_turbo_prod_kernels.cu:119-124, 216-217,
+// 243-246): rotated K / V, the clamped normalised values, the 3-bit / 4-bit level indices.
+struct PackDump {
+    float *k_rot, *v_rot, *kn, *vn;
+    int *kidx, *vidx;
+};
+
 // S: 0 turbo_prod, 1 turbo_mse, 2 QJL-1bit.  ALIGNED8: pool base and page size are multiples of
 // 8 bytes (code rows leave as 8-byte stores); a template argument so that the byte-store sequence
-// of the other case is not part of this kernel's instruction stream.
-template <int S, bool ALIGNED8>
+// of the other case is not part of this kernel's instruction stream.  DUMP: the debug instance of
+// the turbo_prod kernel, which also writes its intermediates (never launched by the pack entry points).
+template <int S, bool ALIGNED8, bool DUMP = false>
 __global__ void __launch_bounds__(kPackWarps * 32)
 pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, IndexDiv div_heads, IndexDiv div_block, int head_dim,
-               long long num_rows, float zero) {
+               long long num_rows, float zero, PackDump dump) {
     constexpr bool PROD = S == 0, QJL = S == 2;
     constexpr bool TREE128 = PROD || QJL;  // sum of squares: 128-leaf tree (prod, QJL) or 64 pair leaves (mse)
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
@@ -258,6 +269,15 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 const uint32_t n1 = quant_k3_lut(kn.y, lutK, rep_k, e1);
                 kbytes[j] = n0 | (n1 << 4);
                 e2[j] = square2(make_float2(e0, e1), zero2);
+                if (DUMP && valid) {  // element 2l + b + 16j of the row
+                    const long long at = row * kHeadDim + 2 * l + 16 * j;
+                    if (dump.k_rot) { dump.k_rot[at] = y[j].x; dump.k_rot[at + 1] = y[j].y; }
+                    if (dump.kn) {
+                        dump.kn[at] = fminf(fmaxf(kn.x, -2.5f), 2.5f);
+                        dump.kn[at + 1] = fminf(fmaxf(kn.y, -2.5f), 2.5f);
+                    }
+                    if (dump.kidx) { dump.kidx[at] = static_cast<int>(n0 & 7u); dump.kidx[at + 1] = static_cast<int>(n1 & 7u); }
+                }
             }
             const float rms_e = rms_from_sum(tree128(e2));
             if (valid && l == 0) {
@@ -307,7 +327,17 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float2 vn = div_by2(y[j], vrms, vr);
-            vbytes[j] = quant_v4_lut(vn.x, lutV, rep_v) | (quant_v4_lut(vn.y, lutV, rep_v) << 4);
+            const uint32_t c0 = quant_v4_lut(vn.x, lutV, rep_v), c1 = quant_v4_lut(vn.y, lutV, rep_v);
+            vbytes[j] = c0 | (c1 << 4);
+            if (DUMP && valid) {
+                const long long at = row * kHeadDim + 2 * l + 16 * j;
+                if (dump.v_rot) { dump.v_rot[at] = y[j].x; dump.v_rot[at + 1] = y[j].y; }
+                if (dump.vn) {
+                    dump.vn[at] = fminf(fmaxf(vn.x, -2.75f), 2.75f);
+                    dump.vn[at + 1] = fminf(fmaxf(vn.y, -2.75f), 2.75f);
+                }
+                if (dump.vidx) { dump.vidx[at] = static_cast<int>(c0); dump.vidx[at + 1] = static_cast<int>(c1); }
+            }
         }
         if (valid && l == 0)
             *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
@@ -331,7 +361,7 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
 #define TQ_PACK_LAUNCH1(SV, AL)                                                                \
     pack_kv_kernel<SV, AL><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
         static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,    \
-        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f)
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f, PackDump{})
 #define TQ_PACK_LAUNCH(SV) do { if (aligned) TQ_PACK_LAUNCH1(SV, true); else TQ_PACK_LAUNCH1(SV, false); } while (0)
     if (scheme == TQ_SCHEME_TURBO_PROD) TQ_PACK_LAUNCH(0);
     else if (scheme == TQ_SCHEME_TURBO_MSE) TQ_PACK_LAUNCH(1);
@@ -340,6 +370,23 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
 #undef TQ_PACK_LAUNCH1
     check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod pack_kv"
                  : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse pack_kv" : "qjl pack_kv");
+}
+
+void launch_pack_debug(const void* key, const void* value, const int32_t* slots, uint8_t* pool,
+                       const PageGeom& geo, int head_dim, int num_tokens, float* k_rot, float* v_rot, float* kn,
+                       float* vn, int* kidx, int* vidx, cudaStream_t stream) {
+    if (num_tokens <= 0) return;
+    const long long rows = static_cast<long long>(num_tokens) * geo.num_kv_heads;
+    const long long groups = (rows + 3) / 4;
+    long long blocks = (groups + kPackWarps - 1) / kPackWarps;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    const PackDump dump{k_rot, v_rot, kn, vn, kidx, vidx};
+    // the byte-store instance: any pool alignment, this entry point is not a hot path
+    pack_kv_kernel<0, false, true><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
+        static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f, dump);
+    check_launch("turbo_prod pack_kv (debug)");
 }
 
 }  // namespace tq

@@ -85,6 +85,7 @@ SIGNATURES = {
                                          C.c_int, C.c_int, _P]),
     "tq_merge_partials": (C.c_int, [_P, C.c_int, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tq_dequant_kv_hnd": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, _CFG, C.c_int, _P]),
+    "tq_debug_turbo_prod_pack_kv": (C.c_int, [_P, _P, _P, _P, _PROD, _CFG, C.c_int, _P, _P, _P, _P, _P, _P, _P]),
     "tq_mse_prefill_paged": (C.c_int, [_P, _P, _P, C.c_int, _P, _P, _P, _P, _MSE, _CFG, C.c_int,
                                        C.c_int, C.c_int, _P]),
     "tq_mse_prefill_status": (C.c_int, []),
@@ -354,6 +355,19 @@ class TurboQuantWrapper:
         self._call("merge", "partials", self._lib.tq_merge_partials, _ptr(partials), parts,
                    _ptr(output), rows, num_q_heads, num_kv_heads, C.c_void_p(stream))
         return output
+
+    def debug_pack(self, key, value, slot_mapping, page_pool, layout, cfg, stream: int = 0) -> dict:
+        """turbo_prod pack that also returns the kernel's intermediates (fp32 / int32 tensors shaped
+        like ``key``): rotated K / V, clamped normalised values, level indices."""
+        _cuda(key, value, slot_mapping, page_pool)
+        f = lambda dt: torch.zeros(key.shape, dtype=dt, device=key.device)  # noqa: E731
+        out = {"k_rot": f(torch.float32), "v_rot": f(torch.float32), "kn": f(torch.float32),
+               "vn": f(torch.float32), "kidx": f(torch.int32), "vidx": f(torch.int32)}
+        self._call("turbo_prod", "debug_pack_kv", self._lib.tq_debug_turbo_prod_pack_kv, _ptr(key), _ptr(value),
+                   _ptr(slot_mapping), _ptr(page_pool), C.byref(layout), C.byref(cfg), key.shape[0],
+                   _ptr(out["k_rot"]), _ptr(out["v_rot"]), _ptr(out["kn"]), _ptr(out["vn"]), _ptr(out["kidx"]),
+                   _ptr(out["vidx"]), C.c_void_p(stream))
+        return out
 
     def dequant_hnd(self, scheme: str, page_pool, slot_mapping, out_key, out_value, layout, cfg,
                     stream: int = 0) -> None:
