@@ -311,7 +311,8 @@ def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges
     """One measurement of the long-context decode with every sequence's KV range cut over the
     ranks (strong scaling: the total work is fixed).  Every rank holds the pages of its contiguous,
     page-aligned token range of every sequence; per layer: local split-KV decode -> (acc, m, l)
-    partials, exchange (peer stores over NVLink, or one NCCL all-gather), local log-sum-exp merge.
+    partials, exchange (peer stores over NVLink with the final merge inside the publishing kernel:
+    two launches per layer; or one NCCL all-gather and a merge launch), local log-sum-exp merge.
     Returns {exchange: dict} for every name in `exchanges` ("peer", "nccl"; same on every rank):
     whole-job GB/s, microseconds per layer, and the time of the local decode part alone (the same
     launches without the exchange) for the share spent outside it."""
@@ -348,11 +349,9 @@ def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges
         for l in range(L):
             if xchg is not None:
                 xchg.exchange += 1
-                tq.decode_paged_publish("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg, xchg.ptr_array,
-                                        rank, world, xchg.rows_cap, xchg.exchange, N, lo, hi, workspace=ws,
-                                        stream=stream)
-                tq.peer_merge(xchg.buf, world, B * HQ, xchg.rows_cap, xchg.exchange, out[l].view(B * HQ, 128),
-                              HQ, H, stream)
+                tq.decode_paged_exchange("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg, xchg.ptr_array,
+                                         rank, world, xchg.rows_cap, xchg.exchange, N, lo, hi, out[l],
+                                         workspace=ws, stream=stream)
                 continue
             tq.decode_paged("turbo_prod", q[l], pools[l], tables[l], lens, lay, cfg,
                             partials_out=part.view(B, HQ, 130), max_kv_tokens=N, kv_begin=lo, kv_end=hi,

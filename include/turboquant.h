@@ -289,6 +289,17 @@ int tq_decode_paged_publish(int scheme, const tq_half* query, const uint8_t* pag
                             int max_kv_tokens, int kv_begin, int kv_end, void* workspace,
                             size_t workspace_bytes, void* const* peer_buffers, int rank, int world,
                             int rows_cap, unsigned int exchange, tq_stream_t stream);
+/* tq_decode_paged_publish followed by tq_peer_merge as one call: this rank's token range is decoded,
+ * its records are stored into every peer's buffer, and output[rows][128] receives the merge of all
+ * ranks' records.  With at most 4 x (SM count) rows the publishing kernel waits for the peers' flags
+ * itself and finishes the merge (two launches per call instead of three); with more rows the
+ * stand-alone merge is launched behind it. */
+int tq_decode_paged_exchange(int scheme, const tq_half* query, const uint8_t* page_pool,
+                             const int32_t* block_tables, int table_stride, const int32_t* seq_lens,
+                             const void* layout, const TQConfig* cfg, int batch, int num_q_heads,
+                             int max_kv_tokens, int kv_begin, int kv_end, void* workspace,
+                             size_t workspace_bytes, void* const* peer_buffers, int rank, int world,
+                             int rows_cap, unsigned int exchange, tq_half* output, tq_stream_t stream);
 int tq_peer_publish(const float* local_partials, void* const* peer_buffers, int rank, int world,
                     int rows, int rows_cap, unsigned int exchange, tq_stream_t stream);
 int tq_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange,

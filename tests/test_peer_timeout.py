@@ -42,3 +42,33 @@ def test_peer_merge_wait_runs_out_and_the_context_survives(tq):
     torch.cuda.synchronize()
     assert tq.peer_status() == 0
     assert torch.equal(out, want)
+
+
+def test_fused_exchange_with_one_rank_equals_plain_decode(tq, oracle):
+    """tq_decode_paged_exchange (decode, publish, wait, final merge in two launches) with a world of one
+    rank: the same bits as tq_decode_paged, twice in a row (both buffer parities, the self-resetting
+    ticket)."""
+    import numpy as np
+
+    from tests.test_zz_no_alloc import _case
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(8)
+    lens, hq, h = [900, 333], 28, 4
+    pool, tables = _case(oracle, "turbo_prod", rng, lens, h)
+    cfg = tq.default_config()
+    cfg.num_kv_heads = h
+    lay = tq.make_layout_for(cfg)
+    q = torch.from_numpy(rng.standard_normal((2, hq, 128)).astype(np.float16).view(np.int16)).to(dev).view(torch.float16)
+    args = ("turbo_prod", q, torch.from_numpy(pool).to(dev), torch.from_numpy(tables).to(dev),
+            torch.tensor(lens, dtype=torch.int32, device=dev), lay, cfg)
+    want = tq.decode_paged(*args, max_kv_tokens=max(lens))
+    rows = 2 * hq
+    buf = torch.zeros(tq.peer_buffer_bytes(1, rows), dtype=torch.uint8, device=dev)
+    ptrs = (C.c_void_p * 1)(buf.data_ptr())
+    tq.peer_clear_status()
+    for exchange in (1, 2, 3):
+        out = torch.full_like(want, 5.0)
+        tq.decode_paged_exchange(*args, ptrs, 0, 1, rows, exchange, max(lens), 0, max(lens), out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    assert tq.peer_status() == 0

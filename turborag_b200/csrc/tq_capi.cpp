@@ -537,6 +537,69 @@ extern "C" int tq_decode_paged_publish(int scheme, const tq_half* query, const u
     });
 }
 
+extern "C" int tq_decode_paged_exchange(int scheme, const tq_half* query, const uint8_t* page_pool,
+                                        const int32_t* block_tables, int table_stride,
+                                        const int32_t* seq_lens, const void* layout, const TQConfig* cfg,
+                                        int batch, int num_q_heads, int max_kv_tokens, int kv_begin,
+                                        int kv_end, void* workspace, size_t workspace_bytes,
+                                        void* const* peer_buffers, int rank, int world, int rows_cap,
+                                        unsigned int exchange, tq_half* output, tq_stream_t stream) {
+    if (!query || !page_pool || !block_tables || !seq_lens || !layout || !cfg || !peer_buffers || !output) return -1;
+    return guarded([&] {
+        check_shape(*cfg, "decode_paged_exchange");
+        check_align(query, 8, "query");
+        check_align(output, 4, "output");
+        if (batch < 0 || num_q_heads < 1 || max_kv_tokens < 0 || table_stride < 0)
+            throw std::runtime_error("decode_paged_exchange: negative size");
+        if (static_cast<long long>(table_stride) * cfg->block_size < max_kv_tokens)
+            throw std::runtime_error("decode_paged_exchange: block table narrower than max_kv_tokens");
+        const long long rows = static_cast<long long>(batch) * num_q_heads;
+        if (world < 1 || world > 8 || rank < 0 || rank >= world || rows > rows_cap)
+            throw std::runtime_error("decode_paged_exchange: bad rank / world / rows_cap");
+        if (rows == 0) return;
+        tq::DecodeArgs a{};
+        a.scheme = scheme;
+        a.query = query;
+        a.pool = page_pool;
+        a.block_tables = block_tables;
+        a.table_stride = table_stride;
+        a.seq_lens = seq_lens;
+        a.geo = geom_for(scheme, layout, *cfg);
+        a.head_dim = cfg->head_dim;
+        a.batch = batch;
+        a.num_q_heads = num_q_heads;
+        a.ref_query_layout = 0;
+        a.max_kv_tokens = max_kv_tokens;
+        a.kv_begin = kv_begin;
+        a.kv_end = kv_end;
+        a.workspace = workspace;
+        a.workspace_bytes = workspace_bytes;
+        const size_t rec = (size_t(2) * world * rows_cap * TQ_PARTIAL_STRIDE * sizeof(float) + 255) / 256 * 256;
+        for (int q = 0; q < world; ++q) {
+            if (!peer_buffers[q]) throw std::runtime_error("decode_paged_exchange: null peer buffer");
+            a.peer.records[q] = static_cast<float*>(peer_buffers[q]);
+            a.peer.flags[q] = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(peer_buffers[q]) + rec);
+        }
+        a.peer.ticket = a.peer.flags[rank] + 2 * world;
+        a.peer.world = world;
+        a.peer.rank = rank;
+        a.peer.rows_cap = rows_cap;
+        a.peer.exchange = exchange;
+        // The publishing kernel finishes the exchange itself when all of its CTAs are resident at once
+        // (they wait for a flag that its own last CTA raises): at most one CTA per row, eight warps each.
+        const bool fused = rows <= 4ll * tq::sm_count();
+        if (fused) {
+            a.peer.final_out = output;
+            a.peer.wait_ns = tq::peer_wait_ns();
+            a.peer.status = tq::peer_status_ptr();
+        }
+        tq::launch_decode(a, static_cast<cudaStream_t>(stream));
+        if (!fused)
+            tq::launch_peer_merge(peer_buffers[rank], world, static_cast<int>(rows), rows_cap, exchange, output,
+                                  num_q_heads, cfg->num_kv_heads, cfg->head_dim, static_cast<cudaStream_t>(stream));
+    });
+}
+
 extern "C" int tq_merge_partials(const float* partials, int num_parts, tq_half* output, int rows,
                                  int num_q_heads, int num_kv_heads, tq_stream_t stream) {
     if (!partials || !output) return -1;

@@ -1211,6 +1211,77 @@ merge_kernel(const float* __restrict__ partials, int num_parts, long long part_s
                                  "r"(peer.exchange) : "memory");
             }
         }
+        if (!peer.final_out) return;
+        // Finish the exchange here: wait (bounded) until every rank's records of this exchange have
+        // landed in this rank's own buffer, then merge them for this CTA's rows.  The host only asks for
+        // this when the whole grid is resident at once (the own flag is raised by the last CTA).
+        if (threadIdx.x == 0) {
+            const unsigned int* mine = peer.flags[peer.rank] + (peer.exchange & 1u) * peer.world;
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+            bool bad = false;
+            for (int q = 0; q < peer.world && !bad; ++q) {
+                while (true) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + q) : "memory");
+                    if (v == peer.exchange) break;
+                    unsigned long long t1;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                    if (t1 - t0 > peer.wait_ns) {
+                        bad = true;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            if (bad) atomicMax(peer.status, 1);
+        }
+        __syncthreads();
+        if (row >= rows || sub != 0) return;
+        {
+            // the arithmetic of the stand-alone peer merge: records read through L2 (peer stores do not
+            // pass this GPU's L1), ranks in order
+            const long long part_stride_w = static_cast<long long>(peer.rows_cap) * TQ_PARTIAL_STRIDE;
+            const float* base = peer.records[peer.rank] +
+                                static_cast<long long>(peer.exchange & 1u) * peer.world * part_stride_w +
+                                static_cast<long long>(row) * TQ_PARTIAL_STRIDE;
+            float mmax = kInitMaxLogit;
+            for (int s = 0; s < peer.world; ++s) mmax = fmaxf(mmax, __ldcg(base + s * part_stride_w + 128));
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+            for (int s = 0; s < peer.world; ++s) {
+                const float* ps = base + s * part_stride_w;
+                const float w = __expf(__ldcg(ps + 128) - mmax);
+                l = fmaf(__ldcg(ps + 129), w, l);
+                const float2 v0 = __ldcg(reinterpret_cast<const float2*>(ps + 4 * lane));
+                const float2 v1 = __ldcg(reinterpret_cast<const float2*>(ps + 4 * lane + 2));
+                acc[0] = fmaf(v0.x, w, acc[0]);
+                acc[1] = fmaf(v0.y, w, acc[1]);
+                acc[2] = fmaf(v1.x, w, acc[2]);
+                acc[3] = fmaf(v1.y, w, acc[3]);
+            }
+            const int G = num_q_heads / num_kv_heads;
+            const int h = (row % rows_per_seq) / G;
+            const float inv_l = l > 0.0f ? 1.0f / l : 1.0f;  // tq_turbo_prod_kernels.cu:561-564
+            float x[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] = acc[e] * inv_l;
+            const float a0 = x[0] + x[1], a1 = x[0] - x[1], a2 = x[2] + x[3], a3 = x[2] - x[3];
+            x[0] = a0 + a2; x[2] = a0 - a2; x[1] = a1 + a3; x[3] = a1 - a3;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, x[e], m);
+                    x[e] = (lane & m) ? ov - x[e] : x[e] + ov;
+                }
+            }
+            const float c = inv_sqrt_dim(head_dim);
+            const float s0 = (h & 1) ? -c : c;
+            __half2* dst = reinterpret_cast<__half2*>(static_cast<__half*>(peer.final_out) +
+                                                      static_cast<long long>(row) * kHeadDim + 4 * lane);
+            dst[0] = __floats2half2_rn(x[0] * s0, x[1] * -s0);
+            dst[1] = __floats2half2_rn(x[2] * s0, x[3] * -s0);
+        }
         return;
     }
     if (row >= rows) return;

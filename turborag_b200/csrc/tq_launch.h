@@ -54,7 +54,21 @@ struct PeerOut {
     unsigned int* ticket;
     int world, rank, rows_cap;
     unsigned int exchange;
+    // Optional: finish the exchange in the publishing kernel itself.  After a CTA has stored its rows'
+    // records it waits (at most wait_ns) until every rank's flag in this rank's own buffer shows
+    // `exchange`, merges the world records of its rows and writes fp16 final_out[row][128]; a wait that
+    // runs out sets *status to 1.  Null final_out: the caller merges with tq_peer_merge.
+    void* final_out;
+    unsigned long long wait_ns;
+    int* status;
 };
+// Bound of the peer flag waits (tq_peer_set_wait_ns) and the device address of the status word
+// tq_peer_status reads, for launches outside tq_peer.cu that wait for peers.
+unsigned long long peer_wait_ns();
+int* peer_status_ptr();
+// Stand-alone merge of the records that arrived in this rank's buffer (what tq_peer_merge launches).
+void launch_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange, void* output,
+                       int num_q_heads, int num_kv_heads, int head_dim, cudaStream_t stream);
 
 struct DecodeArgs {
     int scheme;                   // TQ_SCHEME_*

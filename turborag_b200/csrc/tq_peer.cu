@@ -151,6 +151,34 @@ peer_merge_kernel(const float* __restrict__ records, const unsigned int* __restr
 }
 
 }  // namespace
+
+unsigned long long peer_wait_ns() { return g_wait_ns; }
+
+void launch_peer_merge(const void* my_buffer, int world, int rows, int rows_cap, unsigned int exchange, void* output,
+                       int num_q_heads, int num_kv_heads, int head_dim, cudaStream_t stream) {
+    if (rows == 0) return;
+    const size_t rec = (size_t(2) * world * rows_cap * TQ_PARTIAL_STRIDE * sizeof(float) + 255) / 256 * 256;
+    const float* records = static_cast<const float*>(my_buffer);
+    const unsigned int* flags =
+        reinterpret_cast<const unsigned int*>(static_cast<const unsigned char*>(my_buffer) + rec);
+    peer_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(records, flags, world, rows, rows_cap, exchange,
+                                                          static_cast<__half*>(output), num_q_heads, num_kv_heads,
+                                                          head_dim, g_wait_ns);
+    check_launch("peer merge");
+}
+
+int* peer_status_ptr() {
+    static int* ptrs[64] = {};
+    int dev = 0;
+    check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64) throw std::runtime_error("peer exchange: device index out of range");
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        check_cuda(cudaGetSymbolAddress(&p, g_peer_status), "cudaGetSymbolAddress(peer status)");
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
 }  // namespace tq
 
 extern "C" size_t tq_peer_buffer_bytes(int world, int rows_cap) {
@@ -195,15 +223,8 @@ extern "C" int tq_peer_merge(const void* my_buffer, int world, int rows, int row
         if (world < 1 || world > tq::kMaxPeers || rows < 0 || rows > rows_cap || head_dim != 128 ||
             num_kv_heads < 1 || num_q_heads % num_kv_heads != 0 || rows % num_q_heads != 0)
             throw std::runtime_error("peer_merge: bad shape");
-        if (rows == 0) return 0;
-        const size_t rec = (size_t(2) * world * rows_cap * TQ_PARTIAL_STRIDE * sizeof(float) + 255) / 256 * 256;
-        const float* records = static_cast<const float*>(my_buffer);
-        const unsigned int* flags =
-            reinterpret_cast<const unsigned int*>(static_cast<const unsigned char*>(my_buffer) + rec);
-        tq::peer_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-            records, flags, world, rows, rows_cap, exchange, reinterpret_cast<__half*>(output), num_q_heads,
-            num_kv_heads, head_dim, tq::g_wait_ns);
-        tq::check_launch("peer merge");
+        tq::launch_peer_merge(my_buffer, world, rows, rows_cap, exchange, output, num_q_heads, num_kv_heads,
+                              head_dim, static_cast<cudaStream_t>(stream));
         return 0;
     } catch (const std::exception& e) {
         tq::set_last_error(e.what());

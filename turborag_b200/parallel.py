@@ -125,16 +125,15 @@ def decode_kv_split_peer(xchg: PeerExchange, scheme, query, page_pool, block_tab
                          cfg, max_kv_tokens: int, output: torch.Tensor, workspace=None,
                          stream: int = 0) -> torch.Tensor:
     """``decode_kv_split`` with the partials exchanged by peer stores instead of an all-gather:
-    decode kernel, split merge that stores the records into every peer's buffer, merge of the
-    records that arrived here -- three launches, no collective."""
+    decode kernel, then a split merge that stores the records into every peer's buffer, waits for
+    the peers' flags and merges the records that arrived here -- two launches, no collective (three
+    for batches too large for that kernel's grid to be resident at once)."""
     tq = xchg.tq
     b, hq, _ = query.shape
     rows = b * hq
     begin, end = kv_token_range(max_kv_tokens, xchg.rank, xchg.world, cfg.block_size)
     xchg.exchange += 1
-    tq.decode_paged_publish(scheme, query, page_pool, block_tables, seq_lens, layout, cfg, xchg.ptr_array,
-                            xchg.rank, xchg.world, xchg.rows_cap, xchg.exchange, max_kv_tokens, begin, end,
-                            workspace=workspace, stream=stream)
-    tq.peer_merge(xchg.buf, xchg.world, rows, xchg.rows_cap, xchg.exchange, output.view(rows, -1), hq,
-                  cfg.num_kv_heads, stream)
+    tq.decode_paged_exchange(scheme, query, page_pool, block_tables, seq_lens, layout, cfg, xchg.ptr_array,
+                             xchg.rank, xchg.world, xchg.rows_cap, xchg.exchange, max_kv_tokens, begin, end,
+                             output, workspace=workspace, stream=stream)
     return output

@@ -93,6 +93,9 @@ SIGNATURES = {
     "tq_decode_paged_publish": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _CFG, C.c_int, C.c_int,
                                           C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, C.c_int, C.c_int,
                                           C.c_int, C.c_uint, _P]),
+    "tq_decode_paged_exchange": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, _P, _P, _CFG, C.c_int, C.c_int,
+                                           C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P, C.c_int, C.c_int,
+                                           C.c_int, C.c_uint, _P, _P]),
     "tq_peer_publish": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, _P]),
     "tq_peer_merge": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_uint, _P, C.c_int, C.c_int, C.c_int, _P]),
     "tq_peer_status": (C.c_int, []),
@@ -410,6 +413,20 @@ class TurboQuantWrapper:
                    C.cast(C.byref(layout), C.c_void_p), C.byref(cfg), b, hq, max_kv_tokens, kv_begin, kv_end,
                    _ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(),
                    C.cast(peer_ptrs, C.c_void_p), rank, world, rows_cap, exchange, C.c_void_p(stream))
+
+    def decode_paged_exchange(self, scheme, query, page_pool, block_tables, seq_lens, layout, cfg, peer_ptrs,
+                              rank: int, world: int, rows_cap: int, exchange: int, max_kv_tokens: int,
+                              kv_begin: int, kv_end: int, output, workspace=None, stream: int = 0) -> None:
+        """Decode this rank's token range, publish the records to every peer and merge all ranks'
+        records into ``output`` ([B, Hq, 128] fp16) -- the publishing kernel finishes the exchange
+        itself when the batch is small enough for its grid to be resident at once."""
+        _cuda(query, page_pool, block_tables, seq_lens, workspace, output)
+        b, hq, _ = query.shape
+        self._call(scheme, "decode_paged_exchange", self._lib.tq_decode_paged_exchange, SCHEME_ID[scheme],
+                   _ptr(query), _ptr(page_pool), _ptr(block_tables), block_tables.shape[1], _ptr(seq_lens),
+                   C.cast(C.byref(layout), C.c_void_p), C.byref(cfg), b, hq, max_kv_tokens, kv_begin, kv_end,
+                   _ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(),
+                   C.cast(peer_ptrs, C.c_void_p), rank, world, rows_cap, exchange, _ptr(output), C.c_void_p(stream))
 
     def peer_merge(self, my_buffer, world: int, rows: int, rows_cap: int, exchange: int, output,
                    num_q_heads: int, num_kv_heads: int, stream: int = 0) -> None:
