@@ -52,9 +52,10 @@ constexpr int kWaitLimit = 1 << 20;
 constexpr float kRescaleLag = 8.0f;  // log2 units a row maximum may run ahead of the one in use
 
 // shared-memory map (bytes); every operand tile starts on a 1024-byte boundary
-constexpr int kOffLut = 0;                      // 256 rows x 32 replicas x half2 (128 B per row)
+constexpr int kOffLut = 0;                      // 256 rows of 256 B: 32 replicas x half2 in the first 128 B of a row,
+                                                // so that a lookup address is one byte permute (byte << 8 | lane * 4)
 constexpr int kKvStages = 3;
-constexpr int kOffKV = 32768;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
+constexpr int kOffKV = 65536;                   // stage s: K [2][64][128 B] at +32768 s, V behind it
 constexpr int kOffScale = kOffKV + kKvStages * 32768;  // per K/V stage: kscale[64], vscale[64] (fp32)
 constexpr int kOffBar = kOffScale + 2048;       // mbarriers, TMEM base
 constexpr int kRawStages = 3;
@@ -140,6 +141,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (ok) return true;
     }
     return false;
+}
+// One poll that the hardware may suspend for up to `ns` nanoseconds while the phase is incomplete.
+__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
 }
 // Non-blocking test of the same condition.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
@@ -286,7 +295,7 @@ prefill_tc_kernel(PrefillTcParams p) {
     for (int i = tid; i < 256 * 8; i += kThreadsTc) {
         const uint32_t row = i >> 3, n0 = row & 15u, n1 = row >> 4;
         const uint32_t e = level4_half_bits(n0) | (level4_half_bits(n1) << 16);
-        *reinterpret_cast<uint4*>(smem + kOffLut + row * 128 + (i & 7) * 16) = make_uint4(e, e, e, e);
+        *reinterpret_cast<uint4*>(smem + kOffLut + row * 256 + (i & 7) * 16) = make_uint4(e, e, e, e);
     }
     fence_async_smem();
     if (tid == 0) {
@@ -348,7 +357,7 @@ prefill_tc_kernel(PrefillTcParams p) {
         const int u = warp < 8 ? tid - 128 : tid - 288;   // 0..255
         const int ut = u & 63, uq = u >> 6;   // token of the tile, 16-byte quarter of its 64 code bytes
         const int uh = uq >> 1;               // dim chunk (64 dims) the quarter belongs to
-        const uint32_t lane_v = static_cast<uint32_t>(lane) * 8u;  // table address = (byte << 8 | lane * 8) >> 1
+        const uint32_t lane_v = static_cast<uint32_t>(lane) * 4u;  // table address = byte << 8 | lane * 4
         const int32_t* table = p.block_tables + static_cast<long long>(b) * p.table_stride;
         // Page bytes travel global -> shared with cp.async, two tiles ahead, into a ring of
         // three raw stages (an HBM round trip is longer than a tile takes, and loads parked in
@@ -406,10 +415,10 @@ prefill_tc_kernel(PrefillTcParams p) {
             uint32_t o[16];
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
-                o[4 * wi + 0] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5504u) >> 1));
-                o[4 * wi + 1] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5514u) >> 1));
-                o[4 * wi + 2] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5524u) >> 1));
-                o[4 * wi + 3] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + (prmt_t(w[wi], lane_v, 0x5534u) >> 1));
+                o[4 * wi + 0] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w[wi], lane_v, 0x5504u));
+                o[4 * wi + 1] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w[wi], lane_v, 0x5514u));
+                o[4 * wi + 2] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w[wi], lane_v, 0x5524u));
+                o[4 * wi + 3] = *reinterpret_cast<const uint32_t*>(smem + kOffLut + prmt_t(w[wi], lane_v, 0x5534u));
             }
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi)
@@ -511,8 +520,13 @@ prefill_tc_kernel(PrefillTcParams p) {
                 if (progress) {
                     idle = 0;
                 } else {
-                    // a tight polling loop would take issue slots from the warps of this scheduler
-                    __nanosleep(100);
+                    // a tight polling loop would take issue slots from the warps of this scheduler: sleep in
+                    // the barrier unit on the condition that comes first in a steady pipeline (the P tile of
+                    // the oldest open product, else the next K/V tile), at most a microsecond at a time
+                    if (next_pv < next_s)
+                        mbar_try_wait_for(bar_p_full + 8 * (next_pv & 1), (next_pv >> 1) & 1, 1000u);
+                    else
+                        mbar_try_wait_for(bar_kv_full + 8 * (next_s % kKvStages), (next_s / kKvStages) & 1, 1000u);
                     if (++idle > kWaitLimit) {
                         fail = 2;
                         break;
