@@ -649,11 +649,13 @@ def ours(args):
         # ---- the same B sequences dealt over the ranks (strong scaling, no collective) ----------
         if B % world == 0:
             b_loc = B // world
+            # fewer sequences are split more ways: the split partials need their own, larger workspace
+            ws_loc = torch.empty(max(tq.decode_workspace_bytes(b_loc, HQ, N, cfg), 16), dtype=torch.uint8, device=dev)
 
             def step_strong():
                 for l in range(L):
                     tq.decode_paged("turbo_prod", q_dev[l][:b_loc], pools[l], tables[l][:b_loc], lens[:b_loc],
-                                    lay, cfg, output=out_dev[l][:b_loc], max_kv_tokens=N, workspace=ws,
+                                    lay, cfg, output=out_dev[l][:b_loc], max_kv_tokens=N, workspace=ws_loc,
                                     stream=stream)
             for _ in range(args.warmup):
                 step_strong()
