@@ -75,15 +75,24 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms.
+
+    The query process takes a moment to come up (longer on a box with many GPUs), so it is started
+    ahead of the warm-up, `begin()` / `end()` mark the loaded window, and only rows that arrive
+    inside it are used.  A timed region shorter than a few sampling periods is followed by an
+    untimed continuation of the same loop (`hold_load`) so that the window still holds samples
+    taken under that load."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    MIN_WINDOW_MS = 400.0
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.rows = []
         self.proc = None
+        self.t0 = self.t1 = None
+        self.window = "timed region"
 
     def start(self):
         try:
@@ -93,19 +102,47 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
+
+    def wait_ready(self, timeout_s: float = 8.0):
+        """Returns once the first row has arrived (or the time is up)."""
+        t_end = time.monotonic() + timeout_s
+        while self.proc is not None and not self.rows and time.monotonic() < t_end:
+            time.sleep(0.02)
+
+    def begin(self):
+        self.t0 = time.monotonic()
+
+    def end(self):
+        self.t1 = time.monotonic()
+
+    def hold_load(self, total_ms: float, ms_per_step: float, step, sync):
+        """Closes the window; if the timed region was short, first keeps `step` running (untimed,
+        the same count on every rank) until the window is MIN_WINDOW_MS long."""
+        if self.proc is not None and total_ms < self.MIN_WINDOW_MS:
+            n = int(min(5000, max(1, np.ceil((self.MIN_WINDOW_MS - total_ms) / max(ms_per_step, 1e-3)))))
+            for _ in range(n):
+                step()
+            sync()
+            self.window = f"timed region + {n} untimed steps of the same loop"
+        self.end()
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        time.sleep(0.25)
+        if self.t1 is None:
+            self.end()
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
+        t0 = self.t0 if self.t0 is not None else 0.0
+        for t, r in self.rows:
+            if not t0 <= t <= self.t1:
+                continue
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -115,7 +152,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm),
+                "window": self.window}
 
 
 def synth_kv(torch, n, h, dev, gen):
@@ -226,19 +264,21 @@ def reference_gpu_arm(args):
             out_host[b].copy_(outs[b], non_blocking=True)
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local).start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.wait_ready()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.begin()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
+    sampler.hold_load(ms * args.steps, ms, step, torch.cuda.synchronize)
+    clocks = sampler.stop()
     step_e2e()
     t0 = time.perf_counter()
     e2e_steps = max(1, min(args.steps, 5))
@@ -307,7 +347,7 @@ def workload_name(args):
 # long-context decode with the KV sequence split across ranks (one exchange step per layer)
 # -------------------------------------------------------------------------------------
 
-def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges, steps, warmup):
+def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges, steps, warmup, sampler=None):
     """One measurement of the long-context decode with every sequence's KV range cut over the
     ranks (strong scaling: the total work is fixed).  Every rank holds the pages of its contiguous,
     page-aligned token range of every sequence; per layer: local split-KV decode -> (acc, m, l)
@@ -372,11 +412,15 @@ def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn):
+    def timed(fn, clocks=None):
         for _ in range(warmup):
             fn()
+        if clocks is not None:
+            clocks.wait_ready()
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if clocks is not None:
+            clocks.begin()
         e0.record()
         for _ in range(steps):
             fn()
@@ -385,7 +429,10 @@ def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges
         t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) / steps
+        total = float(t.item())
+        if clocks is not None:
+            clocks.hold_load(total, total / steps, fn, sync_all)
+        return total / steps
 
     ms_local = timed(step_local_only)
     total_bytes = L * B * (N * H * 134 + (N // 16) * 4)  # whole job, all ranks together
@@ -396,7 +443,7 @@ def longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, exchanges
             xchg = PeerExchange(tq, B * HQ, dev)
         else:
             xchg = None
-        ms_per_step = timed(step)
+        ms_per_step = timed(step, sampler if exchange == exchanges[0] else None)
         status = tq.peer_status() if xchg is not None else 0
         res[exchange] = {
             "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_per_step,
@@ -427,9 +474,9 @@ def longctx(args):
         dist.init_process_group("nccl", device_id=dev)
     tq = turborag_b200.TurboQuantWrapper()
     B, N, L, HQ, H = args.batch, args.kv_tokens, args.layers, args.q_heads, args.kv_heads
-    sampler = ClockSampler(local)
-    sampler.start()
-    r = longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, (args.exchange,), args.steps, args.warmup)
+    sampler = ClockSampler(local).start()
+    r = longctx_measure(torch, dist, tq, dev, rank, world, B, N, L, HQ, H, (args.exchange,), args.steps, args.warmup,
+                        sampler=sampler)
     r = next(iter(r.values()))
     clocks = sampler.stop()
     peak, peak_kind = peaks()
@@ -525,20 +572,22 @@ def ours(args):
     traffic = DECODE_DRAM_TRAFFIC_PER_LAUNCH if default_shape else None
 
     # ---- value: pages resident, device-timed ------------------------------------------
+    sampler = ClockSampler(local).start()
     for _ in range(args.warmup):
         step_resident()
+    sampler.wait_ready()
     sync_all()
-    sampler = ClockSampler(local)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.begin()
     e0.record()
     for _ in range(args.steps):
         step_resident()
     e1.record()
     sync_all()
     total_ms = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop()
     ms_per_step = total_ms / args.steps
+    sampler.hold_load(total_ms, ms_per_step, step_resident, sync_all)
+    clocks = sampler.stop()
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
     launch_ms = total_ms / (args.steps * L)
     achieved = bytes_per_launch / (launch_ms * 1e-3) / 1e9
