@@ -108,8 +108,19 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// (a & b) ^ c and (a & m) | (b & ~m) as ONE three-input logic instruction each.  Written as the
+// instruction: left to the compiler, expressions of this kind with two constant operands came out
+// as two or more operations (measured: 72 logic instructions per 16-token block for the residual
+// signs where 32 suffice).
 __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
-    return (a & b) ^ c;  // one LOP3
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t lop3_select(uint32_t a, uint32_t b, uint32_t m) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(d) : "r"(a), "r"(b), "r"(m));
+    return d;
 }
 // x >> N as the high word of x * 2^(32-N): runs on the multiply-add pipe, which the unpack
 // leaves idle, instead of the half-rate integer/logic pipe that limits this kernel.
@@ -610,8 +621,8 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
             for (int w = 0; w < 2; ++w) {
                 const uint32_t wa = w ? cur.v[2 * pr].y : cur.v[2 * pr].x;          // token 2tig (+8)
                 const uint32_t wb = w ? cur.v[2 * pr + 1].y : cur.v[2 * pr + 1].x;  // token 2tig+1 (+8)
-                ilo[pr][w] = (wa & kLoNib) | (shl_mul<4>(wb) & ~kLoNib);
-                ihi[pr][w] = (shr_mul<4>(wa) & kLoNib) | (wb & ~kLoNib);
+                ilo[pr][w] = lop3_select(wa, shl_mul<4>(wb), kLoNib);
+                ihi[pr][w] = lop3_select(shr_mul<4>(wa), wb, kLoNib);
             }
         }
 #pragma unroll
@@ -911,6 +922,18 @@ static_assert(kFastWarpBytes >= kWarpSmemBytes, "the merge record reuses the rin
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
+// The same with immediate byte offsets on both addresses.
+template <int DST_OFF, int SRC_OFF>
+__device__ __forceinline__ void cp_async16_at(uint32_t dst_smem, unsigned long long src) {
+    asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;" ::"r"(dst_smem), "l"(src), "n"(DST_OFF),
+                 "n"(SRC_OFF) : "memory");
+}
+// a * b + c with 32-bit a, b and a 64-bit c: one instruction on the multiply-add pipe
+__device__ __forceinline__ unsigned long long mad_wide(uint32_t a, uint32_t b, unsigned long long c) {
+    unsigned long long d;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -974,13 +997,10 @@ decode_paged16_kernel(DecodeParams p) {
     auto v_piece = [](int t, int c) {
         return 1024 + 128 * ((t & 1) + 2 * (t >> 3) + 4 * (c >> 1)) + 32 * ((t >> 1) & 3) + 16 * (c & 1);
     };
-    uint32_t v_src[2], v_dst[2], v_rd[4];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int i = lane + 32 * k, t = i >> 2, c = i & 3;
-        v_src[k] = p.geo.v_codes + ((t * H + h) << 6) + (c << 4);
-        v_dst[k] = v_piece(t, c);
-    }
+    // the lane's two V pieces are tokens t and t + 8 of chunk c: 512*H bytes apart in the page, 256 in the stage
+    uint32_t v_rd[4];
+    const uint32_t v_off = p.geo.v_codes + (((lane >> 2) * H + h) << 6) + ((lane & 3) << 4);
+    const uint32_t v_dst = v_piece(lane >> 2, lane & 3);
 #pragma unroll
     for (int j = 0; j < 4; ++j)
         v_rd[j] = v_piece(2 * tig + (j & 1) + 8 * (j >> 1), g >> 1) + 8 * (g & 1);
@@ -1012,18 +1032,27 @@ decode_paged16_kernel(DecodeParams p) {
         ids = it < n_iter ? __ldg(table + it * kStreams) : 0;
         ids_base = it0;
     };
+    // Address arithmetic of a fill, spelled out: one wide multiply-add gives the page's address, one
+    // more per distinct in-page offset adds the lane's 32-bit offset, the second piece of a pair is an
+    // immediate offset of the copy instruction (written as generic 64-bit pointer arithmetic the fill
+    // of one block cost ~90 instructions).
+    const uint32_t page_size32 = static_cast<uint32_t>(p.geo.page_size);
+    const unsigned long long pool64 = reinterpret_cast<unsigned long long>(p.pool);
+    const uint32_t lane16 = lane * 16;
     auto issue = [&](int it, uint32_t dst) {
         if (it < n_iter) {
             if (it - ids_base >= 32) refill(it);
-            const int page = __shfl_sync(0xffffffffu, ids, it - ids_base);
-            const uint8_t* src = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
-            const uint8_t* ks = src + k_off;
-            cp_async16(dst + lane * 16, ks);
-            cp_async16(dst + 512 + lane * 16, ks + 512 * H);
-            cp_async16(dst + v_dst[0], src + v_src[0]);
-            cp_async16(dst + v_dst[1], src + v_src[1]);
-            if (sc_on[0]) cp_async16(dst + sc_dst[0], src + sc_src[0]);
-            if (kRegions * kPiecesPerRegion > 32 && sc_on[1]) cp_async16(dst + sc_dst[1], src + sc_src[1]);
+            const uint32_t page = static_cast<uint32_t>(__shfl_sync(0xffffffffu, ids, it - ids_base));
+            const unsigned long long src = mad_wide(page, page_size32, pool64);
+            const unsigned long long ks = mad_wide(k_off, 1u, src);
+            cp_async16_at<0, 0>(dst + lane16, ks);
+            cp_async16_at<512, 512 * H>(dst + lane16, ks);
+            const unsigned long long vs = mad_wide(v_off, 1u, src);
+            cp_async16_at<0, 0>(dst + v_dst, vs);
+            cp_async16_at<256, 512 * H>(dst + v_dst, vs);
+            if (sc_on[0]) cp_async16_at<0, 0>(dst + sc_dst[0], mad_wide(sc_src[0], 1u, src));
+            if (kRegions * kPiecesPerRegion > 32 && sc_on[1])
+                cp_async16_at<0, 0>(dst + sc_dst[1], mad_wide(sc_src[1], 1u, src));
         }
         cp_async_commit();  // one group per iteration, empty or not, keeps the count uniform
     };
