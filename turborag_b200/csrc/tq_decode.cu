@@ -22,6 +22,7 @@
 // Arithmetic: rotated-domain dot products in fp16 x fp16 -> fp32, softmax state
 // and accumulators in fp32 (within 2e-3 of the reference's fp32 path).
 #include <climits>
+#include <type_traits>
 #include <mutex>
 
 #include "tq_common.cuh"
@@ -420,7 +421,7 @@ __device__ __forceinline__ uint32_t sign_half2(uint32_t nw) {
     return (lo & 0x8000u) | (hi & 0x80000000u) | 0x3C003C00u;
 }
 
-template <bool PROD, int MODE, bool LUT = false, bool QJL = false, bool SIGNQ = false>
+template <bool PROD, int MODE, bool LUT = false, bool QJL = false, bool SIGNQ = false, bool RAGGED = true>
 __device__ __forceinline__ void process_block(const DecodeParams& p, const BlockCtx& c,
                                               const BlockRaw& cur, int tb, int t_end,
                                               WarpState& st) {
@@ -549,7 +550,7 @@ __device__ __forceinline__ void process_block(const DecodeParams& p, const Block
         return;
     }
 
-    if (tb + 16 > t_end) {  // only the last block of a sequence can be ragged
+    if (RAGGED && tb + 16 > t_end) {  // only the last block of a sequence can be ragged
         if (!ok0) lg[0] = lg[1] = -INFINITY;
         if (!ok1) lg[2] = lg[3] = -INFINITY;
     }
@@ -1061,8 +1062,13 @@ decode_paged16_kernel(DecodeParams p) {
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) issue(s, ring_addr + s * kStageBytes);
 
-    int stage = 0;  // stage holding iteration `it`
-    for (int it = 0; it < n_iter; ++it) {
+    int stage = 0;  // stage holding the iteration in hand
+    int tb = r.t_begin + 16 * (r.blk_lo + r.stream);
+    // One ring step and one block.  `ragged` is a compile-time tag: only the last block of the token
+    // range can end inside its 16 tokens, so the loop proper runs without the masking code and that
+    // block, if this warp owns it, runs once through a second copy.
+    auto step = [&](int it, auto ragged) {
+        constexpr bool kRagged = decltype(ragged)::value;
         const int fill = stage == 0 ? kStages - 1 : stage - 1;  // (it + kStages - 1) % kStages
         // Two orders of the same ring step.  turbo_mse pages (less arithmetic per byte) want the
         // refill in flight before the warp waits for block `it`.  turbo_prod pages are served
@@ -1076,7 +1082,6 @@ decode_paged16_kernel(DecodeParams p) {
         __syncwarp();  // pieces are copied by other lanes
         if constexpr (kRefillAfterWait) issue(it + kStages - 1, ring_addr + fill * kStageBytes);
         const uint8_t* stg = ring + stage * kStageBytes;
-        const int tb = r.t_begin + 16 * (r.blk_lo + r.stream + it * kStreams);
         BlockRaw cur;
         cur.k0 = *reinterpret_cast<const uint4*>(stg + lane * 16);
         cur.k1 = *reinterpret_cast<const uint4*>(stg + 512 + lane * 16);
@@ -1093,16 +1098,21 @@ decode_paged16_kernel(DecodeParams p) {
         cur.vs1 = ld(256 + 16 * H);
         cur.re0 = PROD ? ld(512) : 0.0f;
         cur.re1 = PROD ? ld(512 + 16 * H) : 0.0f;
-        if (tb + 16 > r.t_end) {
+        if (kRagged) {
             // rows past the end of the sequence may hold anything: zero their scales so that
             // P * vs stays finite (their logits are masked to -inf in process_block)
             if (tb + g >= r.t_end) cur.ks0 = cur.vs0 = cur.re0 = 0.0f;
             if (tb + g + 8 >= r.t_end) cur.ks1 = cur.vs1 = cur.re1 = 0.0f;
         }
-        process_block<PROD, 0, true, false, kSignQ>(p, ctx, cur, tb, r.t_end, st);
+        process_block<PROD, 0, true, false, kSignQ, kRagged>(p, ctx, cur, tb, r.t_end, st);
         if constexpr (!kRefillAfterWait) __syncwarp();  // every lane is done reading this stage before it is refilled
         stage = stage == kStages - 1 ? 0 : stage + 1;
-    }
+        tb += 16 * kStreams;
+    };
+    const bool last_ragged = n_iter > 0 && tb + 16 * kStreams * (n_iter - 1) + 16 > r.t_end;
+    const int n_full = last_ragged ? n_iter - 1 : n_iter;
+    for (int it = 0; it < n_full; ++it) step(it, std::false_type{});
+    if (last_ragged) step(n_full, std::true_type{});
     cp_async_wait<0>();
     decode_epilogue(p, kFastWarpBytes, ctx, r, st);
 }
