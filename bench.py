@@ -63,7 +63,7 @@ FALLBACK_HBM_GBS = 6650.0
 # per-layer shape. Captured with ncu at half the batch (141.06 MB read + 5.09 MB written for
 # 140.6 MB of pages) and scaled by the pages one launch reads: every page is read once, so
 # traffic grows in proportion. Only valid for the default shape; other shapes report null.
-DECODE_DRAM_TRAFFIC_PER_LAUNCH = 2 * (141.06e6 + 5.09e6)
+DECODE_DRAM_TRAFFIC_PER_LAUNCH = 2 * (141.06e6 + 4.15e6)
 OUTLIERS = (3, 17, 64, 101)
 
 
