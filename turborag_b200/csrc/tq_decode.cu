@@ -929,12 +929,6 @@ __device__ __forceinline__ void cp_async16_at(uint32_t dst_smem, unsigned long l
     asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;" ::"r"(dst_smem), "l"(src), "n"(DST_OFF),
                  "n"(SRC_OFF) : "memory");
 }
-// a * b + c with 32-bit a, b and a 64-bit c: one instruction on the multiply-add pipe
-__device__ __forceinline__ unsigned long long mad_wide(uint32_t a, uint32_t b, unsigned long long c) {
-    unsigned long long d;
-    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
-    return d;
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -10,6 +10,8 @@
 // The QJL-1bit scheme (qjl_pack_kv_kernel, src/cuda/tq_qjl_kernels.cu:69-170) is the third
 // instance of the same kernel: K keeps one sign bit per rotated dimension and the row's RMS, V
 // is quantised as in turbo_prod, and the rotation has no per-head sign.
+#include <climits>
+#include <stdexcept>
 #include "tq_common.cuh"
 #include "tq_launch.h"
 
@@ -51,9 +53,22 @@ __device__ __forceinline__ float next_up_of_negated(float n) {  // smallest floa
     return -__uint_as_float(__float_as_uint(n) - 1u);
 }
 
-// lutV row c: 16 x (threshold, code below it); lutK row c: 8 x (threshold, level below, level
-// above, code below).
-__device__ void build_luts(uint8_t* lutK, uint8_t* lutV, bool need_k) {
+// (a & b) | c as one three-input logic instruction (table row addresses).
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// lutV row c: 16 x (threshold, code below it).
+// The K nibble (residual sign << 3 | 3-bit code) is a step function of the clamped value with 15
+// thresholds: the 7 decision thresholds of the code and the 8 levels themselves (the residual
+// e = x - level is >= 0 exactly when x >= level).  They are at least 0.2449 apart, so a cell of
+// width 3/16 still holds at most one.  lutK1 row c: 16 x (threshold in the cell or +inf, byte
+// offset into lutK2 of the interval below it, this replica's offset included); lutK2: for interval
+// i (0..15 = number of thresholds <= x) a pair of 128-byte rows, the second one serving "x >= the
+// cell's threshold", each 16 x (level, nibble).
+__device__ void build_luts(uint8_t* lutK1, uint8_t* lutK2, uint8_t* lutV, bool need_k) {
     const float v4[15] = {next_up_of_negated(TQ_V4_N7), next_up_of_negated(TQ_V4_N6),
                           next_up_of_negated(TQ_V4_N5), next_up_of_negated(TQ_V4_N4),
                           next_up_of_negated(TQ_V4_N3), next_up_of_negated(TQ_V4_N2),
@@ -76,23 +91,34 @@ __device__ void build_luts(uint8_t* lutK, uint8_t* lutV, bool need_k) {
         for (int r = 0; r < 16; ++r) row[r] = make_float2(t, __int_as_float(base));
     }
     if (!need_k) return;
+    // all 15 thresholds in ascending order: level j sits between code thresholds j - 1 and j
+    float th[15];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        th[2 * j] = lv3[j];
+        if (j < 7) th[2 * j + 1] = k3[j];
+    }
     for (int c = threadIdx.x; c < kCellsK; c += blockDim.x) {
         float t = inf;
-        int base = 0;
+        int below = 0;
 #pragma unroll
-        for (int j = 0; j < 7; ++j) {
-            const int cj = static_cast<int>(cell_k(k3[j]));
-            if (cj < c) ++base;
-            if (cj == c) t = k3[j];
+        for (int j = 0; j < 15; ++j) {
+            const int cj = static_cast<int>(cell_k(th[j]));
+            if (cj < c) ++below;
+            if (cj == c) t = th[j];
         }
-        float lo = lv3[0], hi = lv3[0];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (j == base) lo = lv3[j];
-            if (j == (base < 7 ? base + 1 : 7)) hi = lv3[j];
-        }
-        float4* row = reinterpret_cast<float4*>(lutK + c * kLutRowBytes);
-        for (int r = 0; r < 8; ++r) row[r] = make_float4(t, lo, hi, __int_as_float(base));
+        float2* row = reinterpret_cast<float2*>(lutK1 + c * kLutRowBytes);
+        for (int r = 0; r < 16; ++r) row[r] = make_float2(t, __int_as_float(below * 256 + r * 8));
+    }
+    for (int i = threadIdx.x; i < 32; i += blockDim.x) {
+        // interval i / 2 + i % 2 (the last pair's second row is never addressed: no threshold above th[14])
+        const int iv = min((i >> 1) + (i & 1), 15);
+        // interval iv lies in [th[iv - 1], th[iv]): its code is the number of code thresholds at or below it,
+        // its residual is non-negative when its lower end is the level itself (odd number of thresholds below)
+        const int code = iv >> 1;
+        const int nibble = code | ((iv & 1) ? 8 : 0);
+        float2* row = reinterpret_cast<float2*>(lutK2 + i * kLutRowBytes);
+        for (int r = 0; r < 16; ++r) row[r] = make_float2(lv3[code], __int_as_float(nibble));
     }
 }
 
@@ -100,21 +126,23 @@ __device__ void build_luts(uint8_t* lutK, uint8_t* lutV, bool need_k) {
 // `rep` = (lane % 16) * 8, this lane's replica inside a row.
 __device__ __forceinline__ uint32_t quant_v4_lut(float x, const uint8_t* lutV, uint32_t rep) {
     const uint32_t u = __float_as_uint(__fmaf_rn(x, kCellScale, kMagicV));
-    const float2 e = *reinterpret_cast<const float2*>(lutV + ((u & kRowMaskV) | rep));
+    const float2 e = *reinterpret_cast<const float2*>(lutV + lop3_and_or(u, kRowMaskV, rep));
     return __float_as_uint(e.y) + (x >= e.x ? 1u : 0u);
 }
 
-// K nibble = residual sign << 3 | 3-bit code, and the residual e = clamp(kn) - level.
-// `rep` = (lane % 8) * 16.
-__device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK, uint32_t rep, float& e) {
+// K nibble = residual sign << 3 | 3-bit code, and the residual e = clamp(kn) - level: two table
+// steps, the comparison result (all ones or zero) picks the second row of the interval pair.
+// `rep` = (lane % 16) * 8.
+__device__ __forceinline__ uint32_t quant_k3_lut(float kn, const uint8_t* lutK1, const uint8_t* lutK2, uint32_t rep,
+                                                 float& e) {
     const float xc = fminf(fmaxf(kn, -2.5f), 2.5f);
     const uint32_t u = __float_as_uint(__fmaf_rn(xc, kCellScale, kMagicK));
-    const float4 t = *reinterpret_cast<const float4*>(lutK + ((u & kRowMaskK) | rep));
-    const bool above = xc >= t.x;
-    e = __fsub_rn(xc, above ? t.z : t.y);
-    // residual sign bit (e >= 0): the complement of e's sign bit, moved to bit 3 (a difference of equal
-    // finite values is +0 under round-to-nearest, so -0 does not occur)
-    return (__float_as_uint(t.w) + (above ? 1u : 0u)) | ((~__float_as_uint(e) >> 28) & 8u);
+    const float2 c = *reinterpret_cast<const float2*>(lutK1 + lop3_and_or(u, kRowMaskK, rep));
+    uint32_t ge;
+    asm("set.ge.u32.f32 %0, %1, %2;" : "=r"(ge) : "f"(xc), "f"(c.x));
+    const float2 r = *reinterpret_cast<const float2*>(lutK2 + lop3_and_or(ge, 128u, __float_as_uint(c.y)));
+    e = __fsub_rn(xc, r.x);
+    return __float_as_uint(r.y);
 }
 
 // Squares that feed the reference's summation tree.  A packed mul.rn.f32x2 whose only consumer
@@ -138,10 +166,10 @@ __device__ __forceinline__ void store_codes(const uint32_t (&byte_j)[8], uint8_t
     __syncwarp();
     const uint2 v = *reinterpret_cast<const uint2*>(row + 8 * l);
     __syncwarp();
-    if (!valid) return;
     if (aligned8) {
-        *reinterpret_cast<uint2*>(dst + 8 * l) = v;
+        st_global_v2_if(reinterpret_cast<unsigned long long>(dst) + 8 * l, v, valid);
     } else {
+        if (!valid) return;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             dst[8 * l + i] = static_cast<uint8_t>(v.x >> (8 * i));
@@ -162,51 +190,61 @@ struct PackDump {
 // 8 bytes (code rows leave as 8-byte stores); a template argument so that the byte-store sequence
 // of the other case is not part of this kernel's instruction stream.  DUMP: the debug instance of
 // the turbo_prod kernel, which also writes its intermediates (never launched by the pack entry points).
-template <int S, bool ALIGNED8, bool DUMP = false>
-__global__ void __launch_bounds__(kPackWarps * 32)
+// POW2: the kv head count and the tokens per page are powers of two (every layout in use), so
+// token = row / H and page = slot / block_size are shifts; the other instance divides.
+template <int S, bool ALIGNED8, bool DUMP = false, bool POW2 = false>
+__global__ void __launch_bounds__(kPackWarps * 32, (DUMP || S == 0) ? 0 : 4)
 pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                const int32_t* __restrict__ slot_mapping, uint8_t* __restrict__ page_pool,
                PageGeom geo, IndexDiv div_heads, IndexDiv div_block, int head_dim,
-               long long num_rows, float zero, PackDump dump) {
+               int num_rows, float zero, PackDump dump) {
     constexpr bool PROD = S == 0, QJL = S == 2;
     constexpr bool TREE128 = PROD || QJL;  // sum of squares: 128-leaf tree (prod, QJL) or 64 pair leaves (mse)
     __shared__ __align__(16) float xchg[kPackWarps][kXchgWarpFloats];
-    __shared__ __align__(128) uint8_t lutK[PROD ? kCellsK * kLutRowBytes : 16];
+    __shared__ __align__(128) uint8_t lutK1[PROD ? kCellsK * kLutRowBytes : 16];
+    __shared__ __align__(128) uint8_t lutK2[PROD ? 32 * kLutRowBytes : 16];
     __shared__ __align__(128) uint8_t lutV[kCellsV * kLutRowBytes];
-    build_luts(lutK, lutV, PROD);
+    build_luts(lutK1, lutK2, lutV, PROD);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rr = lane >> 3, l = lane & 7;
-    const uint32_t rep_v = (lane & 15) * 8, rep_k = (lane & 7) * 16;
+    const uint32_t rep_v = (lane & 15) * 8;
     float* buf = xchg[warp];
     uint8_t* code_buf = reinterpret_cast<uint8_t*>(buf);
     const int H = geo.num_kv_heads;
     const float c = inv_sqrt_dim(head_dim);
     const float2 zero2 = make_float2(zero, zero);
-    const long long groups = (num_rows + 3) >> 2;
-    const long long warps_total = static_cast<long long>(gridDim.x) * kPackWarps;
+    const int groups = (num_rows + 3) >> 2;  // rows are counted in 32 bits (checked by the launcher)
+    const int warps_total = static_cast<int>(gridDim.x) * kPackWarps;
+    // loop-invariant halves of the addresses: a row is 256 bytes of fp16, this lane's part starts at 32 l
+    const unsigned long long key64 = reinterpret_cast<unsigned long long>(key) + 32 * l;
+    const unsigned long long val64 = reinterpret_cast<unsigned long long>(value) + 32 * l;
+    const unsigned long long slots64 = reinterpret_cast<unsigned long long>(slot_mapping);
+    const unsigned long long pool64 = reinterpret_cast<unsigned long long>(page_pool);
+    const unsigned int page_size32 = static_cast<unsigned int>(geo.page_size);
 
-    for (long long g = static_cast<long long>(blockIdx.x) * kPackWarps + warp; g < groups;
-         g += warps_total) {
-        const long long row_raw = g * 4 + rr;
+    for (int g = blockIdx.x * kPackWarps + warp; g < groups; g += warps_total) {
+        const int row_raw = g * 4 + rr;
         const bool valid = row_raw < num_rows;
-        const long long row = valid ? row_raw : num_rows - 1;  // keep all lanes converged
-        const long long tok = index_div(row, div_heads);
-        const int h = static_cast<int>(row - tok * H);
+        const int row = valid ? row_raw : num_rows - 1;  // keep all lanes converged
+        const int tok = POW2 ? (row >> div_heads.shift) : row / H;
+        const int h = row - tok * H;
         // odd heads: the whole rotated row is negated; the QJL sign hash has no head term
         // (tq_qjl_kernels.cu:18-21)
         const float cs = (!QJL && (h & 1)) ? -c : c;
 
-        const uint4* kp = key + row * 16 + 2 * l;
-        const uint4* vp = value + row * 16 + 2 * l;
+        const uint4* kp = reinterpret_cast<const uint4*>(mad_wide(row, 256u, key64));
+        const uint4* vp = reinterpret_cast<const uint4*>(mad_wide(row, 256u, val64));
         const uint4 k_lo = ld_stream(kp), k_hi = ld_stream(kp + 1);
         const uint4 v_lo = ld_stream(vp), v_hi = ld_stream(vp + 1);
-        const int slot = __ldg(slot_mapping + tok);
+        const int slot = __ldg(reinterpret_cast<const int32_t*>(mad_wide(tok, 4u, slots64)));
 
-        const int blk = index_div(slot, div_block);
+        const int blk = POW2 ? (slot >> div_block.shift) : slot / geo.block_size;
         const int tib = slot - blk * geo.block_size;
-        uint8_t* page = page_pool + static_cast<unsigned long long>(blk) * geo.page_size;
+        const unsigned long long page64 = mad_wide(blk, page_size32, pool64);
+        uint8_t* page = reinterpret_cast<uint8_t*>(page64);
         const unsigned int th = static_cast<unsigned int>(tib * H + h);
+        const bool head_lane = valid && l == 0;  // the lane that writes the row's scales
 
         float2 x[8], y[8];
 
@@ -265,12 +303,12 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             for (int j = 0; j < 8; ++j) {
                 float e0, e1;
                 const float2 kn = div_by2(y[j], krms, kr);
-                const uint32_t n0 = quant_k3_lut(kn.x, lutK, rep_k, e0);
-                const uint32_t n1 = quant_k3_lut(kn.y, lutK, rep_k, e1);
+                const uint32_t n0 = quant_k3_lut(kn.x, lutK1, lutK2, rep_v, e0);
+                const uint32_t n1 = quant_k3_lut(kn.y, lutK1, lutK2, rep_v, e1);
                 kbytes[j] = n0 | (n1 << 4);
                 e2[j] = square2(make_float2(e0, e1), zero2);
                 if (DUMP && valid) {  // element 2l + b + 16j of the row
-                    const long long at = row * kHeadDim + 2 * l + 16 * j;
+                    const long long at = static_cast<long long>(row) * kHeadDim + 2 * l + 16 * j;
                     if (dump.k_rot) { dump.k_rot[at] = y[j].x; dump.k_rot[at + 1] = y[j].y; }
                     if (dump.kn) {
                         dump.kn[at] = fminf(fmaxf(kn.x, -2.5f), 2.5f);
@@ -280,10 +318,8 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 }
             }
             const float rms_e = rms_from_sum(tree128(e2));
-            if (valid && l == 0) {
-                *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
-                *reinterpret_cast<__half*>(page + geo.k_res + th * 2) = __float2half_rn(rms_e);
-            }
+            st_global_u16_if(mad_wide(geo.k_scales + th * 2, 1u, page64), __half_as_ushort(__float2half_rn(krms)), head_lane);
+            st_global_u16_if(mad_wide(geo.k_res + th * 2, 1u, page64), __half_as_ushort(__float2half_rn(rms_e)), head_lane);
         } else {
             float pr[8];
 #pragma unroll
@@ -296,12 +332,11 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 const float2 kn = div_by2(y[j], krms, kr);
                 kbytes[j] = quant_v4_lut(kn.x, lutV, rep_v) | (quant_v4_lut(kn.y, lutV, rep_v) << 4);
             }
-            if (valid && l == 0)
-                *reinterpret_cast<__half*>(page + geo.k_scales + th * 2) = __float2half_rn(krms);
+            st_global_u16_if(mad_wide(geo.k_scales + th * 2, 1u, page64), __half_as_ushort(__float2half_rn(krms)), head_lane);
         }
         if (!QJL)
-            store_codes(kbytes, code_buf, page + geo.k_codes + th * 64, lane, valid,
-                        ALIGNED8);
+            store_codes(kbytes, code_buf, reinterpret_cast<uint8_t*>(mad_wide(geo.k_codes + th * 64, 1u, page64)), lane,
+                        valid, ALIGNED8);
 
         // ---------------- V ----------------
         fwht_phase1_from_half(v_lo, v_hi, x);
@@ -330,7 +365,7 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
             const uint32_t c0 = quant_v4_lut(vn.x, lutV, rep_v), c1 = quant_v4_lut(vn.y, lutV, rep_v);
             vbytes[j] = c0 | (c1 << 4);
             if (DUMP && valid) {
-                const long long at = row * kHeadDim + 2 * l + 16 * j;
+                const long long at = static_cast<long long>(row) * kHeadDim + 2 * l + 16 * j;
                 if (dump.v_rot) { dump.v_rot[at] = y[j].x; dump.v_rot[at + 1] = y[j].y; }
                 if (dump.vn) {
                     dump.vn[at] = fminf(fmaxf(vn.x, -2.75f), 2.75f);
@@ -339,10 +374,9 @@ pack_kv_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value,
                 if (dump.vidx) { dump.vidx[at] = static_cast<int>(c0); dump.vidx[at + 1] = static_cast<int>(c1); }
             }
         }
-        if (valid && l == 0)
-            *reinterpret_cast<__half*>(page + geo.v_scales + th * 2) = __float2half_rn(vrms);
-        store_codes(vbytes, code_buf, page + geo.v_codes + th * 64, lane, valid,
-                    ALIGNED8);
+        st_global_u16_if(mad_wide(geo.v_scales + th * 2, 1u, page64), __half_as_ushort(__float2half_rn(vrms)), head_lane);
+        store_codes(vbytes, code_buf, reinterpret_cast<uint8_t*>(mad_wide(geo.v_codes + th * 64, 1u, page64)), lane,
+                    valid, ALIGNED8);
     }
 }
 
@@ -358,16 +392,21 @@ void launch_pack(int scheme, const void* key, const void* value, const int32_t* 
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     const bool aligned = (reinterpret_cast<uintptr_t>(pool) & 7) == 0 && (geo.page_size & 7) == 0;
-#define TQ_PACK_LAUNCH1(SV, AL)                                                                \
-    pack_kv_kernel<SV, AL><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(         \
-        static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,    \
-        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f, PackDump{})
+    if (rows > INT_MAX) throw std::runtime_error("pack: more than 2^31 - 1 token-heads in one call");
+    const IndexDiv dh = make_index_div(geo.num_kv_heads), db = make_index_div(geo.block_size);
+    const bool pow2 = dh.shift >= 0 && db.shift >= 0;
+#define TQ_PACK_LAUNCH2(SV, AL, P2)                                                            \
+    pack_kv_kernel<SV, AL, false, P2><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>( \
+        static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo, dh, db, head_dim, \
+        static_cast<int>(rows), 0.0f, PackDump{})
+#define TQ_PACK_LAUNCH1(SV, AL) do { if (pow2) TQ_PACK_LAUNCH2(SV, AL, true); else TQ_PACK_LAUNCH2(SV, AL, false); } while (0)
 #define TQ_PACK_LAUNCH(SV) do { if (aligned) TQ_PACK_LAUNCH1(SV, true); else TQ_PACK_LAUNCH1(SV, false); } while (0)
     if (scheme == TQ_SCHEME_TURBO_PROD) TQ_PACK_LAUNCH(0);
     else if (scheme == TQ_SCHEME_TURBO_MSE) TQ_PACK_LAUNCH(1);
     else TQ_PACK_LAUNCH(2);
 #undef TQ_PACK_LAUNCH
 #undef TQ_PACK_LAUNCH1
+#undef TQ_PACK_LAUNCH2
     check_launch(scheme == TQ_SCHEME_TURBO_PROD ? "turbo_prod pack_kv"
                  : scheme == TQ_SCHEME_TURBO_MSE ? "turbo_mse pack_kv" : "qjl pack_kv");
 }
@@ -383,9 +422,10 @@ void launch_pack_debug(const void* key, const void* value, const int32_t* slots,
     if (blocks > cap) blocks = cap;
     const PackDump dump{k_rot, v_rot, kn, vn, kidx, vidx};
     // the byte-store instance: any pool alignment, this entry point is not a hot path
-    pack_kv_kernel<0, false, true><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
+    if (rows > INT_MAX) throw std::runtime_error("pack: more than 2^31 - 1 token-heads in one call");
+    pack_kv_kernel<0, false, true, false><<<static_cast<unsigned>(blocks), kPackWarps * 32, 0, stream>>>(
         static_cast<const uint4*>(key), static_cast<const uint4*>(value), slots, pool, geo,
-        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, rows, 0.0f, dump);
+        make_index_div(geo.num_kv_heads), make_index_div(geo.block_size), head_dim, static_cast<int>(rows), 0.0f, dump);
     check_launch("turbo_prod pack_kv (debug)");
 }
 
