@@ -368,44 +368,40 @@ prefill_tc_kernel(PrefillTcParams p) {
         // 16-byte piece uq of token ut sits at an XOR-ed position, so the 16-byte reads of eight
         // neighbouring tokens cover all banks
         const uint32_t code_off = static_cast<uint32_t>(ut * 64 + ((uq ^ ((ut >> 1) & 3)) << 4));
-        // Block-table entries: lane l of a warp holds the entry of prefix tile ids_base + l / 2, page
-        // 2 (warp % 2) + l % 2 of that tile (a warp's 32 tokens lie in two pages), i.e. 16 tiles per
-        // load; the next 16 are loaded half a block early and handed out by shuffles.
-        const int page_sel = 2 * ((u >> 5) & 1);
-        auto load_ids = [&](int base_tile) {
-            const int tile = base_tile + (lane >> 1);
-            if (tile >= n_pref) return 0;
-            const int t = min((tile_lo + tile) * kTileTok + 16 * (page_sel + (lane & 1)), n_prefix - 1);
-            return __ldg(table + (t >> 4));
+        // Source addresses: a thread always copies the same in-page bytes (token ut % 16 of its page, quarter
+        // uq), so everything but the page is loop-invariant and an address is one wide multiply-add of the
+        // page id.  Tokens past the end of the prefix read the prefix's last page (any finite bytes do: their
+        // scales are written as zero and their scores masked).  The page id of tile it + 2 is loaded while
+        // tile it + 1 is prefetched: one 4-byte load per thread and tile, no shuffles.
+        const uint32_t page_size32 = static_cast<uint32_t>(p.geo.page_size);
+        const unsigned th = static_cast<unsigned>((ut & 15) * H + h);
+        const unsigned long long pool64 = reinterpret_cast<unsigned long long>(p.pool);
+        const unsigned long long k_src = pool64 + p.geo.k_codes + th * 64 + 16 * uq;
+        const unsigned long long v_src = pool64 + p.geo.v_codes + th * 64 + 16 * uq;
+        const unsigned long long ks_src = pool64 + p.geo.k_scales + ((th * 2) & ~3u);
+        const unsigned long long vs_src = pool64 + p.geo.v_scales + ((th * 2) & ~3u);
+        const int last_page = (n_prefix - 1) >> 4;
+        const int page0 = tile_lo * (kTileTok / 16) + (ut >> 4);  // index of this thread's page of tile 0
+        auto load_id = [&](int it) {
+            return it < n_pref ? __ldg(table + min(page0 + (kTileTok / 16) * it, last_page)) : 0;
         };
-        int ids_base = 0, ids_cur = load_ids(0), ids_next = 0;
-        auto page_of = [&](int it) {   // warp-uniform control flow
-            if (it - ids_base >= 16) {
-                ids_cur = ids_next;
-                ids_base += 16;
-            }
-            if (it - ids_base == 8) ids_next = load_ids(ids_base + 16);
-            int page = __shfl_sync(0xffffffffu, ids_cur, 2 * (it - ids_base) + ((ut >> 4) & 1));
-            // tokens past the end of the prefix read the last valid token's page
-            const int t = (tile_lo + it) * kTileTok + ut;
-            if (t >= n_prefix) page = __ldg(table + ((n_prefix - 1) >> 4));
-            return page;
-        };
-        auto prefetch = [&](int it) {
-            if (it < n_pref) {
-                const int page = page_of(it);
-                const int t = min((tile_lo + it) * kTileTok + ut, n_prefix - 1);
-                const uint8_t* pg = p.pool + static_cast<unsigned long long>(page) * p.geo.page_size;
-                const unsigned th = static_cast<unsigned>((t & 15) * H + h);
-                const uint32_t dst = raw_base + (it % kRawStages) * kRawStage;
-                cp_async16_t(dst + code_off, pg + p.geo.k_codes + th * 64 + 16 * uq);
-                cp_async16_t(dst + 4096 + code_off, pg + p.geo.v_codes + th * 64 + 16 * uq);
+        int pf_it = 0, pf_id = load_id(0), pf_id_next = load_id(1);
+        uint32_t pf_dst = raw_base;  // stage of tile pf_it
+        auto prefetch_next = [&]() {
+            if (pf_it < n_pref) {
+                const uint32_t page = static_cast<uint32_t>(pf_id);
+                cp_async16_t(pf_dst + code_off, reinterpret_cast<const void*>(mad_wide(page, page_size32, k_src)));
+                cp_async16_t(pf_dst + 4096 + code_off, reinterpret_cast<const void*>(mad_wide(page, page_size32, v_src)));
                 if (uq == 0) {  // the aligned 4-byte words that hold this token-head's two fp16 scales
-                    cp_async4_t(dst + 8192 + ut * 8, pg + p.geo.k_scales + ((th * 2) & ~3u));
-                    cp_async4_t(dst + 8192 + ut * 8 + 4, pg + p.geo.v_scales + ((th * 2) & ~3u));
+                    cp_async4_t(pf_dst + 8192 + ut * 8, reinterpret_cast<const void*>(mad_wide(page, page_size32, ks_src)));
+                    cp_async4_t(pf_dst + 8192 + ut * 8 + 4, reinterpret_cast<const void*>(mad_wide(page, page_size32, vs_src)));
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");  // one group per tile, empty or not
+            pf_id = pf_id_next;
+            pf_id_next = load_id(pf_it + 2);
+            ++pf_it;
+            pf_dst = pf_dst == raw_base + (kRawStages - 1) * kRawStage ? raw_base : pf_dst + kRawStage;
         };
         // four code words (32 codes) -> four 16-byte units of fp16 operands.  All table loads are
         // issued before the first store: shared-memory stores and loads through unrelated pointers
@@ -427,22 +423,22 @@ prefill_tc_kernel(PrefillTcParams p) {
         };
         // one tile: its raw bytes have landed -> start the copies of tile it + 2 -> wait for the
         // operand stage -> unpack (or copy a chunk tile)
+        int st = 0, kv_round = 0;        // operand stage of the tile in hand (it % kKvStages), it / kKvStages
+        uint32_t raw_rd = kOffRaw;       // raw stage of the tile in hand
+        const uint32_t sc_rd = 8192u + ut * 8u + ((th * 2u) & 2u);
         auto do_tile = [&](int it) {
-            const int st = it % kKvStages;
             asm volatile("cp.async.wait_group 1;" ::: "memory");  // every byte a thread reads it copied itself
-            prefetch(it + 2);
-            if (it >= kKvStages && !warp_wait(bar_kv_empty + 8 * st, (it / kKvStages - 1) & 1)) { fail = 1; return; }
+            prefetch_next();  // tile it + 2
+            if (kv_round > 0 && !warp_wait(bar_kv_empty + 8 * st, (kv_round - 1) & 1)) { fail = 1; return; }
             uint8_t* ktile = smem + kOffKV + st * 32768;
             uint8_t* vtile = ktile + 16384;
             float* kscale = reinterpret_cast<float*>(smem + kOffScale) + st * 128;
             float* vscale = kscale + 64;
             if (it < n_pref) {
-                const uint8_t* rawst = smem + kOffRaw + (it % kRawStages) * kRawStage;
+                const uint8_t* rawst = smem + raw_rd;
                 const uint4 kc = *reinterpret_cast<const uint4*>(rawst + code_off);
                 const uint4 vc = *reinterpret_cast<const uint4*>(rawst + 4096 + code_off);
                 const int t0 = (tile_lo + it) * kTileTok;
-                const int tcl = min(t0 + ut, n_prefix - 1);
-                const uint32_t sc_rd = 8192u + ut * 8u + ((((tcl & 15) * H + h) * 2u) & 2u);
                 const unsigned short ks_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd);
                 const unsigned short vs_bits = *reinterpret_cast<const unsigned short*>(rawst + sc_rd + 4);
                 // this thread's 32 dims: dim chunk uh of the tile, units 4 (uq % 2) .. + 3 inside it
@@ -478,9 +474,14 @@ prefill_tc_kernel(PrefillTcParams p) {
             }
             fence_async_smem();
             mbar_arrive(bar_kv_full + 8 * st);
+            if (++st == kKvStages) {
+                st = 0;
+                ++kv_round;
+            }
+            raw_rd = raw_rd == kOffRaw + (kRawStages - 1) * kRawStage ? kOffRaw : raw_rd + kRawStage;
         };
-        prefetch(0);
-        prefetch(1);
+        prefetch_next();
+        prefetch_next();
         for (int it = 0; it < n_tiles && !fail; ++it) do_tile(it);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp == 12) {
