@@ -732,6 +732,8 @@ def ours(args):
             sec["longctx_kvsplit_nccl"] = lc.get("nccl")
         torch.cuda.empty_cache()
         if rank == 0 and world == 1:
+            sec["decode_turbo_mse"] = decode_mse_numbers(torch, tq, dev, gen, B, N, HQ, H, peak)
+            torch.cuda.empty_cache()
             sec["prefill_turbo_mse"] = prefill_numbers(torch, tq, dev, gen)
             if not args.skip_cpu:
                 sec["cpu_attention_ref_single_head"] = cpu_attention_ref_numbers()
@@ -741,6 +743,50 @@ def ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def decode_mse_numbers(torch, tq, dev, gen, B, N, HQ, H, peak, layers=4, steps=5):
+    """The headline decode shape over turbo_mse pages (4-bit K and V, 132 bytes per token-head): `layers`
+    pools of B sequences x N tokens packed on the device, pages permuted, every launch reads another pool
+    (inputs larger than L2)."""
+    cfg = tq.default_config()
+    cfg.num_kv_heads = H
+    lay = tq.make_mse_layout_for(cfg)
+    pages_per_seq = N // 16
+    pages = B * pages_per_seq
+    pools = torch.zeros(layers, pages * lay.page_size_bytes, dtype=torch.uint8, device=dev)
+    tables = torch.empty(layers, B, pages_per_seq, dtype=torch.int32, device=dev)
+    tpos = torch.arange(N, device=dev)
+    for l in range(layers):
+        tables[l] = torch.randperm(pages, device=dev, generator=gen).to(torch.int32).view(B, pages_per_seq)
+        for b in range(B):
+            k, v = synth_kv(torch, N, H, dev, gen)
+            slots = (tables[l, b][tpos // 16].to(torch.int64) * 16 + tpos % 16).to(torch.int32)
+            tq.mse_pack(k, v, slots, pools[l], lay, cfg)
+    lens = torch.full((B,), N, dtype=torch.int32, device=dev)
+    q = torch.randn(layers, B, HQ, 128, device=dev, generator=gen).to(torch.float16)
+    out = torch.zeros(layers, B, HQ, 128, dtype=torch.float16, device=dev)
+    ws = torch.empty(max(tq.decode_workspace_bytes(B, HQ, N, cfg), 16), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        for l in range(layers):
+            tq.decode_paged("turbo_mse", q[l], pools[l], tables[l], lens, lay, cfg, output=out[l],
+                            max_kv_tokens=N, workspace=ws, stream=stream)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (steps * layers)
+    nbytes = B * (N * H * 132 + pages_per_seq * 4)
+    gbs = nbytes / (us * 1e-6) / 1e9
+    return {"value": gbs, "unit": UNIT, "us_per_layer": us, "frac_of_hbm_peak": gbs / peak,
+            "bytes_per_launch": nbytes, "shape": f"b{B}_kv{N}_q{HQ}kv{H}"}
 
 
 def prefill_numbers(torch, tq, dev, gen, batch=8, nq=256, n=32768, hq=16, h=2, iters=5):

@@ -1092,7 +1092,7 @@ decode_paged16_kernel(DecodeParams p) {
         cur.vs1 = ld(256 + 16 * H);
         cur.re0 = PROD ? ld(512) : 0.0f;
         cur.re1 = PROD ? ld(512 + 16 * H) : 0.0f;
-        if (kRagged) {
+        if (kRagged && tb + 16 > r.t_end) {
             // rows past the end of the sequence may hold anything: zero their scales so that
             // P * vs stays finite (their logits are masked to -inf in process_block)
             if (tb + g >= r.t_end) cur.ks0 = cur.vs0 = cur.re0 = 0.0f;
@@ -1103,10 +1103,17 @@ decode_paged16_kernel(DecodeParams p) {
         stage = stage == kStages - 1 ? 0 : stage + 1;
         tb += 16 * kStreams;
     };
-    const bool last_ragged = n_iter > 0 && tb + 16 * kStreams * (n_iter - 1) + 16 > r.t_end;
-    const int n_full = last_ragged ? n_iter - 1 : n_iter;
-    for (int it = 0; it < n_full; ++it) step(it, std::false_type{});
-    if (last_ragged) step(n_full, std::true_type{});
+    // (turbo_mse pages: the single loop with the run-time check measured 3635 GB/s against 3215 with
+    // the second copy, turbo_prod pages 3228 against 3330 -- hence per scheme.)
+    constexpr bool kPeelRagged = PROD;
+    if constexpr (kPeelRagged) {
+        const bool last_ragged = n_iter > 0 && tb + 16 * kStreams * (n_iter - 1) + 16 > r.t_end;
+        const int n_full = last_ragged ? n_iter - 1 : n_iter;
+        for (int it = 0; it < n_full; ++it) step(it, std::false_type{});
+        if (last_ragged) step(n_full, std::true_type{});
+    } else {
+        for (int it = 0; it < n_iter; ++it) step(it, std::true_type{});
+    }
     cp_async_wait<0>();
     decode_epilogue(p, kFastWarpBytes, ctx, r, st);
 }
