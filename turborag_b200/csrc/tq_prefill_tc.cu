@@ -121,6 +121,25 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// The same with the descriptor handed over as its two 32-bit words and the accumulate flag as a
+// template argument.  One thread issues every MMA of a CTA and waits until the tensor pipe takes each
+// one; whatever it computes between two MMAs is added to that.  The words of a descriptor differ
+// between k-steps only by a constant in the low one (start address >> 4).
+template <bool ACCUMULATE>
+__device__ __forceinline__ void mma_f16_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, {%6, %6, %6, %6}, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACCUMULATE ? 1 : 0), "r"(0u) : "memory");
+}
+// Low and high word of make_desc(addr, lbo, sbo).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
@@ -490,32 +509,43 @@ prefill_tc_kernel(PrefillTcParams p) {
             // Two counters: S tiles issued, P V tiles issued.  Whichever operand set is ready first
             // is issued first; S may run at most two tiles ahead of P V (two S buffers).
             int next_s = 0, next_pv = 0, idle = 0;
+            int s_stage = 0, pv_stage = 0;   // next_s % kKvStages, next_pv % kKvStages
+            uint32_t s_phase = 0;            // (next_s / kKvStages) & 1
             while (next_pv < n_tiles) {
                 bool progress = false;
                 if (next_s < n_tiles && next_s <= next_pv + 1 &&
-                    mbar_test(bar_kv_full + 8 * (next_s % kKvStages), (next_s / kKvStages) & 1)) {
+                    mbar_test(bar_kv_full + 8 * s_stage, s_phase)) {
                     tc_fence_after();
-                    const uint32_t k_addr = sbase + kOffKV + (next_s % kKvStages) * 32768;
+                    const uint32_t k_lo = desc_lo(sbase + kOffKV + s_stage * 32768, 16);
+                    const uint32_t s_tmem = tmem + 64 * (next_s & 1);
+                    // k-steps 0-7: Q hi, 8-15: Q lo against the same K tile (dim chunk (ks & 7) / 4, 32 bytes per step)
+                    mma_f16_ts_words<false>(s_tmem, tmem_q, k_lo, desc_hi(1024), kIdescS);
 #pragma unroll
-                    for (int ks = 0; ks < 16; ++ks)  // k-steps 0-7: Q hi, 8-15: Q lo against the same K tile
-                        mma_f16_ts(tmem + 64 * (next_s & 1), tmem_q + 8 * ks,
-                                   make_desc(k_addr + ((ks & 7) >> 2) * 8192 + (ks & 3) * 32, 16, 1024), kIdescS,
-                                   ks > 0 ? 1u : 0u);
+                    for (int ks = 1; ks < 16; ++ks)
+                        mma_f16_ts_words<true>(s_tmem, tmem_q + 8 * ks,
+                                               k_lo + ((((ks & 7) >> 2) * 8192 + (ks & 3) * 32) >> 4), desc_hi(1024), kIdescS);
                     mma_commit(bar_s_full + 8 * (next_s & 1));
                     ++next_s;
+                    if (++s_stage == kKvStages) {
+                        s_stage = 0;
+                        s_phase ^= 1u;
+                    }
                     progress = true;
                 }
                 if (next_pv < next_s && mbar_test(bar_p_full + 8 * (next_pv & 1), (next_pv >> 1) & 1)) {
                     tc_fence_after();
-                    const uint32_t v_addr = sbase + kOffKV + (next_pv % kKvStages) * 32768 + 16384;
+                    const uint32_t v_lo = desc_lo(sbase + kOffKV + pv_stage * 32768 + 16384, 8192);
+                    const uint32_t p_tmem = tmem_p + 32 * (next_pv & 1);
+                    // 16 tokens = 8 TMEM columns of P per instruction
+                    if (next_pv > 0) mma_f16_ts_words<true>(tmem_o, p_tmem, v_lo, desc_hi(1024), kIdescPV);
+                    else mma_f16_ts_words<false>(tmem_o, p_tmem, v_lo, desc_hi(1024), kIdescPV);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)  // 16 tokens = 8 TMEM columns of P per instruction
-                        mma_f16_ts(tmem_o, tmem_p + 32 * (next_pv & 1) + 8 * ks,
-                                   make_desc(v_addr + ks * 2048, 8192, 1024), kIdescPV,
-                                   (next_pv > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 1; ks < 4; ++ks)
+                        mma_f16_ts_words<true>(tmem_o, p_tmem + 8 * ks, v_lo + ks * (2048 >> 4), desc_hi(1024), kIdescPV);
                     mma_commit(bar_pv_done + 8 * (next_pv & 1));
-                    mma_commit(bar_kv_empty + 8 * (next_pv % kKvStages));
+                    mma_commit(bar_kv_empty + 8 * pv_stage);
                     ++next_pv;
+                    if (++pv_stage == kKvStages) pv_stage = 0;
                     progress = true;
                 }
                 if (progress) {
@@ -527,7 +557,7 @@ prefill_tc_kernel(PrefillTcParams p) {
                     if (next_pv < next_s)
                         mbar_try_wait_for(bar_p_full + 8 * (next_pv & 1), (next_pv >> 1) & 1, 1000u);
                     else
-                        mbar_try_wait_for(bar_kv_full + 8 * (next_s % kKvStages), (next_s / kKvStages) & 1, 1000u);
+                        mbar_try_wait_for(bar_kv_full + 8 * s_stage, s_phase, 1000u);
                     if (++idle > kWaitLimit) {
                         fail = 2;
                         break;
